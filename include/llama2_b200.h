@@ -1,0 +1,181 @@
+/*
+ * llama2_b200 -- C ABI of the B200-native llama2.rs token loop.
+ *
+ * Every entry point replaces one seam of the reference crate (file:line given per
+ * declaration, paths relative to the reference project).  All functions return 0 on
+ * success and a negative L2_E* code on failure; l2_last_error() gives the message of
+ * the calling thread's last failure.  No exception or abort crosses this boundary.
+ *
+ * There is no CPU fallback: every compute entry point fails with L2_ECUDA when no
+ * CUDA device is usable.
+ *
+ * Threading: one host thread per model handle; all device work of a handle runs on
+ * one CUDA stream; calls on one handle are not re-entrant.
+ */
+#ifndef LLAMA2_B200_H
+#define LLAMA2_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define L2_OK 0
+#define L2_EINVAL (-1)   /* bad argument */
+#define L2_EFORMAT (-2)  /* checkpoint header / size mismatch (check_static, mmap length assert) */
+#define L2_ECUDA (-3)    /* CUDA runtime failure or no device */
+#define L2_EIO (-4)      /* file could not be opened / read / written */
+#define L2_ERANGE (-5)   /* position / steps beyond SEQ_LEN, token beyond VOCAB_SIZE */
+#define L2_ESTATUS (-6)  /* a device-side bounded wait gave up (status word set) */
+
+#define L2_START 1 /* src/tokenizer.rs:10 */
+#define L2_RET 13  /* src/tokenizer.rs:11 */
+
+/* The reference's compile-time constants (src/constants.rs:7-74) as a run-time record. */
+typedef struct l2_config {
+    int32_t dim;        /* DIM */
+    int32_t hidden_dim; /* HIDDEN_DIM */
+    int32_t n_layers;   /* N_LAYERS */
+    int32_t n_heads;    /* N_HEADS */
+    int32_t n_kv_heads; /* N_HEADS / ATTN_GROUPS */
+    int32_t vocab_size; /* VOCAB_SIZE */
+    int32_t seq_len;    /* SEQ_LEN */
+    int32_t group_size; /* GROUPSIZE: 32 | 64 | 128 */
+} l2_config;
+
+/* What the reference fixes with cargo features (Cargo.toml:28-43, build.rs:5-43). */
+typedef struct l2_options {
+    const char* model_size; /* "7B" | "13B" | "70B"; NULL = take the shape from the file header and attn_groups below */
+    int32_t group_size;     /* group_32 | group_64 | group_128 */
+    int32_t attn_groups;    /* ATTN_GROUPS when model_size is NULL (1 = no GQA) */
+    int32_t device;         /* CUDA device ordinal, -1 = current device */
+    int32_t debug;          /* print the configuration, as LlamaModel::from_file(debug=true) does */
+    int32_t max_batch;      /* largest B accepted by l2_forward / prefill chunk (0 = default 64) */
+    int32_t flags;          /* L2_FLAG_* */
+} l2_options;
+
+#define L2_FLAG_NO_GRAPH 1 /* launch kernels directly instead of replaying the per-token CUDA graph */
+#define L2_FLAG_NO_PDL 2   /* do not use programmatic dependent launch between the kernels of a token */
+
+typedef struct l2_model l2_model;     /* LlamaModel (src/lib.rs:28-36, 68-77) */
+typedef struct l2_state l2_state;     /* RunState (src/models.rs:29-42) */
+typedef struct l2_qlinear l2_qlinear; /* QLinearCuda (src/gptq_cuda.rs:93-110) */
+typedef struct l2_tokenizer l2_tokenizer; /* Tokenizer (src/tokenizer.rs:13-19) */
+
+const char* l2_last_error(void);
+/* Kernels launched by this library in this process so far (graph replays count their nodes). */
+uint64_t l2_launch_count(void);
+
+/* ---- shapes and checkpoint format ------------------------------------------------ */
+
+/* The constants module selected by the 7B/13B/70B features (src/constants.rs:7-41). */
+int l2_preset_config(const char* model_size, int group_size, l2_config* out);
+/* size_of::<QTransformerWeights>() (src/gptq.rs:34-84): payload bytes after the 28-byte header. */
+size_t l2_checkpoint_bytes(const l2_config* c);
+
+/* Seeded synthetic checkpoint in the export.py layout (export.py:83-119): nibbles U{0..15},
+ * zero nibbles U{6..9}, scales U[0.002,0.02], act-order g_index from a seeded permutation,
+ * embeddings/classifier N(0,0.02), norm weights 1+N(0,0.02).  Host only. */
+int l2_synth_fill(const l2_config* c, uint64_t seed, void* payload, size_t nbytes, int threads);
+int l2_synth_write_file(const l2_config* c, uint64_t seed, const char* path, int threads);
+
+/* ---- model handle: LlamaModel::from_file (src/lib.rs:45-63, 88-104) ----------------- */
+
+int l2_model_open(const char* checkpoint, const l2_options* opt, l2_model** out);
+/* The same on the bytes that follow the header (what the reference mmaps at offset 28). */
+int l2_model_open_blob(const l2_config* c, const void* payload, size_t nbytes,
+                       const l2_options* opt, l2_model** out);
+/* Generates the l2_synth_fill checkpoint tensor by tensor straight into device memory. */
+int l2_model_open_synthetic(const l2_config* c, uint64_t seed, const l2_options* opt, l2_model** out);
+void l2_model_close(l2_model* m);
+int l2_model_config(const l2_model* m, l2_config* out);
+/* LlamaModel::prefill() (src/lib.rs:41-43, 84-86): 1, batched prefill is supported. */
+int l2_model_prefill(const l2_model* m);
+/* Run this handle's device work on a caller-owned cudaStream_t (NULL = the handle's own). */
+int l2_model_set_stream(l2_model* m, void* cuda_stream);
+/* Packed weight bytes one decode token must stream: all QLinear qweight+qzeros+scales,
+ * the f32 classifier and the norm weights. */
+uint64_t l2_model_decode_bytes(const l2_model* m);
+
+/* ---- run state: RunState::new (src/models.rs:36-41) --------------------------------- */
+
+int l2_state_new(l2_model* m, l2_state** out); /* device-resident KV cache, zeroed */
+int l2_state_reset(l2_state* s);               /* zero the caches and rewind to position 0 */
+void l2_state_free(l2_state* s);
+/* Debug read-back of one layer's caches, [SEQ][KVH][HS] each (either pointer may be NULL). */
+int l2_state_read_kv(l2_state* s, int layer, float* key_cache, float* value_cache);
+
+/* ---- forward pass: transformer<B> (src/models.rs:178-298) ---------------------------- */
+
+/* tokens[B], pos[B] host arrays; logits (host, VOCAB floats) is written only when B == 1
+ * and may be NULL. */
+int l2_forward(l2_model* m, l2_state* s, const int32_t* tokens, const int32_t* pos, int B, float* logits);
+
+/* ---- token loop: prefill<A> + generate (src/inference.rs:16-193) --------------------- */
+
+/* The prefill ladder (src/inference.rs:78-127): feeds [START, prompt...] positions in
+ * chunks while pos + chunk < n_prompt and returns the first position left to the B=1
+ * loop.  The ladder 64/32/16/8/4/2 is used when chunk == 0. */
+int l2_prefill(l2_model* m, l2_state* s, const int32_t* prompt, int n_prompt, int chunk, int32_t* pos_out);
+
+/* One iteration of the decode loop (src/inference.rs:141-190) with the host in the loop:
+ * forward at `pos`, then next = forced_next if >= 0, else argmax (temperature == 0) or
+ * a temperature sample drawn with *rng_seed (src/util.rs:71-113). */
+int l2_decode_step(l2_model* m, l2_state* s, int32_t token, int32_t pos, float temperature,
+                   uint64_t* rng_seed, int32_t forced_next, int32_t* next, float* logits);
+
+/* Positions [pos0, steps) of the decode loop without host round trips: token selection
+ * stays on the device and the per-token graph is replayed back to back.  out_tokens gets
+ * steps - pos0 ids (teacher-forced ones included). */
+int l2_decode_run(l2_model* m, l2_state* s, const int32_t* prompt, int n_prompt, int32_t pos0,
+                  int32_t steps, float temperature, uint64_t* rng_seed, int32_t* out_tokens);
+
+/* generate() on token ids (the reference takes text and encodes it, src/inference.rs:62-67).
+ * A fresh RunState is used, as in the reference (src/inference.rs:59).  logits_trace
+ * (NULL or [n_out][VOCAB]) forces one host round trip per token.  elapsed/prefill/decode
+ * times are device times in ms.  Returns the number of tokens written or a negative code. */
+int l2_generate_ids(l2_model* m, const int32_t* prompt, int n_prompt, int steps, float temperature,
+                    uint64_t* rng_seed, int use_prefill, int32_t* out_tokens, int32_t* out_pos0,
+                    float* logits_trace, double* elapsed_ms, double* prefill_ms, double* decode_ms);
+
+/* ---- one quantised linear layer: QLinear::matvec<B> (src/gptq.rs:94-176,
+ *      src/gptq_cuda.rs:50-90, 120-179) ---------------------------------------------- */
+
+/* Arrays are host pointers in the checkpoint layout: qweight [OUT][IN/8] i32,
+ * qzeros [OUT/8][GROUPS] i32, scales [OUT][GROUPS] f32, g_index [IN] i32. */
+int l2_qlinear_create(int in, int out, int group_size, const int32_t* qweight, const int32_t* qzeros,
+                      const float* scales, const int32_t* g_index, int device, l2_qlinear** h);
+/* x [B][IN] -> xout [B][OUT], host f32 buffers; copies to and from the device inside the call. */
+int l2_qlinear_matvec(l2_qlinear* h, const float* x, float* xout, int B);
+/* The same on device buffers, enqueued on cuda_stream (no copies, no synchronisation). */
+int l2_qlinear_matvec_dev(l2_qlinear* h, const float* x_dev, float* xout_dev, int B, void* cuda_stream);
+void l2_qlinear_free(l2_qlinear* h);
+
+/* ---- sampling helpers (src/util.rs:39-46, 71-113) ----------------------------------- */
+uint32_t l2_random_u32(uint64_t* seed);
+float l2_random_f32(uint64_t* seed);
+
+/* ---- tokenizer (src/tokenizer.rs:22-108, src/util.rs:29-37,116-123); host only ------- */
+int l2_tokenizer_open(const char* filename, int vocab_size, l2_tokenizer** out);
+void l2_tokenizer_free(l2_tokenizer* t);
+/* bpe_encode: returns the number of ids (written up to cap), or a negative code. */
+int l2_tokenizer_encode(const l2_tokenizer* t, const char* text, int32_t* ids, int cap);
+/* vocab[id] as a NUL-terminated UTF-8 string owned by the tokenizer. */
+const char* l2_tokenizer_vocab(const l2_tokenizer* t, int32_t id);
+/* get_token (src/util.rs:116-123): strips one leading space after START. */
+const char* l2_tokenizer_piece(const l2_tokenizer* t, int32_t prev, int32_t next);
+
+/* ---- host-side repack, exposed so that it can be checked without a GPU --------------- */
+/* Device layout of one QLinear as built at load time: returns malloc'ed arrays the caller
+ * frees with l2_host_free.  rows_order (NULL or [OUT]) re-orders output rows. */
+int l2_debug_repack(int in, int out, int group_size, const int32_t* qweight, const int32_t* qzeros,
+                    const float* scales, const int32_t* rows_order, uint32_t** qw_dev, float** scales_dev,
+                    uint32_t** zeros_dev, int* groups_padded);
+void l2_host_free(void* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

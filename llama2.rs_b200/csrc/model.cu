@@ -1,0 +1,786 @@
+// Model handle, run state and token loop behind the C ABI: loads a checkpoint into the
+// device layout, captures the per-token forward (src/models.rs:178-298) into CUDA graphs
+// and drives prefill / decode (src/inference.rs:16-193).
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "model.h"
+
+using namespace l2;
+
+namespace l2 {
+
+static int dev_alloc(void** p, size_t bytes, std::vector<void*>& allocs, size_t* total = nullptr) {
+    L2_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+    allocs.push_back(*p);
+    if (total) *total += bytes;
+    return L2_OK;
+}
+
+template <class T>
+static int dev_upload(T** p, const void* src, size_t count, std::vector<void*>& allocs, size_t* total = nullptr) {
+    if (int rc = dev_alloc(reinterpret_cast<void**>(p), count * sizeof(T), allocs, total)) return rc;
+    L2_CUDA(cudaMemcpy(*p, src, count * sizeof(T), cudaMemcpyHostToDevice));
+    return L2_OK;
+}
+
+static int ilog2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }
+
+int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vector<void*>& allocs, size_t* bytes) {
+    d.in = p.in; d.out = p.out; d.gp = p.gp;
+    d.gshift = ilog2((p.in / p.groups) / 32);
+    const int slabs = (p.in / 32 + 31) / 32;  // warp-wide 128-bit loads per row
+    d.ks = 1;
+    while (d.ks * 2 <= slabs && d.ks < GEMV_WARPS) d.ks *= 2;
+    if (int rc = dev_upload(&d.qw, p.qw.data(), p.qw.size() / 4, allocs, bytes)) return rc;
+    if (int rc = dev_upload(&d.sc, p.sc.data(), p.sc.size(), allocs, bytes)) return rc;
+    if (int rc = dev_upload(&d.zr, p.zr.data(), p.zr.size(), allocs, bytes)) return rc;
+    if (g_index) {
+        if (int rc = dev_upload(&d.perm, g_index, (size_t)p.in, allocs, bytes)) return rc;
+        std::vector<int32_t> inv = inverse_permutation(g_index, p.in);
+        if (int rc = dev_upload(&d.inv, inv.data(), (size_t)p.in, allocs, bytes)) return rc;
+    }
+    return L2_OK;
+}
+
+__global__ void permute_kernel(const float* __restrict__ x, const int* __restrict__ perm, float* __restrict__ xp, int n) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n) xp[j] = x[perm[j]];
+}
+
+void launch_permute(const float* x, const int* perm, float* xp, int n, cudaStream_t st) {
+    permute_kernel<<<(n + 255) / 256, 256, 0, st>>>(x, perm, xp, n);
+    g_launches++;
+}
+
+static void fill_job(GemvJob& j, const DevQ& a, const float* x, const float* nw, float* out, int epi) {
+    j = GemvJob{};
+    j.qw = a.qw; j.sc = a.sc; j.zr = a.zr;
+    j.x = x; j.nw = nw; j.out = out;
+    j.rows = a.out; j.in = a.in; j.gp = a.gp; j.gshift = a.gshift; j.ks = a.ks;
+    j.epi = epi;
+}
+
+// Splits `grid` CTAs over the jobs in proportion to their rows (all jobs of a launch share IN).
+static void split_ctas(GemvParams& p, int grid) {
+    long long total = 0;
+    for (int i = 0; i < p.njobs; i++) total += p.job[i].rows;
+    int used = 0;
+    for (int i = 0; i < p.njobs; i++) {
+        int n = i + 1 == p.njobs ? grid - used : (int)((long long)grid * p.job[i].rows / total);
+        if (n < 1) n = 1;
+        p.job[i].cta0 = used;
+        p.job[i].ncta = n;
+        used += n;
+    }
+}
+
+static int gemv_grid(int sms, int in, bool dual, int njobs) {
+    int g = sms * gemv_ctas_per_sm(in, dual);
+    return g < njobs ? njobs : g;
+}
+
+int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, cudaStream_t st) {
+    GemvParams p{};
+    p.njobs = 1;
+    p.eps = 0.f;
+    fill_job(p.job[0], q, xp, nullptr, y, EPI_STORE);
+    const int grid = gemv_grid(sms, q.in, false, 1);
+    split_ctas(p, grid);
+    launch_gemv(p, grid, gemv_smem_bytes(q.in, false), false, st, false);
+    L2_CUDA(cudaGetLastError());
+    return L2_OK;
+}
+
+static int check_device(int device, int* out_dev, int* sms) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        return fail(L2_ECUDA, "no usable CUDA device (%s); this library has no CPU fallback", cudaGetErrorString(e));
+    int dev = device;
+    if (dev < 0) L2_CUDA(cudaGetDevice(&dev));
+    if (dev >= n) return fail(L2_EINVAL, "device %d out of range (%d devices)", dev, n);
+    L2_CUDA(cudaSetDevice(dev));
+    cudaDeviceProp prop;
+    L2_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major < 10) return fail(L2_ECUDA, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+    *out_dev = dev;
+    *sms = prop.multiProcessorCount;
+    L2_CUDA(kernels_init());
+    return L2_OK;
+}
+
+// Builds the device model from a tensor source.
+static int build_model(const Shape& shape, Source& src, const l2_options* opt, l2_model** out) {
+    std::unique_ptr<l2_model> m(new l2_model);
+    m->shape = shape;
+    if (opt) m->opt = *opt;
+    if (int rc = check_device(opt ? opt->device : -1, &m->device, &m->sms)) return rc;
+    m->use_graph = !(m->opt.flags & L2_FLAG_NO_GRAPH);
+    m->use_pdl = !(m->opt.flags & L2_FLAG_NO_PDL);
+    L2_CUDA(cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking));
+    m->stream = m->own_stream;
+    const l2_config& c = shape.c;
+    const int D = c.dim, L = c.n_layers, V = c.vocab_size, G = c.group_size;
+    std::vector<uint32_t> s0, s1, s2, s3;
+    size_t* tot = &m->device_bytes;
+
+    m->eps = *reinterpret_cast<const float*>(src.get(T_RMS_EPS, 0, S_DENSE, s0));
+    if (int rc = dev_upload(&m->tok_emb, src.get(T_TOK_EMB, 0, S_DENSE, s0), (size_t)V * D, m->allocs, tot)) return rc;
+    if (int rc = dev_upload(&m->wcls, src.get(T_WCLS, 0, S_DENSE, s0), (size_t)V * D, m->allocs, tot)) return rc;
+    if (int rc = dev_upload(&m->rms_final, src.get(T_RMS_FINAL, 0, S_DENSE, s0), (size_t)D, m->allocs, tot)) return rc;
+    {   // RoPE table with the reference's f32 formula (src/models.rs:107-110)
+        const int half = HS / 2;
+        std::vector<float> co((size_t)c.seq_len * half), si((size_t)c.seq_len * half);
+        for (int p = 0; p < c.seq_len; p++)
+            for (int i = 0; i < half; i++) {
+                const float freq = 1.0f / powf(10000.0f, (float)(2 * i % HS) / (float)HS);
+                const float val = (float)p * freq;
+                co[(size_t)p * half + i] = cosf(val);
+                si[(size_t)p * half + i] = sinf(val);
+            }
+        if (int rc = dev_upload(&m->rope_cos, co.data(), co.size(), m->allocs, tot)) return rc;
+        if (int rc = dev_upload(&m->rope_sin, si.data(), si.size(), m->allocs, tot)) return rc;
+    }
+
+    m->layers.resize(L);
+    uint64_t qbytes = 0;
+    std::vector<int32_t> gi, gi2;
+    std::vector<float> nw, nwp;
+    auto load_q = [&](int t, int l, DevQ& d, const int32_t* rows_order, std::vector<int32_t>* keep_gi) -> int {
+        int in, outn;
+        shape.qdims(t, &in, &outn);
+        const uint32_t* qw = src.get(t, l, S_QWEIGHT, s0);
+        const uint32_t* qz = src.get(t, l, S_QZEROS, s1);
+        const uint32_t* sc = src.get(t, l, S_SCALES, s2);
+        const uint32_t* gx = src.get(t, l, S_GINDEX, s3);
+        const int32_t* gidx = reinterpret_cast<const int32_t*>(gx);
+        if (!is_permutation(gidx, in)) return fail(L2_EFORMAT, "tensor %d layer %d: g_index is not a permutation of 0..%d", t, l, in - 1);
+        PackedQ p;
+        repack_qlinear(in, outn, G, reinterpret_cast<const int32_t*>(qw), reinterpret_cast<const int32_t*>(qz),
+                       reinterpret_cast<const float*>(sc), rows_order, p);
+        if (keep_gi) keep_gi->assign(gidx, gidx + in);
+        qbytes += (shape.sub_words(t, S_QWEIGHT) + shape.sub_words(t, S_QZEROS) + shape.sub_words(t, S_SCALES)) * 4;
+        return upload_qlinear(p, gidx, d, m->allocs, tot);
+    };
+    auto permuted_norm = [&](const float* w, const std::vector<int32_t>& g, float** dst) -> int {
+        nwp.resize(g.size());
+        for (size_t j = 0; j < g.size(); j++) nwp[j] = w[g[j]];
+        return dev_upload(dst, nwp.data(), nwp.size(), m->allocs, tot);
+    };
+    std::vector<uint32_t> sn;
+    for (int l = 0; l < L; l++) {
+        DevLayer& y = m->layers[l];
+        const float* att = reinterpret_cast<const float*>(src.get(T_RMS_ATT, l, S_DENSE, sn));
+        nw.assign(att, att + D);
+        if (int rc = load_q(T_WQ, l, y.wq, nullptr, &gi)) return rc;
+        if (int rc = permuted_norm(nw.data(), gi, &y.nw_q)) return rc;
+        if (int rc = load_q(T_WK, l, y.wk, nullptr, &gi)) return rc;
+        if (int rc = permuted_norm(nw.data(), gi, &y.nw_k)) return rc;
+        if (int rc = load_q(T_WV, l, y.wv, nullptr, &gi)) return rc;
+        if (int rc = permuted_norm(nw.data(), gi, &y.nw_v)) return rc;
+        if (int rc = load_q(T_WO, l, y.wo, nullptr, nullptr)) return rc;
+        const float* ffn = reinterpret_cast<const float*>(src.get(T_RMS_FFN, l, S_DENSE, sn));
+        nw.assign(ffn, ffn + D);
+        // w2 first: its act-order permutation becomes the row order of w1 and w3, so that the
+        // SwiGLU output is produced directly in w2's K order.
+        if (int rc = load_q(T_W2, l, y.w2, nullptr, &gi2)) return rc;
+        if (int rc = load_q(T_W1, l, y.w1, gi2.data(), &gi)) return rc;
+        if (int rc = permuted_norm(nw.data(), gi, &y.nw_1)) return rc;
+        if (int rc = load_q(T_W3, l, y.w3, gi2.data(), &gi)) return rc;
+        if (int rc = permuted_norm(nw.data(), gi, &y.nw_3)) return rc;
+    }
+    // warm the occupancy cache outside of any stream capture
+    gemv_grid(m->sms, D, false, 1);
+    gemv_grid(m->sms, D, true, 1);
+    gemv_grid(m->sms, c.hidden_dim, false, 1);
+    m->decode_bytes = qbytes + (uint64_t)V * D * 4 + (uint64_t)(2 * L + 1) * D * 4;
+    if (m->opt.debug) {
+        printf("Configuration: Config { dim: %d, hidden_dim: %d, n_layers: %d, n_heads: %d, n_kv_heads: %d, vocab_size: %d, seq_len: %d, group_size: %d }\n",
+               c.dim, c.hidden_dim, c.n_layers, c.n_heads, c.n_kv_heads, c.vocab_size, c.seq_len, c.group_size);
+        printf("CUDA device %d, %d SMs, %.2f GB of weights on device\n", m->device, m->sms, m->device_bytes / 1e9);
+    }
+    *out = m.release();
+    return L2_OK;
+}
+
+static void free_allocs(std::vector<void*>& a) {
+    for (void* p : a) cudaFree(p);
+    a.clear();
+}
+
+// ---- the forward pass as a sequence of launches ------------------------------------------------
+
+static void set_scatter3(float** sdst, const int** sidx, int* n, l2_state* s, const DevLayer* next) {
+    if (!next) { *n = 0; return; }
+    sdst[0] = s->xq; sidx[0] = next->wq.inv;
+    sdst[1] = s->xk; sidx[1] = next->wk.inv;
+    sdst[2] = s->xv; sidx[2] = next->wv.inv;
+    *n = 3;
+}
+
+static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    const bool pdl = m->use_pdl;
+    const int L = c.n_layers, D = c.dim;
+    {
+        EmbedParams e{};
+        e.table = m->tok_emb; e.ctl = s->ctl; e.prompt = s->prompt; e.x = s->x;
+        e.dim = D; e.vocab = c.vocab_size; e.feed_prompt = kind == G_FEED;
+        set_scatter3(e.sdst, e.sidx, &e.nscatter, s, &m->layers[0]);
+        launch_embed(e, st, false);  // first node of the token: plain stream order
+    }
+    for (int l = 0; l < L; l++) {
+        const DevLayer& y = m->layers[l];
+        {   // rmsnorm + wq/wk/wv (src/models.rs:217-226)
+            GemvParams p{};
+            p.njobs = 3; p.eps = m->eps;
+            fill_job(p.job[0], y.wq, s->xq, y.nw_q, s->q, EPI_STORE);
+            fill_job(p.job[1], y.wk, s->xk, y.nw_k, s->k, EPI_STORE);
+            fill_job(p.job[2], y.wv, s->xv, y.nw_v, s->v, EPI_STORE);
+            const int grid = gemv_grid(m->sms, D, false, 3);
+            split_ctas(p, grid);
+            launch_gemv(p, grid, gemv_smem_bytes(D, false), false, st, pdl);
+        }
+        {   // rope + cache append + attention (:228-256)
+            AttnParams a{};
+            a.q = s->q; a.k = s->k; a.v = s->v;
+            const size_t ls = (size_t)c.seq_len * m->shape.kv_dim();
+            a.kc = s->kc + (size_t)l * ls; a.vc = s->vc + (size_t)l * ls;
+            a.rope_cos = m->rope_cos; a.rope_sin = m->rope_sin;
+            a.ctl = s->ctl; a.part = s->part; a.counter = s->counter;
+            a.out = s->att; a.oidx = y.wo.inv;
+            a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups();
+            a.max_split = s->max_split; a.split_min = 64;
+            launch_attn(a, st, pdl);
+        }
+        {   // wo + residual (:260-264); the new x goes to w1's and w3's K order as well
+            GemvParams p{};
+            p.njobs = 1; p.eps = m->eps;
+            fill_job(p.job[0], y.wo, s->att, nullptr, s->x, EPI_RESID);
+            p.job[0].sdst[0] = s->x1; p.job[0].sidx[0] = y.w1.inv;
+            p.job[0].sdst[1] = s->x3; p.job[0].sidx[1] = y.w3.inv;
+            p.job[0].nscatter = 2;
+            const int grid = gemv_grid(m->sms, D, false, 1);
+            split_ctas(p, grid);
+            launch_gemv(p, grid, gemv_smem_bytes(D, false), false, st, pdl);
+        }
+        {   // rmsnorm + w1/w3 + SwiGLU (:266-276)
+            GemvParams p{};
+            p.njobs = 1; p.eps = m->eps;
+            fill_job(p.job[0], y.w1, s->x1, y.nw_1, s->hb, EPI_SWIGLU);
+            p.job[0].qw2 = y.w3.qw; p.job[0].sc2 = y.w3.sc; p.job[0].zr2 = y.w3.zr;
+            p.job[0].x2 = s->x3; p.job[0].nw2 = y.nw_3;
+            const int grid = gemv_grid(m->sms, D, true, 1);
+            split_ctas(p, grid);
+            launch_gemv(p, grid, gemv_smem_bytes(D, true), true, st, pdl);
+        }
+        {   // w2 + residual (:279-285); the new x goes to the next layer's q/k/v K orders
+            GemvParams p{};
+            p.njobs = 1; p.eps = m->eps;
+            fill_job(p.job[0], y.w2, s->hb, nullptr, s->x, EPI_RESID);
+            set_scatter3(p.job[0].sdst, p.job[0].sidx, &p.job[0].nscatter, s, l + 1 < L ? &m->layers[l + 1] : nullptr);
+            const int grid = gemv_grid(m->sms, c.hidden_dim, false, 1);
+            split_ctas(p, grid);
+            launch_gemv(p, grid, gemv_smem_bytes(c.hidden_dim, false), false, st, pdl);
+        }
+    }
+    if (kind == G_DECODE || kind == G_FWD_CLS) {  // final rmsnorm + classifier (:288-297)
+        ClsParams cp{};
+        cp.w = m->wcls; cp.x = s->x; cp.nw = m->rms_final; cp.logits = s->logits;
+        cp.rows = c.vocab_size; cp.in = D; cp.eps = m->eps;
+        launch_cls(cp, m->sms * 2, st, pdl);
+    }
+    if (kind == G_DECODE) {
+        SelectParams sp{};
+        sp.logits = s->logits; sp.ctl = s->ctl; sp.prompt = s->prompt; sp.out_tokens = s->out_tokens; sp.vocab = c.vocab_size;
+        launch_select(sp, st, pdl);
+    } else if (kind == G_FEED) {
+        launch_advance(s->ctl, st, pdl);
+    }
+    L2_CUDA(cudaGetLastError());
+    return L2_OK;
+}
+
+static int nodes_per_forward(const l2_model* m, int kind) {
+    int n = 1 + 5 * m->shape.c.n_layers;
+    if (kind == G_DECODE) n += 2;
+    if (kind == G_FWD_CLS || kind == G_FEED) n += 1;
+    return n;
+}
+
+// Runs one forward of the given kind on the model's stream (graph replay unless disabled).
+static int run_forward(l2_state* s, int kind) {
+    l2_model* m = s->m;
+    if (!m->use_graph) return enqueue_forward(s, kind, m->stream);
+    if (!s->graphs[kind]) {
+        cudaStream_t cap;
+        L2_CUDA(cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking));
+        const unsigned long long before = g_launches;
+        L2_CUDA(cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal));
+        int rc = enqueue_forward(s, kind, cap);
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamEndCapture(cap, &graph);
+        g_launches = before;  // captured launches have not run
+        if (rc != L2_OK) { if (graph) cudaGraphDestroy(graph); cudaStreamDestroy(cap); return rc; }
+        if (e != cudaSuccess) { cudaStreamDestroy(cap); return fail(L2_ECUDA, "graph capture failed: %s", cudaGetErrorString(e)); }
+        e = cudaGraphInstantiate(&s->graphs[kind], graph, 0);
+        cudaGraphDestroy(graph);
+        cudaStreamDestroy(cap);
+        if (e != cudaSuccess) return fail(L2_ECUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+        s->graph_nodes[kind] = nodes_per_forward(m, kind);
+    }
+    L2_CUDA(cudaGraphLaunch(s->graphs[kind], m->stream));
+    g_launches += s->graph_nodes[kind];
+    return L2_OK;
+}
+
+static int write_ctl(l2_state* s, int pos, int token, int n_prompt, int force, float temperature, uint64_t rng) {
+    // Each upload needs its own pinned record until the copy has run: cycle through a ring
+    // (slot 0 is kept for read-backs) and drain the stream when it wraps.
+    if (++s->ctl_slot >= CTL_RING) {
+        L2_CUDA(cudaStreamSynchronize(s->m->stream));
+        s->ctl_slot = 1;
+    }
+    Ctl* h = s->h_ctl + s->ctl_slot;
+    memset(h, 0, sizeof(Ctl));
+    h->pos = pos; h->token = token; h->n_prompt = n_prompt; h->force = force;
+    h->temperature = temperature; h->rng = rng; h->last_next = -1;
+    L2_CUDA(cudaMemcpyAsync(s->ctl, h, sizeof(Ctl), cudaMemcpyHostToDevice, s->m->stream));
+    return L2_OK;
+}
+
+static int upload_prompt(l2_state* s, const int32_t* prompt, int n_prompt) {
+    const l2_config& c = s->m->shape.c;
+    if (n_prompt < 0 || n_prompt > c.seq_len) return fail(L2_ERANGE, "prompt of %d tokens exceeds SEQ_LEN %d", n_prompt, c.seq_len);
+    for (int i = 0; i < n_prompt; i++)
+        if (prompt[i] < 0 || prompt[i] >= c.vocab_size) return fail(L2_ERANGE, "prompt token %d out of range", prompt[i]);
+    if (n_prompt) L2_CUDA(cudaMemcpyAsync(s->prompt, prompt, sizeof(int) * n_prompt, cudaMemcpyHostToDevice, s->m->stream));
+    return L2_OK;
+}
+
+// Positions the prefill ladder covers for a prompt of n tokens (src/inference.rs:24, 78-127).
+static int ladder_positions(int n, int chunk) {
+    static const int ladder[6] = {64, 32, 16, 8, 4, 2};
+    int pos = 0;
+    if (chunk > 0) { while (pos + chunk < n) pos += chunk; return pos; }
+    for (int a : ladder) while (pos + a < n) pos += a;
+    return pos;
+}
+
+}  // namespace l2
+
+// ---- C ABI: model -------------------------------------------------------------------------------
+
+extern "C" uint64_t l2_launch_count(void) { return g_launches; }
+
+static int resolve_shape(const l2_options* opt, const int32_t* header, Shape* out) {
+    // Config::load + check_static (src/constants.rs:94-119); n_kv_heads in the file is ignored.
+    l2_config c{};
+    c.dim = header[0]; c.hidden_dim = header[1]; c.n_layers = header[2]; c.n_heads = header[3];
+    c.vocab_size = header[5] < 0 ? -header[5] : header[5];
+    c.seq_len = header[6];
+    c.group_size = opt && opt->group_size ? opt->group_size : 128;
+    if (opt && opt->model_size) {
+        l2_config p;
+        if (int rc = l2_preset_config(opt->model_size, c.group_size, &p)) return rc;
+        if (p.dim != c.dim || p.hidden_dim != c.hidden_dim || p.n_layers != c.n_layers || p.n_heads != c.n_heads || p.vocab_size != c.vocab_size)
+            return fail(L2_EFORMAT, "checkpoint header (dim %d, hidden %d, layers %d, heads %d, vocab %d) does not match model size %s",
+                        c.dim, c.hidden_dim, c.n_layers, c.n_heads, c.vocab_size, opt->model_size);
+        c.n_kv_heads = p.n_kv_heads;
+    } else {
+        const int ag = opt && opt->attn_groups > 0 ? opt->attn_groups : 1;
+        if (c.n_heads <= 0 || c.n_heads % ag) return fail(L2_EFORMAT, "attn_groups %d does not divide n_heads %d", ag, c.n_heads);
+        c.n_kv_heads = c.n_heads / ag;
+    }
+    if (int rc = validate_config(c)) return rc;
+    out->c = c;
+    return L2_OK;
+}
+
+extern "C" int l2_model_open_blob(const l2_config* c, const void* payload, size_t nbytes, const l2_options* opt, l2_model** out) {
+    clear_error();
+    if (!c || !payload || !out) return fail(L2_EINVAL, "l2_model_open_blob: null argument");
+    if (int rc = validate_config(*c)) return rc;
+    Shape s{*c};
+    if (nbytes != s.total_words() * 4)  // src/lib.rs:97
+        return fail(L2_EFORMAT, "payload is %zu bytes, QTransformerWeights for this configuration is %zu", nbytes, s.total_words() * 4);
+    BlobSource src(s, payload);
+    return build_model(s, src, opt, out);
+}
+
+extern "C" int l2_model_open(const char* checkpoint, const l2_options* opt, l2_model** out) {
+    clear_error();
+    if (!checkpoint || !out) return fail(L2_EINVAL, "l2_model_open: null argument");
+    int fd = open(checkpoint, O_RDONLY);
+    if (fd < 0) return fail(L2_EIO, "cannot open %s", checkpoint);
+    struct stat st;
+    int32_t header[7];
+    if (fstat(fd, &st) != 0 || st.st_size < (off_t)sizeof header || read(fd, header, sizeof header) != (ssize_t)sizeof header) {
+        close(fd);
+        return fail(L2_EIO, "cannot read the header of %s", checkpoint);
+    }
+    Shape s;
+    if (int rc = resolve_shape(opt, header, &s)) { close(fd); return rc; }
+    const size_t payload = (size_t)st.st_size - sizeof header;
+    if (payload != s.total_words() * 4) {
+        close(fd);
+        return fail(L2_EFORMAT, "%s holds %zu payload bytes, QTransformerWeights for this configuration is %zu", checkpoint, payload, s.total_words() * 4);
+    }
+    void* map = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+    close(fd);
+    if (map == MAP_FAILED) return fail(L2_EIO, "mmap of %s failed", checkpoint);
+    BlobSource src(s, static_cast<const char*>(map) + sizeof header);
+    int rc = build_model(s, src, opt, out);
+    munmap(map, (size_t)st.st_size);  // everything lives on the device now
+    return rc;
+}
+
+extern "C" int l2_model_open_synthetic(const l2_config* c, uint64_t seed, const l2_options* opt, l2_model** out) {
+    clear_error();
+    if (!c || !out) return fail(L2_EINVAL, "l2_model_open_synthetic: null argument");
+    if (int rc = validate_config(*c)) return rc;
+    Shape s{*c};
+    SynthSource src(s, seed, default_threads());
+    return build_model(s, src, opt, out);
+}
+
+extern "C" void l2_model_close(l2_model* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    if (m->gen_state) l2_state_free(m->gen_state);
+    free_allocs(m->allocs);
+    if (m->own_stream) cudaStreamDestroy(m->own_stream);
+    delete m;
+}
+
+extern "C" int l2_model_config(const l2_model* m, l2_config* out) {
+    if (!m || !out) return fail(L2_EINVAL, "l2_model_config: null argument");
+    *out = m->shape.c;
+    return L2_OK;
+}
+
+extern "C" int l2_model_prefill(const l2_model*) { return 1; }
+
+extern "C" int l2_model_set_stream(l2_model* m, void* cuda_stream) {
+    if (!m) return fail(L2_EINVAL, "l2_model_set_stream: null model");
+    m->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : m->own_stream;
+    return L2_OK;
+}
+
+extern "C" uint64_t l2_model_decode_bytes(const l2_model* m) { return m ? m->decode_bytes : 0; }
+
+// ---- C ABI: run state ---------------------------------------------------------------------------
+
+extern "C" int l2_state_new(l2_model* m, l2_state** out) {
+    clear_error();
+    if (!m || !out) return fail(L2_EINVAL, "l2_state_new: null argument");
+    L2_CUDA(cudaSetDevice(m->device));
+    std::unique_ptr<l2_state> s(new l2_state);
+    s->m = m;
+    const l2_config& c = m->shape.c;
+    const size_t kvn = (size_t)c.n_layers * c.seq_len * m->shape.kv_dim();
+    const int D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
+    auto A = [&](float** p, size_t n) { return dev_alloc(reinterpret_cast<void**>(p), n * sizeof(float), s->allocs); };
+    int rc = 0;
+    if ((rc = A(&s->kc, kvn)) || (rc = A(&s->vc, kvn)) || (rc = A(&s->x, D)) || (rc = A(&s->xq, D)) || (rc = A(&s->xk, D)) ||
+        (rc = A(&s->xv, D)) || (rc = A(&s->q, D)) || (rc = A(&s->k, KV)) || (rc = A(&s->v, KV)) || (rc = A(&s->att, D)) ||
+        (rc = A(&s->x1, D)) || (rc = A(&s->x3, D)) || (rc = A(&s->hb, H)) || (rc = A(&s->logits, c.vocab_size))) {
+        free_allocs(s->allocs);
+        return rc;
+    }
+    // enough (kv head, split) CTAs to cover the SMs about twice
+    s->max_split = std::max(1, std::min(32, (2 * m->sms + c.n_kv_heads - 1) / c.n_kv_heads));
+    if ((rc = A(&s->part, (size_t)c.n_heads * s->max_split * (HS + 2))) ||
+        (rc = dev_alloc(reinterpret_cast<void**>(&s->counter), sizeof(unsigned) * c.n_kv_heads, s->allocs)) ||
+        (rc = dev_alloc(reinterpret_cast<void**>(&s->ctl), sizeof(Ctl), s->allocs)) ||
+        (rc = dev_alloc(reinterpret_cast<void**>(&s->prompt), sizeof(int) * c.seq_len, s->allocs)) ||
+        (rc = dev_alloc(reinterpret_cast<void**>(&s->out_tokens), sizeof(int) * c.seq_len, s->allocs))) {
+        free_allocs(s->allocs);
+        return rc;
+    }
+    if (cudaMallocHost(reinterpret_cast<void**>(&s->h_ctl), sizeof(Ctl) * CTL_RING) != cudaSuccess) {
+        free_allocs(s->allocs);
+        return fail(L2_ECUDA, "cudaMallocHost failed");
+    }
+    l2_state* sp = s.release();
+    if ((rc = l2_state_reset(sp))) { l2_state_free(sp); return rc; }
+    *out = sp;
+    return L2_OK;
+}
+
+extern "C" int l2_state_reset(l2_state* s) {
+    if (!s) return fail(L2_EINVAL, "l2_state_reset: null state");
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    const size_t kvn = (size_t)c.n_layers * c.seq_len * m->shape.kv_dim();
+    L2_CUDA(cudaMemsetAsync(s->kc, 0, kvn * sizeof(float), m->stream));
+    L2_CUDA(cudaMemsetAsync(s->vc, 0, kvn * sizeof(float), m->stream));
+    L2_CUDA(cudaMemsetAsync(s->counter, 0, sizeof(unsigned) * c.n_kv_heads, m->stream));
+    L2_CUDA(cudaMemsetAsync(s->ctl, 0, sizeof(Ctl), m->stream));
+    L2_CUDA(cudaMemsetAsync(s->prompt, 0, sizeof(int) * c.seq_len, m->stream));
+    L2_CUDA(cudaMemsetAsync(s->out_tokens, 0, sizeof(int) * c.seq_len, m->stream));
+    L2_CUDA(cudaStreamSynchronize(m->stream));
+    return L2_OK;
+}
+
+extern "C" void l2_state_free(l2_state* s) {
+    if (!s) return;
+    cudaSetDevice(s->m->device);
+    for (auto& g : s->graphs) if (g) cudaGraphExecDestroy(g);
+    free_allocs(s->allocs);
+    if (s->h_ctl) cudaFreeHost(s->h_ctl);
+    if (s->m->gen_state == s) s->m->gen_state = nullptr;
+    delete s;
+}
+
+extern "C" int l2_state_read_kv(l2_state* s, int layer, float* key_cache, float* value_cache) {
+    if (!s) return fail(L2_EINVAL, "l2_state_read_kv: null state");
+    const l2_config& c = s->m->shape.c;
+    if (layer < 0 || layer >= c.n_layers) return fail(L2_ERANGE, "layer %d out of range", layer);
+    const size_t ls = (size_t)c.seq_len * s->m->shape.kv_dim();
+    L2_CUDA(cudaStreamSynchronize(s->m->stream));
+    if (key_cache) L2_CUDA(cudaMemcpy(key_cache, s->kc + layer * ls, ls * sizeof(float), cudaMemcpyDeviceToHost));
+    if (value_cache) L2_CUDA(cudaMemcpy(value_cache, s->vc + layer * ls, ls * sizeof(float), cudaMemcpyDeviceToHost));
+    return L2_OK;
+}
+
+// ---- C ABI: forward, prefill, decode --------------------------------------------------------------
+
+static int check_state(l2_model* m, l2_state* s, const char* who) {
+    if (!m || !s) return fail(L2_EINVAL, "%s: null handle", who);
+    if (s->m != m) return fail(L2_EINVAL, "%s: the state belongs to another model", who);
+    L2_CUDA(cudaSetDevice(m->device));
+    return L2_OK;
+}
+
+extern "C" int l2_forward(l2_model* m, l2_state* s, const int32_t* tokens, const int32_t* pos, int B, float* logits) {
+    clear_error();
+    if (int rc = check_state(m, s, "l2_forward")) return rc;
+    const l2_config& c = m->shape.c;
+    const int maxb = m->opt.max_batch > 0 ? m->opt.max_batch : 64;
+    if (!tokens || !pos || B < 1 || B > maxb) return fail(L2_EINVAL, "l2_forward: bad batch (B=%d, max %d)", B, maxb);
+    for (int b = 0; b < B; b++) {
+        if (pos[b] < 0 || pos[b] >= c.seq_len) return fail(L2_ERANGE, "l2_forward: position %d outside 0..%d", pos[b], c.seq_len - 1);
+        if (tokens[b] < 0 || tokens[b] >= c.vocab_size) return fail(L2_ERANGE, "l2_forward: token %d outside the vocabulary", tokens[b]);
+        // Rows are evaluated in order, each seeing the cache rows written before it; that equals the
+        // reference (all rows stored, then attention over 0..=pos[b]) when positions ascend.
+        if (b && pos[b] <= pos[b - 1]) return fail(L2_EINVAL, "l2_forward: positions of a batch must be strictly ascending");
+    }
+    for (int b = 0; b < B; b++) {
+        if (int rc = write_ctl(s, pos[b], tokens[b], 0, -1, 0.f, 0)) return rc;
+        if (int rc = run_forward(s, (B == 1 && logits) ? G_FWD_CLS : G_FWD)) return rc;
+    }
+    if (B == 1 && logits) L2_CUDA(cudaMemcpyAsync(logits, s->logits, sizeof(float) * c.vocab_size, cudaMemcpyDeviceToHost, m->stream));
+    L2_CUDA(cudaStreamSynchronize(m->stream));
+    return L2_OK;
+}
+
+static int prefill_async(l2_model* m, l2_state* s, const int32_t* prompt, int n_prompt, int chunk, int32_t* pos_out) {
+    if (int rc = upload_prompt(s, prompt, n_prompt)) return rc;
+    const int covered = ladder_positions(n_prompt, chunk);
+    if (covered > 0) {
+        if (int rc = write_ctl(s, 0, L2_START, n_prompt, -1, 0.f, 0)) return rc;
+        for (int p = 0; p < covered; p++)
+            if (int rc = run_forward(s, G_FEED)) return rc;
+    }
+    *pos_out = covered;
+    return L2_OK;
+}
+
+extern "C" int l2_prefill(l2_model* m, l2_state* s, const int32_t* prompt, int n_prompt, int chunk, int32_t* pos_out) {
+    clear_error();
+    if (int rc = check_state(m, s, "l2_prefill")) return rc;
+    if ((!prompt && n_prompt) || !pos_out || chunk < 0) return fail(L2_EINVAL, "l2_prefill: bad argument");
+    if (int rc = prefill_async(m, s, prompt, n_prompt, chunk, pos_out)) return rc;
+    L2_CUDA(cudaStreamSynchronize(m->stream));
+    return L2_OK;
+}
+
+extern "C" int l2_decode_step(l2_model* m, l2_state* s, int32_t token, int32_t pos, float temperature, uint64_t* rng_seed,
+                              int32_t forced_next, int32_t* next, float* logits) {
+    clear_error();
+    if (int rc = check_state(m, s, "l2_decode_step")) return rc;
+    const l2_config& c = m->shape.c;
+    if (pos < 0 || pos >= c.seq_len) return fail(L2_ERANGE, "l2_decode_step: position %d outside 0..%d", pos, c.seq_len - 1);
+    if (token < 0 || token >= c.vocab_size) return fail(L2_ERANGE, "l2_decode_step: token %d outside the vocabulary", token);
+    if (forced_next >= c.vocab_size) return fail(L2_ERANGE, "l2_decode_step: forced token outside the vocabulary");
+    if (int rc = write_ctl(s, pos, token, 0, forced_next < 0 ? -1 : forced_next, temperature, rng_seed ? *rng_seed : 0)) return rc;
+    if (int rc = run_forward(s, G_DECODE)) return rc;
+    L2_CUDA(cudaMemcpyAsync(s->h_ctl, s->ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, m->stream));
+    if (logits) L2_CUDA(cudaMemcpyAsync(logits, s->logits, sizeof(float) * c.vocab_size, cudaMemcpyDeviceToHost, m->stream));
+    L2_CUDA(cudaStreamSynchronize(m->stream));
+    if (s->h_ctl->status) return fail(L2_ESTATUS, "device status %d", s->h_ctl->status);
+    if (next) *next = s->h_ctl->last_next;
+    if (rng_seed) *rng_seed = s->h_ctl->rng;
+    return L2_OK;
+}
+
+static int decode_run_async(l2_model* m, l2_state* s, const int32_t* prompt, int n_prompt, int pos0, int steps,
+                            float temperature, uint64_t rng) {
+    const int token = pos0 == 0 ? L2_START : prompt[pos0 - 1];  // src/inference.rs:128-132
+    if (int rc = write_ctl(s, pos0, token, n_prompt, -1, temperature, rng)) return rc;
+    for (int p = pos0; p < steps; p++)
+        if (int rc = run_forward(s, G_DECODE)) return rc;
+    return L2_OK;
+}
+
+extern "C" int l2_decode_run(l2_model* m, l2_state* s, const int32_t* prompt, int n_prompt, int32_t pos0, int32_t steps,
+                             float temperature, uint64_t* rng_seed, int32_t* out_tokens) {
+    clear_error();
+    if (int rc = check_state(m, s, "l2_decode_run")) return rc;
+    const l2_config& c = m->shape.c;
+    if (steps > c.seq_len) return fail(L2_ERANGE, "steps %d exceeds SEQ_LEN %d", steps, c.seq_len);
+    if (pos0 < 0 || pos0 > n_prompt || (!prompt && n_prompt)) return fail(L2_EINVAL, "l2_decode_run: bad prompt / start position");
+    if (int rc = upload_prompt(s, prompt, n_prompt)) return rc;
+    if (int rc = decode_run_async(m, s, prompt, n_prompt, pos0, steps, temperature, rng_seed ? *rng_seed : 0)) return rc;
+    const int n = steps > pos0 ? steps - pos0 : 0;
+    if (n && out_tokens) L2_CUDA(cudaMemcpyAsync(out_tokens, s->out_tokens + pos0, sizeof(int) * n, cudaMemcpyDeviceToHost, m->stream));
+    L2_CUDA(cudaMemcpyAsync(s->h_ctl, s->ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, m->stream));
+    L2_CUDA(cudaStreamSynchronize(m->stream));
+    if (s->h_ctl->status) return fail(L2_ESTATUS, "device status %d", s->h_ctl->status);
+    if (rng_seed) *rng_seed = s->h_ctl->rng;
+    return L2_OK;
+}
+
+extern "C" int l2_generate_ids(l2_model* m, const int32_t* prompt, int n_prompt, int steps, float temperature,
+                               uint64_t* rng_seed, int use_prefill, int32_t* out_tokens, int32_t* out_pos0,
+                               float* logits_trace, double* elapsed_ms, double* prefill_ms, double* decode_ms) {
+    clear_error();
+    if (!m || !out_tokens || (!prompt && n_prompt)) return fail(L2_EINVAL, "l2_generate_ids: null argument");
+    L2_CUDA(cudaSetDevice(m->device));
+    const l2_config& c = m->shape.c;
+    if (steps > c.seq_len) return fail(L2_ERANGE, "steps %d exceeds SEQ_LEN %d", steps, c.seq_len);
+    if (!m->gen_state) {
+        if (int rc = l2_state_new(m, &m->gen_state)) return rc;
+    } else if (int rc = l2_state_reset(m->gen_state)) {  // fresh RunState per call (src/inference.rs:59)
+        return rc;
+    }
+    l2_state* s = m->gen_state;
+    cudaEvent_t e0, e1, e2;
+    L2_CUDA(cudaEventCreate(&e0));
+    L2_CUDA(cudaEventCreate(&e1));
+    L2_CUDA(cudaEventCreate(&e2));
+    int rc = L2_OK, pos0 = 0, n_out = 0;
+    uint64_t rng = rng_seed ? *rng_seed : 0;
+    do {
+        if ((rc = upload_prompt(s, prompt, n_prompt))) break;
+        cudaEventRecord(e0, m->stream);  // src/inference.rs:72
+        if (use_prefill && (rc = prefill_async(m, s, prompt, n_prompt, 0, &pos0))) break;
+        cudaEventRecord(e1, m->stream);
+        n_out = steps > pos0 ? steps - pos0 : 0;
+        if (!logits_trace) {
+            if ((rc = decode_run_async(m, s, prompt, n_prompt, pos0, steps, temperature, rng))) break;
+            if (n_out) cudaMemcpyAsync(out_tokens, s->out_tokens + pos0, sizeof(int) * n_out, cudaMemcpyDeviceToHost, m->stream);
+            cudaMemcpyAsync(s->h_ctl, s->ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, m->stream);
+            cudaEventRecord(e2, m->stream);
+            if (cudaStreamSynchronize(m->stream) != cudaSuccess) { rc = fail(L2_ECUDA, "decode failed: %s", cudaGetErrorString(cudaGetLastError())); break; }
+            rng = s->h_ctl->rng;
+        } else {
+            int token = pos0 == 0 ? L2_START : prompt[pos0 - 1];
+            for (int p = pos0; p < steps; p++) {
+                int next = 0;
+                const int forced = p < n_prompt ? prompt[p] : -1;
+                if ((rc = l2_decode_step(m, s, token, p, temperature, &rng, forced, &next, logits_trace + (size_t)(p - pos0) * c.vocab_size))) break;
+                out_tokens[p - pos0] = next;
+                token = next;
+            }
+            if (rc) break;
+            cudaEventRecord(e2, m->stream);
+            cudaStreamSynchronize(m->stream);
+        }
+        float a = 0.f, b = 0.f;
+        cudaEventElapsedTime(&a, e0, e1);
+        cudaEventElapsedTime(&b, e1, e2);
+        if (prefill_ms) *prefill_ms = a;
+        if (decode_ms) *decode_ms = b;
+        if (elapsed_ms) *elapsed_ms = (double)a + b;
+    } while (0);
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+    if (rc) return rc;
+    if (out_pos0) *out_pos0 = pos0;
+    if (rng_seed) *rng_seed = rng;
+    return n_out;
+}
+
+// ---- C ABI: one QLinear ---------------------------------------------------------------------------
+
+extern "C" int l2_qlinear_create(int in, int out, int group_size, const int32_t* qweight, const int32_t* qzeros,
+                                 const float* scales, const int32_t* g_index, int device, l2_qlinear** h) {
+    clear_error();
+    if (!qweight || !qzeros || !scales || !g_index || !h) return fail(L2_EINVAL, "l2_qlinear_create: null argument");
+    if (in <= 0 || out <= 0 || in % 32 || out % 8) return fail(L2_EINVAL, "l2_qlinear_create: IN must be a multiple of 32 and OUT of 8");
+    if (group_size != 32 && group_size != 64 && group_size != 128) return fail(L2_EINVAL, "group_size %d is not 32, 64 or 128", group_size);
+    if (in % group_size) return fail(L2_EINVAL, "group size must divide IN");
+    if ((size_t)in * 4 > 200 * 1024) return fail(L2_EINVAL, "IN %d does not fit the shared-memory staging", in);
+    if (!is_permutation(g_index, in)) return fail(L2_EFORMAT, "g_index is not a permutation of 0..%d", in - 1);
+    std::unique_ptr<l2_qlinear> q(new l2_qlinear);
+    if (int rc = check_device(device, &q->device, &q->sms)) return rc;
+    q->group_size = group_size;
+    PackedQ p;
+    repack_qlinear(in, out, group_size, qweight, qzeros, scales, nullptr, p);
+    if (int rc = upload_qlinear(p, g_index, q->q, q->allocs, nullptr)) { free_allocs(q->allocs); return rc; }
+    L2_CUDA(cudaStreamCreateWithFlags(&q->stream, cudaStreamNonBlocking));
+    *h = q.release();
+    return L2_OK;
+}
+
+static int qlinear_reserve(l2_qlinear* h, int B) {
+    if (B <= h->cap_b) return L2_OK;
+    int rc;
+    if ((rc = dev_alloc(reinterpret_cast<void**>(&h->x_dev), sizeof(float) * h->q.in * B, h->allocs))) return rc;
+    if ((rc = dev_alloc(reinterpret_cast<void**>(&h->xp_dev), sizeof(float) * h->q.in * B, h->allocs))) return rc;
+    if ((rc = dev_alloc(reinterpret_cast<void**>(&h->y_dev), sizeof(float) * h->q.out * B, h->allocs))) return rc;
+    h->cap_b = B;
+    return L2_OK;
+}
+
+extern "C" int l2_qlinear_matvec_dev(l2_qlinear* h, const float* x_dev, float* xout_dev, int B, void* cuda_stream) {
+    clear_error();
+    if (!h || !x_dev || !xout_dev || B < 1) return fail(L2_EINVAL, "l2_qlinear_matvec_dev: bad argument");
+    L2_CUDA(cudaSetDevice(h->device));
+    cudaStream_t st = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : h->stream;
+    if (int rc = qlinear_reserve(h, B)) return rc;
+    for (int b = 0; b < B; b++) {
+        launch_permute(x_dev + (size_t)b * h->q.in, h->q.perm, h->xp_dev + (size_t)b * h->q.in, h->q.in, st);
+        if (int rc = run_gemv_single(h->q, h->xp_dev + (size_t)b * h->q.in, xout_dev + (size_t)b * h->q.out, h->sms, st)) return rc;
+    }
+    return L2_OK;
+}
+
+extern "C" int l2_qlinear_matvec(l2_qlinear* h, const float* x, float* xout, int B) {
+    clear_error();
+    if (!h || !x || !xout || B < 1) return fail(L2_EINVAL, "l2_qlinear_matvec: bad argument");
+    L2_CUDA(cudaSetDevice(h->device));
+    if (int rc = qlinear_reserve(h, B)) return rc;
+    L2_CUDA(cudaMemcpyAsync(h->x_dev, x, sizeof(float) * h->q.in * B, cudaMemcpyHostToDevice, h->stream));
+    if (int rc = l2_qlinear_matvec_dev(h, h->x_dev, h->y_dev, B, h->stream)) return rc;
+    L2_CUDA(cudaMemcpyAsync(xout, h->y_dev, sizeof(float) * h->q.out * B, cudaMemcpyDeviceToHost, h->stream));
+    L2_CUDA(cudaStreamSynchronize(h->stream));
+    return L2_OK;
+}
+
+extern "C" void l2_qlinear_free(l2_qlinear* h) {
+    if (!h) return;
+    cudaSetDevice(h->device);
+    free_allocs(h->allocs);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    delete h;
+}
+
+extern "C" uint32_t l2_random_u32(uint64_t* seed) {  // src/util.rs:71-77
+    uint64_t s = *seed;
+    s ^= s >> 12;
+    s ^= s << 25;
+    s ^= s >> 27;
+    *seed = s;
+    return (uint32_t)((s * 0x2545F4914F6CDD1Dull) >> 32);
+}
+extern "C" float l2_random_f32(uint64_t* seed) { return (float)(l2_random_u32(seed) >> 8) / 16777216.0f; }

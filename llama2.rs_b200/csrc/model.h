@@ -1,0 +1,98 @@
+// Host-side model / run-state records behind the C ABI handles.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <vector>
+
+#include "host_common.h"
+#include "kernels.cuh"
+#include "repack.h"
+
+namespace l2 {
+
+#define L2_CUDA(expr)                                                                              \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return ::l2::fail(L2_ECUDA, "%s: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+    } while (0)
+
+// One QLinear in device layout (see repack.cpp) plus what its producers/consumers need.
+struct DevQ {
+    uint4* qw = nullptr;
+    float* sc = nullptr;
+    uint32_t* zr = nullptr;
+    int* perm = nullptr;  // g_index: permuted position j reads input perm[j]
+    int* inv = nullptr;   // inverse: input o is written to permuted position inv[o]
+    int in = 0, out = 0, gp = 0, gshift = 0, ks = 1;
+};
+
+struct DevLayer {
+    DevQ wq, wk, wv, wo, w1, w2, w3;
+    float *nw_q = nullptr, *nw_k = nullptr, *nw_v = nullptr;  // rms_att_weight in each consumer's K order
+    float *nw_1 = nullptr, *nw_3 = nullptr;                   // rms_ffn_weight likewise
+};
+
+constexpr int CTL_RING = 128;
+
+enum GraphKind : int { G_DECODE = 0, G_FEED, G_FWD_CLS, G_FWD, G_COUNT };
+
+}  // namespace l2
+
+struct l2_model {
+    l2::Shape shape;
+    l2_options opt{};
+    int device = 0;
+    int sms = 148;
+    float eps = 1e-5f;
+    cudaStream_t own_stream = nullptr, stream = nullptr;
+    std::vector<l2::DevLayer> layers;
+    float* tok_emb = nullptr;
+    float* wcls = nullptr;
+    float* rms_final = nullptr;
+    float* rope_cos = nullptr;
+    float* rope_sin = nullptr;
+    std::vector<void*> allocs;
+    uint64_t decode_bytes = 0;
+    size_t device_bytes = 0;
+    l2_state* gen_state = nullptr;  // reused by l2_generate_ids
+    bool use_graph = true, use_pdl = true;
+};
+
+struct l2_state {
+    l2_model* m = nullptr;
+    float *kc = nullptr, *vc = nullptr;  // [L][SEQ][KVH][HS]
+    float *x = nullptr, *xq = nullptr, *xk = nullptr, *xv = nullptr;
+    float *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr;
+    float *x1 = nullptr, *x3 = nullptr, *hb = nullptr, *logits = nullptr;
+    float* part = nullptr;
+    unsigned* counter = nullptr;
+    l2::Ctl* ctl = nullptr;
+    l2::Ctl* h_ctl = nullptr;  // pinned ring of CTL_RING records; h_ctl[0] also receives read-backs
+    int ctl_slot = 0;
+    int* prompt = nullptr;
+    int* out_tokens = nullptr;
+    int max_split = 1;
+    cudaGraphExec_t graphs[l2::G_COUNT] = {nullptr, nullptr, nullptr, nullptr};
+    int graph_nodes[l2::G_COUNT] = {0, 0, 0, 0};
+    std::vector<void*> allocs;
+};
+
+struct l2_qlinear {
+    l2::DevQ q;
+    int device = 0;
+    int sms = 148;
+    int group_size = 128;
+    float *x_dev = nullptr, *xp_dev = nullptr, *y_dev = nullptr;
+    int cap_b = 0;
+    cudaStream_t stream = nullptr;
+    std::vector<void*> allocs;
+};
+
+namespace l2 {
+int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vector<void*>& allocs, size_t* bytes);
+void launch_permute(const float* x, const int* perm, float* xp, int n, cudaStream_t st);
+int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, cudaStream_t st);
+}  // namespace l2
