@@ -1,0 +1,262 @@
+#!/usr/bin/env python
+"""Benchmark of the llama2.rs token loop on B200: batch-1 greedy decode tok/s (and prefill tok/s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 7b|13b|70b] [--impl ours|reference]
+
+A step is one pass of the workload: a seeded random prompt through prefill, then the decode
+loop (BASELINE config 0 for 7B: 32 prompt tokens, 256 greedy tokens).  `value` is decode tok/s with
+weights, KV cache and the loop state resident in HBM (CUDA events on the launching stream);
+`e2e` is the same loop driven token by token through the C ABI with host buffers (l2_decode_step:
+token and position go host->device and the chosen token comes back every step).  Weights are a
+seeded synthetic checkpoint in the reference's .bin layout (there are no real weights offline).
+
+--impl reference times the CPU restatement of the reference's rayon+SIMD path (oracle/, the
+reference itself is nightly Rust and cannot be built here) on the host cores, on a bounded sample
+of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "llama2.rs_b200"))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+
+WORKLOADS = {  # name: (model size, group size, prompt tokens, decode tokens)  -- BASELINE configs 0, 2, 3
+    "7b": ("7B", 128, 32, 256),
+    "13b": ("13B", 128, 128, 512),
+    "70b": ("70B", 64, 64, 256),
+}
+WEIGHT_SEED, PROMPT_SEED = 20240, 7
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = sorted(float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit())
+        reasons = []
+        for i, name in enumerate(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")):
+            if any(r[3 + i] == "Active" for r in self.rows):
+                reasons.append(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def make_prompt(np, n, vocab):
+    return np.random.default_rng(PROMPT_SEED).integers(0, vocab, n).astype(np.int32)
+
+
+class CpuArm:
+    """The CPU restatement on a bounded sample of the workload: the prompt through the reference's
+    prefill ladder, then `sample_tokens` greedy decode tokens; decode tok/s over the B=1 positions."""
+
+    def __init__(self, workload, payload=None, cfg=None):
+        import numpy as np
+        import llama2_rs as l2
+        import oracle as orc
+        self.size, gs, self.n_prompt, _ = WORKLOADS[workload]
+        self.cfg = cfg if cfg is not None else l2.preset_config(self.size, gs)
+        self.payload = payload if payload is not None else l2.synth_fill(self.cfg, WEIGHT_SEED)
+        self.model = orc.Model(self.cfg, self.payload)
+        self.sample_tokens = {"7b": 6, "13b": 4, "70b": 2}[workload]
+        self.prompt = make_prompt(np, self.n_prompt, self.cfg.vocab_size)
+        self.cores = orc.lib().orc_num_threads()
+
+    def run(self):
+        r = self.model.generate_ids(self.prompt, self.n_prompt + self.sample_tokens)
+        n = len(r["tokens"])
+        decode_ms = r["elapsed_ms"] - r["prefill_ms"]
+        prefill_tok_s = r["pos0"] / max(r["prefill_ms"], 1e-9) * 1e3
+        return {"value": n / decode_ms * 1e3, "unit": "tok/s", "cores": self.cores, "kind": "port",
+                "sample": "%s synthetic checkpoint, %d-token prompt through the 64/32/16/8/4/2 prefill ladder (%.0f ms, %.1f tok/s), then %d B=1 positions"
+                          % (self.size, self.n_prompt, r["prefill_ms"], prefill_tok_s, n),
+                "prefill_tok_s": prefill_tok_s}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="7b", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-warmup", type=int, default=3, help="profiling runs may lower the warm-up floor")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    size, gs, n_prompt, n_decode = WORKLOADS[args.workload]
+    config = {"workload": "Llama2-%s GPTQ 4-bit g%d act-order, %d-token random prompt, %d greedy decode tokens, batch 1"
+                          % (size, gs, n_prompt, n_decode),
+              "weights": "seeded synthetic checkpoint (seed %d) in the export.py .bin layout" % WEIGHT_SEED,
+              "l2": "weights streamed per token (%s) exceed the 126 MB L2; no flush needed" % size,
+              "parallelism": "replicas" if world > 1 else "single GPU"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps = max(1, args.steps)
+        arm = CpuArm(args.workload)
+        vals = [arm.run() for _ in range(max(0, args.warmup) + steps)][-steps:]
+        v = sum(x["value"] for x in vals) / len(vals)
+        cb = dict(vals[-1], value=v)
+        print(json.dumps({"impl": "reference", "metric": "batch-1 decode tok/s", "value": v, "unit": "tok/s", "n_gpus": args.gpus,
+                          "steps": steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "cpu_baseline": cb,
+                          "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import llama2_rs as l2
+
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+    dev = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(dev)
+    cfg = l2.preset_config(size, gs)
+    need_payload = rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "70b"
+    payload = l2.synth_fill(cfg, WEIGHT_SEED) if need_payload else None
+    model = l2.LlamaModel.from_blob(cfg, payload, device=dev) if payload is not None else l2.LlamaModel.synthetic(cfg, WEIGHT_SEED, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    model.set_stream(stream.cuda_stream)
+    state = l2.RunState(model)
+    prompt = make_prompt(np, n_prompt, cfg.vocab_size)
+    total = n_prompt + n_decode
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step(timed):
+        state.reset()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            pos0 = l2.prefill(model, state, prompt)
+            e1.record(stream)
+            toks = l2.decode_run(model, state, prompt, pos0, total)
+            e2.record(stream)
+        torch.cuda.synchronize()
+        return pos0, toks, e0.elapsed_time(e1), e1.elapsed_time(e2)
+
+    for _ in range(max(args.min_warmup, args.warmup)):
+        pos0, toks_ref, _, _ = one_step(False)
+    barrier()
+    launches0 = l2.lib.l2_launch_count()
+    with ClockSampler(dev) as clocks:
+        prefill_ms, decode_ms = 0.0, 0.0
+        for _ in range(args.steps):
+            pos0, toks, pf, dc = one_step(True)
+            prefill_ms += pf
+            decode_ms += dc
+            assert np.array_equal(toks, toks_ref), "decode is not reproducible from step to step"
+        # the dominant kernel alone: w1/w3 + SwiGLU GEMV, cycling through the layers (each launch reads other weights)
+        n_dom = 4 * cfg.n_layers
+        l2.check(l2.lib.l2_bench_projection(model._h, state._h, 2, 0, cfg.n_layers))
+        torch.cuda.synchronize()
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record(stream)
+        l2.check(l2.lib.l2_bench_projection(model._h, state._h, 2, 0, n_dom))
+        d1.record(stream)
+        torch.cuda.synchronize()
+        dom_ms = d0.elapsed_time(d1) / n_dom
+    barrier()
+    launches = l2.lib.l2_launch_count() - launches0
+    n_loop = total - pos0           # positions run by the B=1 loop per step (a few teacher-forced ones first)
+    t = torch.tensor([decode_ms, prefill_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    decode_ms, prefill_ms = t.tolist()
+    value = world * n_loop * args.steps / decode_ms * 1e3
+
+    # end to end: the host drives every token through l2_decode_step (host buffers in and out)
+    state.reset()
+    l2.prefill(model, state, prompt)
+    torch.cuda.synchronize()
+    tok = int(prompt[pos0 - 1]) if pos0 > 0 else l2.START
+    t0 = time.perf_counter()
+    for p in range(pos0, total):
+        forced = int(prompt[p]) if p < n_prompt else -1
+        tok, _ = l2.decode_step(model, state, tok, p, forced_next=forced)
+    e2e_s = time.perf_counter() - t0
+    e2e = {"value": world * n_loop / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 40 * n_loop, "d2h_bytes_per_step": 40 * n_loop,
+           "note": "one l2_decode_step call per token: 40-byte loop record up, 40-byte record (chosen token) back"}
+
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peaks()
+    dom_bytes = int(l2.lib.l2_projection_bytes(model._h, 2))
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    tok_s = value / world
+    out = {
+        "metric": "batch-1 decode tok/s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": max(args.min_warmup, args.warmup), "ms_per_step": (decode_ms + prefill_ms) / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations / int4 weights", "data": "synthetic", "config": config,
+        "prefill_tok_s": world * pos0 * args.steps / max(prefill_ms, 1e-9) * 1e3,
+        "decode_ms_per_token": decode_ms / (n_loop * args.steps),
+        "roofline": {"bound": "hbm", "kernel": "gemv_q4 (w1/w3 + SwiGLU)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "bytes_per_launch": dom_bytes, "us_per_launch": dom_ms * 1e3},
+        "token_roofline": {"bytes_per_token": model.decode_bytes, "achieved_gbs": model.decode_bytes * tok_s / 1e9,
+                           "frac_of_8tbs": model.decode_bytes * tok_s / 8e12, "frac_of_measured": model.decode_bytes * tok_s / (peak * 1e9)},
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
+    }
+    if not args.no_cpu_baseline:
+        try:
+            out["cpu_baseline"] = CpuArm(args.workload, payload=payload, cfg=cfg).run()
+        except Exception as e:  # the GPU numbers stand even if the CPU leg cannot run
+            out["cpu_baseline"] = {"error": str(e)}
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -153,6 +153,15 @@ int l2_qlinear_matvec(l2_qlinear* h, const float* x, float* xout, int B);
 int l2_qlinear_matvec_dev(l2_qlinear* h, const float* x_dev, float* xout_dev, int B, void* cuda_stream);
 void l2_qlinear_free(l2_qlinear* h);
 
+/* ---- measurement hooks (no counterpart in the reference, which times whole runs only,
+ *      src/main.rs:61-65) --------------------------------------------------------------- */
+/* Enqueue `count` launches of one projection kernel of the token forward, cycling through the
+ * layers from layer0, on the model's stream; the caller brackets them with events.
+ * which: 0 wq/wk/wv, 1 wo, 2 w1/w3+SwiGLU, 3 w2, 4 classifier, 5 attention. */
+int l2_bench_projection(l2_model* m, l2_state* s, int which, int layer0, int count);
+/* Algorithmic bytes one such launch streams (qweight+qzeros+scales, or the f32 classifier). */
+uint64_t l2_projection_bytes(const l2_model* m, int which);
+
 /* ---- sampling helpers (src/util.rs:39-46, 71-113) ----------------------------------- */
 uint32_t l2_random_u32(uint64_t* seed);
 float l2_random_f32(uint64_t* seed);

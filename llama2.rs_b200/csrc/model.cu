@@ -225,6 +225,92 @@ static void set_scatter3(float** sdst, const int** sidx, int* n, l2_state* s, co
     *n = 3;
 }
 
+// rmsnorm + wq/wk/wv (src/models.rs:217-226)
+static void launch_qkv(l2_state* s, int l, cudaStream_t st, bool pdl) {
+    l2_model* m = s->m;
+    const DevLayer& y = m->layers[l];
+    const int D = m->shape.c.dim;
+    GemvParams p{};
+    p.njobs = 3; p.eps = m->eps;
+    fill_job(p.job[0], y.wq, s->xq, y.nw_q, s->q, EPI_STORE);
+    fill_job(p.job[1], y.wk, s->xk, y.nw_k, s->k, EPI_STORE);
+    fill_job(p.job[2], y.wv, s->xv, y.nw_v, s->v, EPI_STORE);
+    const int grid = gemv_grid(m->sms, D, false, 3);
+    split_ctas(p, grid);
+    launch_gemv(p, grid, gemv_smem_bytes(D, false), false, st, pdl);
+}
+
+// rope + cache append + attention (src/models.rs:228-256)
+static void launch_attention(l2_state* s, int l, cudaStream_t st, bool pdl) {
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    const DevLayer& y = m->layers[l];
+    AttnParams a{};
+    a.q = s->q; a.k = s->k; a.v = s->v;
+    const size_t ls = (size_t)c.seq_len * m->shape.kv_dim();
+    a.kc = s->kc + (size_t)l * ls; a.vc = s->vc + (size_t)l * ls;
+    a.rope_cos = m->rope_cos; a.rope_sin = m->rope_sin;
+    a.ctl = s->ctl; a.part = s->part; a.counter = s->counter;
+    a.out = s->att; a.oidx = y.wo.inv;
+    a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups();
+    a.max_split = s->max_split; a.split_min = 64;
+    launch_attn(a, st, pdl);
+}
+
+// wo + residual (src/models.rs:260-264); the new x goes to w1's and w3's K order as well
+static void launch_wo(l2_state* s, int l, cudaStream_t st, bool pdl) {
+    l2_model* m = s->m;
+    const DevLayer& y = m->layers[l];
+    const int D = m->shape.c.dim;
+    GemvParams p{};
+    p.njobs = 1; p.eps = m->eps;
+    fill_job(p.job[0], y.wo, s->att, nullptr, s->x, EPI_RESID);
+    p.job[0].sdst[0] = s->x1; p.job[0].sidx[0] = y.w1.inv;
+    p.job[0].sdst[1] = s->x3; p.job[0].sidx[1] = y.w3.inv;
+    p.job[0].nscatter = 2;
+    const int grid = gemv_grid(m->sms, D, false, 1);
+    split_ctas(p, grid);
+    launch_gemv(p, grid, gemv_smem_bytes(D, false), false, st, pdl);
+}
+
+// rmsnorm + w1/w3 + SwiGLU (src/models.rs:266-276)
+static void launch_w13(l2_state* s, int l, cudaStream_t st, bool pdl) {
+    l2_model* m = s->m;
+    const DevLayer& y = m->layers[l];
+    const int D = m->shape.c.dim;
+    GemvParams p{};
+    p.njobs = 1; p.eps = m->eps;
+    fill_job(p.job[0], y.w1, s->x1, y.nw_1, s->hb, EPI_SWIGLU);
+    p.job[0].qw2 = y.w3.qw; p.job[0].sc2 = y.w3.sc; p.job[0].zr2 = y.w3.zr;
+    p.job[0].x2 = s->x3; p.job[0].nw2 = y.nw_3;
+    const int grid = gemv_grid(m->sms, D, true, 1);
+    split_ctas(p, grid);
+    launch_gemv(p, grid, gemv_smem_bytes(D, true), true, st, pdl);
+}
+
+// w2 + residual (src/models.rs:279-285); the new x goes to the next layer's q/k/v K orders
+static void launch_w2(l2_state* s, int l, cudaStream_t st, bool pdl) {
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    const DevLayer& y = m->layers[l];
+    GemvParams p{};
+    p.njobs = 1; p.eps = m->eps;
+    fill_job(p.job[0], y.w2, s->hb, nullptr, s->x, EPI_RESID);
+    set_scatter3(p.job[0].sdst, p.job[0].sidx, &p.job[0].nscatter, s, l + 1 < c.n_layers ? &m->layers[l + 1] : nullptr);
+    const int grid = gemv_grid(m->sms, c.hidden_dim, false, 1);
+    split_ctas(p, grid);
+    launch_gemv(p, grid, gemv_smem_bytes(c.hidden_dim, false), false, st, pdl);
+}
+
+static void launch_classifier(l2_state* s, cudaStream_t st, bool pdl) {
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    ClsParams cp{};
+    cp.w = m->wcls; cp.x = s->x; cp.nw = m->rms_final; cp.logits = s->logits;
+    cp.rows = c.vocab_size; cp.in = c.dim; cp.eps = m->eps;
+    launch_cls(cp, m->sms * 2, st, pdl);
+}
+
 static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
@@ -238,66 +324,13 @@ static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
         launch_embed(e, st, false);  // first node of the token: plain stream order
     }
     for (int l = 0; l < L; l++) {
-        const DevLayer& y = m->layers[l];
-        {   // rmsnorm + wq/wk/wv (src/models.rs:217-226)
-            GemvParams p{};
-            p.njobs = 3; p.eps = m->eps;
-            fill_job(p.job[0], y.wq, s->xq, y.nw_q, s->q, EPI_STORE);
-            fill_job(p.job[1], y.wk, s->xk, y.nw_k, s->k, EPI_STORE);
-            fill_job(p.job[2], y.wv, s->xv, y.nw_v, s->v, EPI_STORE);
-            const int grid = gemv_grid(m->sms, D, false, 3);
-            split_ctas(p, grid);
-            launch_gemv(p, grid, gemv_smem_bytes(D, false), false, st, pdl);
-        }
-        {   // rope + cache append + attention (:228-256)
-            AttnParams a{};
-            a.q = s->q; a.k = s->k; a.v = s->v;
-            const size_t ls = (size_t)c.seq_len * m->shape.kv_dim();
-            a.kc = s->kc + (size_t)l * ls; a.vc = s->vc + (size_t)l * ls;
-            a.rope_cos = m->rope_cos; a.rope_sin = m->rope_sin;
-            a.ctl = s->ctl; a.part = s->part; a.counter = s->counter;
-            a.out = s->att; a.oidx = y.wo.inv;
-            a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups();
-            a.max_split = s->max_split; a.split_min = 64;
-            launch_attn(a, st, pdl);
-        }
-        {   // wo + residual (:260-264); the new x goes to w1's and w3's K order as well
-            GemvParams p{};
-            p.njobs = 1; p.eps = m->eps;
-            fill_job(p.job[0], y.wo, s->att, nullptr, s->x, EPI_RESID);
-            p.job[0].sdst[0] = s->x1; p.job[0].sidx[0] = y.w1.inv;
-            p.job[0].sdst[1] = s->x3; p.job[0].sidx[1] = y.w3.inv;
-            p.job[0].nscatter = 2;
-            const int grid = gemv_grid(m->sms, D, false, 1);
-            split_ctas(p, grid);
-            launch_gemv(p, grid, gemv_smem_bytes(D, false), false, st, pdl);
-        }
-        {   // rmsnorm + w1/w3 + SwiGLU (:266-276)
-            GemvParams p{};
-            p.njobs = 1; p.eps = m->eps;
-            fill_job(p.job[0], y.w1, s->x1, y.nw_1, s->hb, EPI_SWIGLU);
-            p.job[0].qw2 = y.w3.qw; p.job[0].sc2 = y.w3.sc; p.job[0].zr2 = y.w3.zr;
-            p.job[0].x2 = s->x3; p.job[0].nw2 = y.nw_3;
-            const int grid = gemv_grid(m->sms, D, true, 1);
-            split_ctas(p, grid);
-            launch_gemv(p, grid, gemv_smem_bytes(D, true), true, st, pdl);
-        }
-        {   // w2 + residual (:279-285); the new x goes to the next layer's q/k/v K orders
-            GemvParams p{};
-            p.njobs = 1; p.eps = m->eps;
-            fill_job(p.job[0], y.w2, s->hb, nullptr, s->x, EPI_RESID);
-            set_scatter3(p.job[0].sdst, p.job[0].sidx, &p.job[0].nscatter, s, l + 1 < L ? &m->layers[l + 1] : nullptr);
-            const int grid = gemv_grid(m->sms, c.hidden_dim, false, 1);
-            split_ctas(p, grid);
-            launch_gemv(p, grid, gemv_smem_bytes(c.hidden_dim, false), false, st, pdl);
-        }
+        launch_qkv(s, l, st, pdl);
+        launch_attention(s, l, st, pdl);
+        launch_wo(s, l, st, pdl);
+        launch_w13(s, l, st, pdl);
+        launch_w2(s, l, st, pdl);
     }
-    if (kind == G_DECODE || kind == G_FWD_CLS) {  // final rmsnorm + classifier (:288-297)
-        ClsParams cp{};
-        cp.w = m->wcls; cp.x = s->x; cp.nw = m->rms_final; cp.logits = s->logits;
-        cp.rows = c.vocab_size; cp.in = D; cp.eps = m->eps;
-        launch_cls(cp, m->sms * 2, st, pdl);
-    }
+    if (kind == G_DECODE || kind == G_FWD_CLS) launch_classifier(s, st, pdl);  // final rmsnorm + classifier (:288-297)
     if (kind == G_DECODE) {
         SelectParams sp{};
         sp.logits = s->logits; sp.ctl = s->ctl; sp.prompt = s->prompt; sp.out_tokens = s->out_tokens; sp.vocab = c.vocab_size;
@@ -708,6 +741,45 @@ extern "C" int l2_generate_ids(l2_model* m, const int32_t* prompt, int n_prompt,
     if (out_pos0) *out_pos0 = pos0;
     if (rng_seed) *rng_seed = rng;
     return n_out;
+}
+
+// Enqueues, for every layer in [layer0, layer0+count), the launch of one projection kernel of the
+// token forward on the model's stream, so that a caller can time that kernel alone with events.
+// which: 0 wq/wk/wv, 1 wo, 2 w1/w3+SwiGLU, 3 w2, 4 classifier (count launches), 5 attention.
+extern "C" int l2_bench_projection(l2_model* m, l2_state* s, int which, int layer0, int count) {
+    clear_error();
+    if (int rc = check_state(m, s, "l2_bench_projection")) return rc;
+    const int L = m->shape.c.n_layers;
+    if (which < 0 || which > 5 || count < 0) return fail(L2_EINVAL, "l2_bench_projection: bad argument");
+    for (int i = 0; i < count; i++) {
+        const int l = (layer0 + i) % L;
+        switch (which) {
+            case 0: launch_qkv(s, l, m->stream, false); break;
+            case 1: launch_wo(s, l, m->stream, false); break;
+            case 2: launch_w13(s, l, m->stream, false); break;
+            case 3: launch_w2(s, l, m->stream, false); break;
+            case 4: launch_classifier(s, m->stream, false); break;
+            default: launch_attention(s, l, m->stream, false); break;
+        }
+    }
+    L2_CUDA(cudaGetLastError());
+    return L2_OK;
+}
+
+// Algorithmic bytes one launch of l2_bench_projection's kernel streams: the checkpoint's
+// qweight + qzeros + scales of the projection(s), or the f32 classifier matrix.
+extern "C" uint64_t l2_projection_bytes(const l2_model* m, int which) {
+    if (!m) return 0;
+    const Shape& sh = m->shape;
+    auto q = [&](int t) { return (uint64_t)(sh.sub_words(t, S_QWEIGHT) + sh.sub_words(t, S_QZEROS) + sh.sub_words(t, S_SCALES)) * 4; };
+    switch (which) {
+        case 0: return q(T_WQ) + q(T_WK) + q(T_WV);
+        case 1: return q(T_WO);
+        case 2: return q(T_W1) + q(T_W3);
+        case 3: return q(T_W2);
+        case 4: return (uint64_t)sh.c.vocab_size * sh.c.dim * 4;
+    }
+    return 0;
 }
 
 // ---- C ABI: one QLinear ---------------------------------------------------------------------------
