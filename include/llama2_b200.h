@@ -153,6 +153,20 @@ int l2_qlinear_matvec(l2_qlinear* h, const float* x, float* xout, int B);
 int l2_qlinear_matvec_dev(l2_qlinear* h, const float* x_dev, float* xout_dev, int B, void* cuda_stream);
 void l2_qlinear_free(l2_qlinear* h);
 
+/* ---- attention of one position (src/models.rs:100-176, 236-249) on device buffers --------- */
+
+/* The RoPE cos/sin table of the reference's formula (src/models.rs:107-110), [seq_len][64] each; host. */
+int l2_rope_table(int seq_len, float* cos_out, float* sin_out);
+/* Bytes of device scratch l2_attention_decode_dev needs (split partials and arrival tickets). */
+size_t l2_attention_workspace_bytes(int n_heads, int n_kv_heads);
+/* rope(q, k, pos); key_cache[pos] = k; value_cache[pos] = v; out = multihead_attention(q, caches, pos)
+ * for head size 128.  All pointers are device memory: q/out [n_heads*128], k/v [n_kv_heads*128],
+ * caches [SEQ][n_kv_heads][128] of one layer, rope tables from l2_rope_table, workspace from the
+ * caller (contents need not be kept between calls).  Enqueued on cuda_stream, no synchronisation. */
+int l2_attention_decode_dev(int n_heads, int n_kv_heads, int pos, const float* q, const float* k, const float* v,
+                            float* key_cache, float* value_cache, const float* rope_cos, const float* rope_sin,
+                            float* out, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
 /* ---- measurement hooks (no counterpart in the reference, which times whole runs only,
  *      src/main.rs:61-65) --------------------------------------------------------------- */
 /* Enqueue `count` launches of one projection kernel of the token forward, cycling through the

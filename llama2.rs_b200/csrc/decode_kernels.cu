@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     grid_dependency_wait();
     grid_launch_dependents();
     const int kvh = blockIdx.x, split = blockIdx.y;
-    const int pos = p.ctl->pos;
+    const int pos = p.pos_fixed >= 0 ? p.pos_fixed : p.ctl->pos;
     const int T = pos + 1;
     int nsplit = (T + p.split_min - 1) / p.split_min;
     nsplit = nsplit < 1 ? 1 : (nsplit > p.max_split ? p.max_split : nsplit);
@@ -470,7 +470,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
     }
     if (nsplit == 1) {
 #pragma unroll
-        for (int g = 0; g < AG; g++) p.out[p.oidx[(kvh * AG + g) * HS + i]] = A[g] / L[g];
+        for (int g = 0; g < AG; g++) {
+            const int o = (kvh * AG + g) * HS + i;
+            p.out[p.oidx ? p.oidx[o] : o] = A[g] / L[g];
+        }
         return;
     }
 #pragma unroll
@@ -501,7 +504,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
             ll += __ldcg(src + (size_t)s * (HS + 2) + HS + 1) * e;
             aa += __ldcg(src + (size_t)s * (HS + 2) + i) * e;
         }
-        p.out[p.oidx[(kvh * AG + g) * HS + i]] = aa / ll;
+        const int o = (kvh * AG + g) * HS + i;
+        p.out[p.oidx ? p.oidx[o] : o] = aa / ll;
     }
 }
 

@@ -69,8 +69,9 @@ struct AttnParams {
     const Ctl* ctl;
     float* part;                                     // [n_heads][max_split][HS+2] split partials
     unsigned* counter;                               // [n_kv_heads] arrival tickets
-    float* out; const int* oidx;                     // attention output scattered into wo's K order
+    float* out; const int* oidx;                     // attention output scattered into wo's K order (null: natural order)
     int n_kv_heads, ag, max_split, split_min;
+    int pos_fixed;                                   // >= 0: use this position instead of ctl->pos
 };
 
 struct ClsParams {

@@ -254,6 +254,7 @@ static void launch_attention(l2_state* s, int l, cudaStream_t st, bool pdl) {
     a.out = s->att; a.oidx = y.wo.inv;
     a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups();
     a.max_split = s->max_split; a.split_min = 64;
+    a.pos_fixed = -1;
     launch_attn(a, st, pdl);
 }
 
@@ -780,6 +781,63 @@ extern "C" uint64_t l2_projection_bytes(const l2_model* m, int which) {
         case 4: return (uint64_t)sh.c.vocab_size * sh.c.dim * 4;
     }
     return 0;
+}
+
+// ---- C ABI: attention of one position on caller-owned device buffers ------------------------------
+
+static int attention_max_split(int n_kv_heads) { return std::max(1, std::min(32, (2 * 148 + n_kv_heads - 1) / n_kv_heads)); }
+
+extern "C" int l2_rope_table(int seq_len, float* cos_out, float* sin_out) {
+    clear_error();
+    if (seq_len <= 0 || !cos_out || !sin_out) return fail(L2_EINVAL, "l2_rope_table: bad argument");
+    const int half = HS / 2;
+    for (int p = 0; p < seq_len; p++)
+        for (int i = 0; i < half; i++) {  // src/models.rs:107-110
+            const float freq = 1.0f / powf(10000.0f, (float)(2 * i % HS) / (float)HS);
+            const float val = (float)p * freq;
+            cos_out[(size_t)p * half + i] = cosf(val);
+            sin_out[(size_t)p * half + i] = sinf(val);
+        }
+    return L2_OK;
+}
+
+extern "C" size_t l2_attention_workspace_bytes(int n_heads, int n_kv_heads) {
+    if (n_heads <= 0 || n_kv_heads <= 0) return 0;
+    return 256 + (size_t)n_heads * attention_max_split(n_kv_heads) * (HS + 2) * sizeof(float);
+}
+
+int l2::check_attention_args(int n_heads, int n_kv_heads, int pos, const void* q, const void* k, const void* v, const void* kc,
+                             const void* vc, const void* rc, const void* rs, const void* out) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return fail(L2_EINVAL, "attention: kv heads must divide heads");
+    const int ag = n_heads / n_kv_heads;
+    if (ag != 1 && ag != 2 && ag != 4 && ag != 8) return fail(L2_EINVAL, "attention: %d query heads per kv head unsupported (1, 2, 4 or 8)", ag);
+    if (pos < 0) return fail(L2_ERANGE, "attention: negative position");
+    if (!q || !k || !v || !kc || !vc || !rc || !rs || !out) return fail(L2_EINVAL, "attention: null device pointer");
+    return L2_OK;
+}
+
+extern "C" int l2_attention_decode_dev(int n_heads, int n_kv_heads, int pos, const float* q, const float* k, const float* v,
+                                       float* key_cache, float* value_cache, const float* rope_cos, const float* rope_sin,
+                                       float* out, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+    clear_error();
+    if (int rc = check_attention_args(n_heads, n_kv_heads, pos, q, k, v, key_cache, value_cache, rope_cos, rope_sin, out)) return rc;
+    if (!workspace || workspace_bytes < l2_attention_workspace_bytes(n_heads, n_kv_heads))
+        return fail(L2_EINVAL, "attention: workspace of %zu bytes needed", l2_attention_workspace_bytes(n_heads, n_kv_heads));
+    if (n_kv_heads * sizeof(unsigned) > 256) return fail(L2_EINVAL, "attention: more than 64 kv heads");
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    L2_CUDA(cudaMemsetAsync(workspace, 0, 256, st));  // arrival tickets start at zero
+    AttnParams a{};
+    a.q = q; a.k = k; a.v = v; a.kc = key_cache; a.vc = value_cache;
+    a.rope_cos = rope_cos; a.rope_sin = rope_sin;
+    a.ctl = nullptr; a.pos_fixed = pos;
+    a.counter = static_cast<unsigned*>(workspace);
+    a.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256);
+    a.out = out; a.oidx = nullptr;
+    a.n_kv_heads = n_kv_heads; a.ag = n_heads / n_kv_heads;
+    a.max_split = attention_max_split(n_kv_heads); a.split_min = 64;
+    launch_attn(a, st, false);
+    L2_CUDA(cudaGetLastError());
+    return L2_OK;
 }
 
 // ---- C ABI: one QLinear ---------------------------------------------------------------------------

@@ -94,5 +94,7 @@ struct l2_qlinear {
 namespace l2 {
 int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vector<void*>& allocs, size_t* bytes);
 void launch_permute(const float* x, const int* perm, float* xp, int n, cudaStream_t st);
+int check_attention_args(int n_heads, int n_kv_heads, int pos, const void* q, const void* k, const void* v, const void* kc,
+                         const void* vc, const void* rc, const void* rs, const void* out);
 int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, cudaStream_t st);
 }  // namespace l2
