@@ -167,6 +167,17 @@ int l2_attention_decode_dev(int n_heads, int n_kv_heads, int pos, const float* q
                             float* key_cache, float* value_cache, const float* rope_cos, const float* rope_sin,
                             float* out, void* workspace, size_t workspace_bytes, void* cuda_stream);
 
+/* The same computation for callers that cannot allocate device memory (no counterpart in the
+ * reference).  Takes no workspace: the split-sequence scratch is a fixed array inside the library
+ * (about 1.1 MB held on every GPU that loads it, until the process exits), which limits it to
+ * 64 query heads and 64 kv heads; larger shapes are rejected with L2_EINVAL.  Calls no cudaMalloc,
+ * cudaFree or other allocating routine.  The device is the current one.  The first call on a
+ * device looks up the array's address: make it before any stream capture.  All calls on a device
+ * share the array: calls that overlap on the GPU race and must be serialised by the caller. */
+int l2_attention_decode_noalloc(int n_heads, int n_kv_heads, int pos, const float* q, const float* k, const float* v,
+                                float* key_cache, float* value_cache, const float* rope_cos, const float* rope_sin,
+                                float* out, void* cuda_stream);
+
 /* ---- measurement hooks (no counterpart in the reference, which times whole runs only,
  *      src/main.rs:61-65) --------------------------------------------------------------- */
 /* Enqueue `count` launches of one projection kernel of the token forward, cycling through the

@@ -73,6 +73,7 @@ SIGNATURES = {
     "l2_rope_table": (C.c_int, [C.c_int, _f32p, _f32p]),
     "l2_attention_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "l2_attention_decode_dev": (C.c_int, [C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
+    "l2_attention_decode_noalloc": (C.c_int, [C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "l2_bench_projection": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int]),
     "l2_projection_bytes": (C.c_uint64, [_vp, C.c_int]),
     "l2_random_u32": (C.c_uint32, [_u64p]),
