@@ -58,6 +58,7 @@ typedef struct l2_options {
 
 #define L2_FLAG_NO_GRAPH 1 /* launch kernels directly instead of replaying the per-token CUDA graph */
 #define L2_FLAG_NO_PDL 2   /* do not use programmatic dependent launch between the kernels of a token */
+#define L2_FLAG_NO_L2_PREFETCH 4 /* do not prefetch the next kernel's weights into L2 */
 
 typedef struct l2_model l2_model;     /* LlamaModel (src/lib.rs:28-36, 68-77) */
 typedef struct l2_state l2_state;     /* RunState (src/models.rs:29-42) */
@@ -187,6 +188,10 @@ int l2_bench_projection(l2_model* m, l2_state* s, int which, int layer0, int cou
 /* Algorithmic bytes one such launch streams (qweight+qzeros+scales, or the f32 classifier). */
 uint64_t l2_projection_bytes(const l2_model* m, int which);
 
+/* Debug: per-CTA clock stamps of the GEMV kernels (8 per CTA); enable != 0 turns tracing on for
+ * launches planned afterwards, host_out (may be NULL) receives the stamps of the last launch. */
+int l2_debug_trace(int enable, unsigned long long* host_out, int n_ctas);
+
 /* ---- sampling helpers (src/util.rs:39-46, 71-113) ----------------------------------- */
 uint32_t l2_random_u32(uint64_t* seed);
 float l2_random_f32(uint64_t* seed);
@@ -202,11 +207,13 @@ const char* l2_tokenizer_vocab(const l2_tokenizer* t, int32_t id);
 const char* l2_tokenizer_piece(const l2_tokenizer* t, int32_t prev, int32_t next);
 
 /* ---- host-side repack, exposed so that it can be checked without a GPU --------------- */
-/* Device layout of one QLinear as built at load time: returns malloc'ed arrays the caller
- * frees with l2_host_free.  rows_order (NULL or [OUT]) re-orders output rows. */
+/* Device layout of one QLinear as built at load time (tiles of 16 rows, units of one group):
+ * qw [tiles][groups][2][32][GS/32] u32 and meta [tiles][groups][20] u32 (16 f32 scales, 2 words of
+ * zero nibbles, 2 words of padding).  Returns malloc'ed arrays the caller frees with
+ * l2_host_free.  rows_order (NULL or [OUT]) re-orders output rows. */
 int l2_debug_repack(int in, int out, int group_size, const int32_t* qweight, const int32_t* qzeros,
-                    const float* scales, const int32_t* rows_order, uint32_t** qw_dev, float** scales_dev,
-                    uint32_t** zeros_dev, int* groups_padded);
+                    const float* scales, const int32_t* rows_order, uint32_t** qw_dev, uint32_t** meta_dev,
+                    int* tiles);
 void l2_host_free(void* p);
 
 #ifdef __cplusplus

@@ -1,16 +1,15 @@
 // Per-token kernels of the B=1 forward pass (src/models.rs:178-298), hand-written for sm_100a.
 //
 //   embed    token embedding row -> residual stream (+ copies in each consumer's K order)
-//   gemv_q4  fused rmsnorm + 4-bit dequant + GEMV for QLinear::matvec (src/gptq.rs:94-176),
-//            with store / residual-add+scatter / SwiGLU epilogues
+//   (the fused rmsnorm + 4-bit dequant + GEMV for QLinear::matvec lives in gemv_kernels.cu)
 //   attn     RoPE (src/models.rs:100-129) + KV append (:236-249) + GQA attention
 //            (:131-176) with split-K over the sequence
 //   cls      final rmsnorm + dense f32 classifier GEMV (src/model.rs:22-31)
 //   select   forced / argmax / temperature sample (src/inference.rs:154-173, src/util.rs:39-113)
 //
-// All of them are HBM-bound streaming kernels: weights are read once with 128-bit loads,
-// activations live in shared memory, reductions are warp shuffles in a fixed order (results
-// are bit-reproducible from run to run).
+// All of them are HBM-bound streaming kernels: weights and caches are read once with 128-bit
+// loads, activations live in shared memory, reductions are warp shuffles in a fixed order
+// (results are bit-reproducible from run to run).
 #include <cfloat>
 #include <cmath>
 
@@ -29,12 +28,6 @@ __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepco
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Streaming 128-bit load: read-only path, do not keep the line in L1 (weights are read once).
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 __device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
     float4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -51,34 +44,6 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
-}
-
-// Byte `sel & 3` of v placed in the low mantissa byte of 2^23: the float 8388608 + byte.
-template <int SEL>
-__device__ __forceinline__ float byte_to_biased_float(uint32_t v) {
-    return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540 + SEL));
-}
-
-// sum over the 32 weights of one 128-bit chunk of (q - z) * x.  zf = 8388608 + z, so
-// (8388608 + q) - zf = q - z exactly.  xv holds the 32 inputs of the chunk.
-__device__ __forceinline__ float dot32(const uint4& w, const float4 (&xv)[8], float zf) {
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t lo = ww[i] & 0x0F0F0F0Fu;         // nibbles 0,2,4,6 in bytes 0..3
-        const uint32_t hi = (ww[i] >> 4) & 0x0F0F0F0Fu;  // nibbles 1,3,5,7
-        const float4 a = xv[2 * i], b = xv[2 * i + 1];
-        s0 = fmaf(byte_to_biased_float<0>(lo) - zf, a.x, s0);
-        s1 = fmaf(byte_to_biased_float<0>(hi) - zf, a.y, s1);
-        s2 = fmaf(byte_to_biased_float<1>(lo) - zf, a.z, s2);
-        s3 = fmaf(byte_to_biased_float<1>(hi) - zf, a.w, s3);
-        s0 = fmaf(byte_to_biased_float<2>(lo) - zf, b.x, s0);
-        s1 = fmaf(byte_to_biased_float<2>(hi) - zf, b.y, s1);
-        s2 = fmaf(byte_to_biased_float<3>(lo) - zf, b.z, s2);
-        s3 = fmaf(byte_to_biased_float<3>(hi) - zf, b.w, s3);
-    }
-    return (s0 + s1) + (s2 + s3);
 }
 
 // Sum of squares of n floats (n % 4 == 0) over the whole block, the same value in every thread.
@@ -119,7 +84,7 @@ __global__ void __launch_bounds__(256) embed_kernel(const __grid_constant__ Embe
     }
 }
 
-void launch_cfg(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 grid, dim3 block, size_t smem,
+static void launch_cfg(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, dim3 grid, dim3 block, size_t smem,
                 cudaStream_t st, bool pdl) {
     cfg = cudaLaunchConfig_t{};
     cfg.gridDim = grid;
@@ -141,212 +106,6 @@ void launch_embed(const EmbedParams& p, cudaStream_t st, bool pdl) {
     cudaLaunchAttribute attr[1];
     launch_cfg(cfg, attr, dim3((p.dim + 255) / 256), dim3(256), 0, st, pdl);
     cudaLaunchKernelEx(&cfg, embed_kernel, p);
-}
-
-// ---- fused rmsnorm + 4-bit dequant + GEMV -------------------------------------------------
-//
-// Work split: a job's rows are cut into blocks of GEMV_R rows; every CTA owns a contiguous,
-// evenly sized range of row blocks.  Inside a CTA the 8 warps form G = 8/ks groups; a group
-// takes one row block per pass and its ks warps split K, each lane streaming 128-bit chunks
-// (32 weights) of its 4 rows.  The 32 matching inputs are read once from shared memory and
-// reused for the 4 rows.  x is staged in shared memory as xs[t][c] (float4 number t of chunk
-// c) so that consecutive lanes read consecutive 16-byte words.
-
-template <bool DUAL>
-struct GemvItem {
-    uint4 w[GEMV_R];
-    float s[GEMV_R];
-    uint32_t z;
-    uint4 w2[DUAL ? GEMV_R : 1];
-    float s2[DUAL ? GEMV_R : 1];
-    uint32_t z2;
-};
-
-template <bool DUAL>
-__device__ __forceinline__ void gemv_load(GemvItem<DUAL>& it, const GemvJob& J, int rb, int c, int C, bool valid) {
-    if (!valid) return;
-    const int row0 = rb * GEMV_R;
-    const int g = c >> J.gshift;
-    const uint4* p = J.qw + (size_t)row0 * C + c;
-#pragma unroll
-    for (int r = 0; r < GEMV_R; r++) it.w[r] = ld_stream(p + (size_t)r * C);
-#pragma unroll
-    for (int r = 0; r < GEMV_R; r++) it.s[r] = __ldg(J.sc + (size_t)(row0 + r) * J.gp + g);
-    it.z = __ldg(J.zr + (size_t)(row0 >> 3) * J.gp + g) >> (4 * (row0 & 7));
-    if (DUAL) {
-        const uint4* p2 = J.qw2 + (size_t)row0 * C + c;
-#pragma unroll
-        for (int r = 0; r < GEMV_R; r++) it.w2[r] = ld_stream(p2 + (size_t)r * C);
-#pragma unroll
-        for (int r = 0; r < GEMV_R; r++) it.s2[r] = __ldg(J.sc2 + (size_t)(row0 + r) * J.gp + g);
-        it.z2 = __ldg(J.zr2 + (size_t)(row0 >> 3) * J.gp + g) >> (4 * (row0 & 7));
-    }
-}
-
-// zero point nibble r of z, plus the reference's "+ 1" (src/gptq.rs:148), as 8388608 + z
-__device__ __forceinline__ float zero_float(uint32_t z, int r) {
-    return __uint_as_float(0x4B000000u | (((z >> (4 * r)) & 15u) + 1u));
-}
-
-template <bool DUAL>
-__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_q4_kernel(const __grid_constant__ GemvParams P) {
-    extern __shared__ float4 smem4[];
-    __shared__ float red[2][GEMV_WARPS][GEMV_R * 2];
-    __shared__ float scratch[34];
-
-    int ji = 0;
-    for (int j = 1; j < P.njobs; j++)
-        if ((int)blockIdx.x >= P.job[j].cta0) ji = j;
-    const GemvJob& J = P.job[ji];
-    const int cta = blockIdx.x - J.cta0;
-    const int C = J.in >> 5;  // 128-bit chunks per row
-    const int nrb = J.rows / GEMV_R;
-    const int rb_begin = (int)(((long long)cta * nrb) / J.ncta);
-    const int rb_end = (int)(((long long)(cta + 1) * nrb) / J.ncta);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ks = J.ks, G = GEMV_WARPS / ks;
-    const int grp = warp / ks, slice = warp % ks;
-    const int nit = (C + ks * 32 - 1) / (ks * 32);
-    const int npass = (rb_end - rb_begin + G - 1) / G;
-    const int total = npass * nit;
-
-    // The first weights do not depend on the previous kernel: put them in flight before waiting.
-    GemvItem<DUAL> cur, nxt;
-    {
-        const int rb = rb_begin + grp, c = slice * 32 + lane;
-        gemv_load<DUAL>(cur, J, rb, c, C, total > 0 && rb < rb_end && c < C);
-    }
-    grid_dependency_wait();
-    grid_launch_dependents();
-    if (total == 0) return;
-
-    // ---- stage the input vector(s), applying rmsnorm when a norm weight is given
-    float4* xs = smem4;
-    float4* xs2 = smem4 + (size_t)8 * C;
-    {
-        float ss = 1.f;
-        if (J.nw) {
-            const float sum = block_sum_sq(J.x, J.in, scratch);
-            ss = 1.0f / sqrtf(sum / (float)J.in + P.eps);  // src/models.rs:58-60
-        }
-        const float4* x4 = reinterpret_cast<const float4*>(J.x);
-        const float4* n4 = reinterpret_cast<const float4*>(J.nw);
-        for (int i = threadIdx.x; i < J.in / 4; i += GEMV_THREADS) {
-            float4 v = x4[i];
-            if (J.nw) {
-                const float4 w = n4[i];
-                v.x = (w.x * ss) * v.x; v.y = (w.y * ss) * v.y; v.z = (w.z * ss) * v.z; v.w = (w.w * ss) * v.w;
-            }
-            xs[(size_t)(i & 7) * C + (i >> 3)] = v;
-        }
-        if (DUAL) {
-            float ss2 = 1.f;
-            if (J.nw2) {
-                const float sum = block_sum_sq(J.x2, J.in, scratch);
-                ss2 = 1.0f / sqrtf(sum / (float)J.in + P.eps);
-            }
-            const float4* y4 = reinterpret_cast<const float4*>(J.x2);
-            const float4* m4 = reinterpret_cast<const float4*>(J.nw2);
-            for (int i = threadIdx.x; i < J.in / 4; i += GEMV_THREADS) {
-                float4 v = y4[i];
-                if (J.nw2) {
-                    const float4 w = m4[i];
-                    v.x = (w.x * ss2) * v.x; v.y = (w.y * ss2) * v.y; v.z = (w.z * ss2) * v.z; v.w = (w.w * ss2) * v.w;
-                }
-                xs2[(size_t)(i & 7) * C + (i >> 3)] = v;
-            }
-        }
-        __syncthreads();
-    }
-
-    float acc[GEMV_R], acc2[GEMV_R];
-    int idx = 0;
-    for (int pass = 0; pass < npass; pass++) {
-        const int rb = rb_begin + pass * G + grp;
-#pragma unroll
-        for (int r = 0; r < GEMV_R; r++) { acc[r] = 0.f; acc2[r] = 0.f; }
-        for (int it = 0; it < nit; it++, idx++) {
-            const int c = slice * 32 + lane + it * ks * 32;
-            const bool valid = rb < rb_end && c < C;
-            {   // prefetch the next item of this warp
-                int np = pass, ni = it + 1;
-                if (ni == nit) { ni = 0; np = pass + 1; }
-                const int nrbk = rb_begin + np * G + grp, nc = slice * 32 + lane + ni * ks * 32;
-                gemv_load<DUAL>(nxt, J, nrbk, nc, C, np < npass && nrbk < rb_end && nc < C);
-            }
-            if (valid) {
-                float4 xv[8];
-#pragma unroll
-                for (int t = 0; t < 8; t++) xv[t] = xs[(size_t)t * C + c];
-#pragma unroll
-                for (int r = 0; r < GEMV_R; r++)
-                    acc[r] = fmaf(cur.s[r], dot32(cur.w[r], xv, zero_float(cur.z, r)), acc[r]);
-                if (DUAL) {
-#pragma unroll
-                    for (int t = 0; t < 8; t++) xv[t] = xs2[(size_t)t * C + c];
-#pragma unroll
-                    for (int r = 0; r < GEMV_R; r++)
-                        acc2[r] = fmaf(cur.s2[r], dot32(cur.w2[r], xv, zero_float(cur.z2, r)), acc2[r]);
-                }
-            }
-            cur = nxt;
-        }
-        // ---- reduce over lanes, then over the ks warps of the group, in a fixed order
-#pragma unroll
-        for (int r = 0; r < GEMV_R; r++) {
-            acc[r] = warp_sum(acc[r]);
-            if (DUAL) acc2[r] = warp_sum(acc2[r]);
-        }
-        float(*rd)[GEMV_R * 2] = red[pass & 1];
-        if (lane == 0) {
-#pragma unroll
-            for (int r = 0; r < GEMV_R; r++) { rd[warp][r] = acc[r]; rd[warp][GEMV_R + r] = acc2[r]; }
-        }
-        __syncthreads();
-        if (threadIdx.x < G * GEMV_R) {
-            const int eg = threadIdx.x / GEMV_R, r = threadIdx.x % GEMV_R;
-            const int erb = rb_begin + pass * G + eg;
-            if (erb < rb_end) {
-                float y = 0.f, y2 = 0.f;
-                for (int s = 0; s < ks; s++) { y += rd[eg * ks + s][r]; y2 += rd[eg * ks + s][GEMV_R + r]; }
-                const int row = erb * GEMV_R + r;
-                if (J.epi == EPI_STORE) {
-                    J.out[row] = y;
-                } else if (J.epi == EPI_SWIGLU) {  // src/models.rs:92-98
-                    const float sg = y * (1.0f / (1.0f + expf(-y)));
-                    J.out[row] = sg * y2;
-                } else {  // residual add (src/models.rs:47-51) + copies for the next consumers
-                    const float v = J.out[row] + y;
-                    J.out[row] = v;
-                    for (int s = 0; s < J.nscatter; s++) J.sdst[s][J.sidx[s][row]] = v;
-                }
-            }
-        }
-    }
-}
-
-size_t gemv_smem_bytes(int in, bool dual) { return (size_t)in * 4 * (dual ? 2 : 1); }
-
-int gemv_ctas_per_sm(int in, bool dual) {
-    // cached: the occupancy query must not run while a stream capture is open
-    static int cache_in[16], cache_val[16], cache_n = 0;
-    const int key = in * 2 + (dual ? 1 : 0);
-    for (int i = 0; i < cache_n; i++)
-        if (cache_in[i] == key) return cache_val[i];
-    int n = 0;
-    if (dual) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_q4_kernel<true>, GEMV_THREADS, gemv_smem_bytes(in, true));
-    else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_q4_kernel<false>, GEMV_THREADS, gemv_smem_bytes(in, false));
-    n = n < 1 ? 1 : (n > 2 ? 2 : n);
-    if (cache_n < 16) { cache_in[cache_n] = key; cache_val[cache_n] = n; cache_n++; }
-    return n;
-}
-
-void launch_gemv(const GemvParams& p, int grid, size_t smem, bool dual, cudaStream_t st, bool pdl) {
-    cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
-    launch_cfg(cfg, attr, dim3(grid), dim3(GEMV_THREADS), smem, st, pdl);
-    if (dual) cudaLaunchKernelEx(&cfg, gemv_q4_kernel<true>, p);
-    else cudaLaunchKernelEx(&cfg, gemv_q4_kernel<false>, p);
 }
 
 // ---- RoPE + KV append + attention, split over the sequence ----------------------------------
@@ -713,8 +472,7 @@ cudaError_t kernels_init() {
     int dev = 0, max_optin = 0;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(gemv_q4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin - 2048)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(gemv_q4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin - 2048)) != cudaSuccess) return e;
+    if ((e = sk_init(max_optin - 2048)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(cls_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin - 2048)) != cudaSuccess) return e;
     return cudaSuccess;
 }

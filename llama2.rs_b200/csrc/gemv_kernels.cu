@@ -1,0 +1,512 @@
+// Fused rmsnorm + 4-bit dequant + GEMV for QLinear::matvec at batch 1 (src/gptq.rs:94-176),
+// hand-written for sm_100a.
+//
+// The kernel is bound by HBM only if it spends about one instruction per 4-bit weight, so the
+// inner product runs on the tensor cores with exact integer arithmetic:
+//
+//   * the activation vector is turned, once per CTA, into four 7-bit digits per element:
+//     X = round(v * 2^e) with |X| < 2^27, X = d0*2^21 + d1*2^14 + d2*2^7 + d3 with d0 = X >> 21 signed
+//     and d1..d3 in 0..127 (block floating point over the whole vector; the error is below 2^-27 of
+//     the largest element, finer than f32);
+//   * weights stay packed nibbles in HBM; in registers a word becomes two MMA operands with three
+//     bit operations (lo = w & 0x0F0F0F0F, hi = (w >> 4) & 0x0F0F0F0F), no int->float conversion;
+//   * mma.sync.m16n8k32 (u8 x s8 -> s32) multiplies 16 rows x 32 weights by the four digit columns;
+//     the sums over one quantisation group are exact integers, the zero point is removed with the
+//     group's digit sums, and one f32 FMA per row and group applies the scale;
+//   * work split: every CTA owns a contiguous run of whole 16-row tiles; the (tile, group) units of
+//     that run are dealt out evenly to the warps as contiguous ranges (contiguous in memory as
+//     well), and tiles that straddle warps are summed through shared memory in warp order, so
+//     results are bit-reproducible and no CTA ever waits for another;
+//   * weights never pass through registers on their way in: every warp owns a small ring of shared
+//     memory slots that it fills with bulk asynchronous copies (cp.async.bulk, completion counted
+//     on an mbarrier per slot) of the next few units of its range; the copies are issued before the
+//     kernel waits for its predecessor and keep HBM streaming while the activations are staged;
+//   * every CTA also asks the L2 to fetch its share of the next kernel's weights
+//     (cp.async.bulk.prefetch.L2).
+//
+// rmsnorm is folded in by linearity: the digits are those of (norm weight * x) and the output is
+// multiplied by 1/sqrt(mean(x^2)+eps) at the end.  Epilogues: store, residual add + scatter into
+// the next consumers' K orders, or SwiGLU (w1 and w3 rows of a tile are processed together).
+#include <cfloat>
+#include <cmath>
+
+#include "kernels.cuh"
+
+namespace l2 {
+
+unsigned long long* g_sk_trace = nullptr;
+
+#define SK_STAMP(i) do { if (P.trace && threadIdx.x == 0) P.trace[blockIdx.x * 8 + (i)] = clock64(); } while (0)
+#define SK_STAMP0() do { if (threadIdx.x == 0) t_entry = clock64(); } while (0)
+
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for a phase of the barrier, but never forever: after SK_WAIT_LIMIT polls it gives up and
+// reports failure (the caller records it in the status word and stops using the data).
+constexpr uint32_t SK_WAIT_LIMIT = 1u << 24;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SK_WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// Bulk asynchronous copy global -> shared of this CTA; bytes and both addresses are multiples of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ float block_reduce_2(float& mx, float sq, float* red /* 2*SK_WARPS+2 floats */) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    }
+    if (lane == 0) { red[warp] = mx; red[SK_WARPS + warp] = sq; }
+    __syncthreads();
+    if (warp == 0) {
+        float m = lane < SK_WARPS ? red[lane] : 0.f;
+        float s = lane < SK_WARPS ? red[SK_WARPS + lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            s += __shfl_xor_sync(0xffffffffu, s, o);
+        }
+        if (lane == 0) { red[2 * SK_WARPS] = m; red[2 * SK_WARPS + 1] = s; }
+    }
+    __syncthreads();
+    mx = red[2 * SK_WARPS];
+    const float total = red[2 * SK_WARPS + 1];
+    __syncthreads();
+    return total;
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 255) | ((uint32_t)(b & 255) << 8) | ((uint32_t)(c & 255) << 16) | ((uint32_t)(d & 255) << 24);
+}
+
+// Turns the vector of one segment into digits and per-group digit sums in shared memory.
+// Returns (in every thread) the factor the integer result has to be multiplied with.
+// Thread i owns the 8-input blocks i, i + 512, ...; the first SK_KEEP of them stay in registers
+// between the two passes (max / sum of squares, then digits).
+constexpr int SK_KEEP = 3;
+
+template <int W>
+__device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digits, int* ss, float* red) {
+    const float4* x4 = reinterpret_cast<const float4*>(sg.x);
+    const float4* n4 = reinterpret_cast<const float4*>(sg.nw);
+    const int nblk = in / 8;
+    float mx = 0.f, sq = 0.f;
+    float4 keep[SK_KEEP][2];
+#pragma unroll
+    for (int k = 0; k < SK_KEEP; k++) keep[k][0] = keep[k][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto fetch = [&](int blk, float4& v0, float4& v1, bool stats) {
+        v0 = x4[2 * blk];
+        v1 = x4[2 * blk + 1];
+        if (stats) sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+        if (sg.nw) {
+            const float4 w0 = n4[2 * blk], w1 = n4[2 * blk + 1];
+            v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
+            v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
+        }
+        if (stats) {
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))));
+            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+        }
+    };
+#pragma unroll
+    for (int k = 0; k < SK_KEEP; k++) {
+        const int blk = threadIdx.x + k * SK_THREADS;
+        if (blk < nblk) fetch(blk, keep[k][0], keep[k][1], true);
+    }
+    for (int blk = threadIdx.x + SK_KEEP * SK_THREADS; blk < nblk; blk += SK_THREADS) {
+        float4 a, b;
+        fetch(blk, a, b, true);
+    }
+    const float total = block_reduce_2(mx, sq, red);
+    const float rs = sg.nw ? 1.0f / sqrtf(total / (float)in + eps) : 1.0f;  // src/models.rs:58-60
+    // P = 2^(26 - E) with 2^E <= max|v| < 2^(E+1): |v * P| < 2^27
+    int e = 0;
+    if (mx > 0.f && mx < INFINITY) e = 26 - (int)((__float_as_uint(mx) >> 23) & 255u) + 127;
+    e = max(-100, min(100, e));
+    const float P = __uint_as_float((uint32_t)(127 + e) << 23);
+    const int stride = in + 16;
+    // called by whole warps; lanes whose block lies beyond the vector pass zeros and valid = false
+    auto emit = [&](int blk, const float4& v0, const float4& v1, bool valid) {
+        const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        uint32_t E[8];  // per element: bytes d3, d2, d1, d0 (d0 signed, the others 0..127)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t X = (uint32_t)__float2int_rn(v[j] * P);
+            E[j] = (X & 0x7Fu) | ((X << 1) & 0x7F00u) | ((X << 2) & 0x7F0000u) | ((X << 3) & 0xFF000000u);
+        }
+        // 4x4 byte transposes: words of one digit for inputs (0,2,4,6) and (1,3,5,7), the order in
+        // which the nibbles of a weight word separate into its low and high halves
+        uint32_t lo[4], hi[4];
+        {
+            const uint32_t a = __byte_perm(E[0], E[2], 0x5140), b2 = __byte_perm(E[0], E[2], 0x7362);
+            const uint32_t c = __byte_perm(E[4], E[6], 0x5140), d = __byte_perm(E[4], E[6], 0x7362);
+            lo[3] = __byte_perm(a, c, 0x5410); lo[2] = __byte_perm(a, c, 0x7632);
+            lo[1] = __byte_perm(b2, d, 0x5410); lo[0] = __byte_perm(b2, d, 0x7632);
+        }
+        {
+            const uint32_t a = __byte_perm(E[1], E[3], 0x5140), b2 = __byte_perm(E[1], E[3], 0x7362);
+            const uint32_t c = __byte_perm(E[5], E[7], 0x5140), d = __byte_perm(E[5], E[7], 0x7362);
+            hi[3] = __byte_perm(a, c, 0x5410); hi[2] = __byte_perm(a, c, 0x7632);
+            hi[1] = __byte_perm(b2, d, 0x5410); hi[0] = __byte_perm(b2, d, 0x7632);
+        }
+        int sum[4];
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            if (valid) *reinterpret_cast<uint2*>(digits + (size_t)p * stride + (size_t)blk * 8) = make_uint2(lo[p], hi[p]);
+            sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
+        }
+        // a group is 4*W consecutive blocks = 4*W consecutive lanes: sum them with shuffles
+        int s01 = 128 * sum[0] + sum[1], s23 = 128 * sum[2] + sum[3];
+#pragma unroll
+        for (int o = 1; o < 4 * W; o <<= 1) {
+            s01 += __shfl_xor_sync(0xffffffffu, s01, o);
+            s23 += __shfl_xor_sync(0xffffffffu, s23, o);
+        }
+        if (valid && (threadIdx.x & (4 * W - 1)) == 0) {
+            const int g = blk / (4 * W);
+            ss[2 * g] = s01;
+            ss[2 * g + 1] = s23;
+        }
+    };
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int rounds = (nblk + SK_THREADS - 1) / SK_THREADS;
+#pragma unroll
+    for (int k = 0; k < SK_KEEP; k++) {
+        const int blk = threadIdx.x + k * SK_THREADS;
+        if (k < rounds && (blk & ~31) < nblk) {  // warp-uniform
+            const bool valid = blk < nblk;
+            emit(blk, valid ? keep[k][0] : zero4, valid ? keep[k][1] : zero4, valid);
+        }
+    }
+    for (int k = SK_KEEP; k < rounds; k++) {
+        const int blk = threadIdx.x + k * SK_THREADS;
+        if ((blk & ~31) < nblk) {
+            const bool valid = blk < nblk;
+            float4 a = zero4, b = zero4;
+            if (valid) fetch(blk, a, b, false);
+            emit(blk, a, b, valid);
+        }
+    }
+    return rs / P;
+}
+
+// Asks the L2 to fetch [p, p + bytes) from HBM; nothing waits on it.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+    const char* c = static_cast<const char*>(p);
+    for (uint32_t off = 0; off < bytes; off += 32768u) {
+        const uint32_t n = min(32768u, bytes - off) & ~15u;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(c + off), "r"(n) : "memory");
+    }
+}
+
+template <int W, int NSEG>
+__global__ void __launch_bounds__(SK_THREADS, 1) gemv_sk_kernel(const SkParams* __restrict__ gp) {
+    constexpr int GS = 32 * W;
+    constexpr int ROWS = 16 * NSEG;  // rows of a (super) tile
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ float red[2 * SK_WARPS + 2];
+    __shared__ float oscale[2];
+    __shared__ __align__(8) uint64_t bars[SK_WARPS * SK_MAX_SLOTS];
+    __shared__ SkParams sp;
+
+    // The launch record lives in global memory: one cooperative 128-bit load per thread brings it into
+    // shared memory (kernel arguments this large would cost a chain of constant-cache misses).
+    long long t_entry = 0;
+    SK_STAMP0();
+    static_assert(sizeof(SkParams) % 16 == 0, "SkParams is copied in 16-byte pieces");
+    if (threadIdx.x < sizeof(SkParams) / 16)
+        reinterpret_cast<uint4*>(&sp)[threadIdx.x] = __ldg(reinterpret_cast<const uint4*>(gp) + threadIdx.x);
+    __syncthreads();
+    const SkParams& P = sp;
+    if (P.trace && threadIdx.x == 0) P.trace[blockIdx.x * 8] = t_entry;
+
+    int ji = 0;
+    for (int j = 1; j < P.njobs; j++)
+        if ((int)blockIdx.x >= P.job[j].cta0) ji = j;
+    const SkJob& J = P.job[ji];
+    const int cta = blockIdx.x - J.cta0;
+    const int G = J.G, Gs = NSEG * G;
+    // whole tiles per CTA: the first `trem` CTAs own tq + 1 tiles, the others tq
+    const int tau_first = cta * J.tq + min(cta, J.trem);
+    const int nt = J.tq + (cta < J.trem ? 1 : 0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = nt * Gs;                      // units of this CTA
+    const int wa = n * warp / SK_WARPS, wb = n * (warp + 1) / SK_WARPS;  // this warp's units, relative to the CTA's first
+    // position of the warp's first unit: tile, segment, group (division by reciprocal, corrected)
+    int w_tl = (int)((float)wa * J.rGs);
+    if (w_tl * Gs > wa) w_tl--; else if ((w_tl + 1) * Gs <= wa) w_tl++;
+    int w_seg = 0, w_g = wa - w_tl * Gs;
+    if (NSEG == 2 && w_g >= G) { w_seg = 1; w_g -= G; }
+
+    // shared memory carve-up
+    const int dstride = J.in + 16;
+    uint8_t* digits = smem;                                              // [NSEG][4][in + 16]
+    int* ss = reinterpret_cast<int*>(smem + (size_t)NSEG * 4 * dstride);  // [NSEG][G][2]
+    float* partial = reinterpret_cast<float*>(ss + NSEG * G * 2);        // [ptiles][SK_WARPS][ROWS]
+    const int CH = P.chunk, NS = P.slots;
+    const uint32_t slot_bytes = (uint32_t)CH * (256u * W + 80u);
+    const size_t fixed_bytes = ((size_t)NSEG * 4 * dstride + (size_t)NSEG * G * 8 + (size_t)P.ptiles * SK_WARPS * ROWS * 4 + 127) & ~(size_t)127;
+    uint8_t* ring = smem + fixed_bytes + (size_t)warp * NS * slot_bytes;  // 128-byte aligned (bulk copies need 16)
+    uint64_t* bar = bars + warp * SK_MAX_SLOTS;
+
+    // ---- weight stream of this warp: chunks of up to CH units that stay inside one (tile, segment)
+    // run, copied into the ring slots round-robin.  Independent of the previous kernel: start now.
+    struct ChunkIt { int u, tl, seg, g; };
+    auto chunk_len = [&](const ChunkIt& it) { return min(min(CH, wb - it.u), G - it.g); };
+    auto advance = [&](ChunkIt& it, int len) {
+        it.u += len;
+        it.g += len;
+        if (it.g == G) { it.g = 0; if (++it.seg == NSEG) { it.seg = 0; it.tl++; } }
+    };
+    auto issue = [&](int slot, const ChunkIt& it, int len) {  // lane 0 only
+        const SkSeg& S = J.seg[NSEG == 1 ? 0 : it.seg];
+        const size_t mu = (size_t)(tau_first + it.tl) * G + it.g;
+        const uint32_t bw = (uint32_t)len * 256u * W, bm = (uint32_t)len * 80u;
+        uint8_t* dst = ring + (size_t)slot * slot_bytes;
+        mbar_expect_tx(bar + slot, bw + bm);
+        bulk_g2s(dst, S.qw + mu * (64 * W), bw, bar + slot);
+        bulk_g2s(dst + (size_t)CH * 256 * W, S.meta + mu * 20, bm, bar + slot);
+    };
+    ChunkIt prod{wa, w_tl, w_seg, w_g}, cons = prod;
+    if (lane == 0) {
+        for (int i = 0; i < NS; i++) mbar_init(bar + i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int i = 0; i < NS && prod.u < wb; i++) {
+            const int len = chunk_len(prod);
+            issue(i, prod, len);
+            advance(prod, len);
+        }
+    }
+    __syncwarp();
+    // the next kernel's weights: every CTA asks the L2 for an equal slice of each range
+    if (lane == 0 && warp < P.n_next) {
+        const size_t per = P.next_slice[warp], off = per * blockIdx.x;
+        if (off < P.next_bytes[warp]) prefetch_l2(static_cast<const char*>(P.next_ptr[warp]) + off, (uint32_t)min(per, P.next_bytes[warp] - off));
+    }
+    // epilogue operands of this warp's first tile that do not depend on the previous kernel
+    const int e_row = (tau_first + warp) * 16 + (lane & 15);
+    const bool e_pre = NSEG == 1 && warp < nt && lane < 16 && e_row < J.rows && J.epi == EPI_RESID;
+    int e_idx[3] = {0, 0, 0};
+    if (e_pre)
+        for (int s = 0; s < 3; s++)
+            if (s < J.nscatter) e_idx[s] = __ldg(J.sidx[s] + e_row);
+    for (int i = threadIdx.x; i < nt * SK_WARPS * ROWS; i += SK_THREADS) partial[i] = 0.f;
+
+    SK_STAMP(1);
+    grid_dependency_wait();
+    grid_launch_dependents();
+    SK_STAMP(2);
+    float e_out = 0.f;
+    if (e_pre) e_out = J.out[e_row];
+
+    // ---- stage the activation digits (its first barrier also orders the zeroing of `partial`)
+    if (n > 0) {
+#pragma unroll
+        for (int s = 0; s < NSEG; s++) {
+            const float f = stage_digits<W>(J.seg[s], J.in, P.eps, digits + (size_t)s * 4 * dstride, ss + s * G * 2, red);
+            if (threadIdx.x == 0) oscale[s] = f;
+        }
+    }
+    __syncthreads();
+
+    SK_STAMP(3);
+    // ---- main loop over this warp's chunks
+    const int r = lane >> 2, t = lane & 3;
+    float tot0 = 0.f, tot1 = 0.f;
+    bool ok = true;
+    auto unit_finish = [&](const uint8_t* msl, int i, int seg, int g, const int (&c)[4]) {
+        if (t < 2) {
+            const uint32_t* mt = reinterpret_cast<const uint32_t*>(msl + (size_t)i * 80);
+            const float s0 = __uint_as_float(mt[r]), s1 = __uint_as_float(mt[8 + r]);
+            const int z0 = (int)((mt[16] >> (4 * r)) & 15u) + 1, z1 = (int)((mt[17] >> (4 * r)) & 15u) + 1;  // src/gptq.rs:148
+            const int sv = ss[((NSEG == 1 ? 0 : seg) * G + g) * 2 + t];
+            tot0 = fmaf(s0, (float)(c[0] * 128 + c[1] - z0 * sv), tot0);
+            tot1 = fmaf(s1, (float)(c[2] * 128 + c[3] - z1 * sv), tot1);
+        }
+    };
+    for (int chunk_no = 0; cons.u < wb; chunk_no++) {
+        const int slot = chunk_no % NS;
+        const int len = chunk_len(cons);
+        if (ok && !mbar_wait(bar + slot, (uint32_t)(chunk_no / NS) & 1u)) {
+            ok = false;
+            if (P.status) atomicExch(P.status, 1001);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            const uint8_t* wsl = ring + (size_t)slot * slot_bytes;
+            const uint8_t* msl = wsl + (size_t)CH * 256 * W;
+            if constexpr (W < 4) {  // smaller units: weights are 8 or 4 bytes per lane and row
+                for (int i = 0; i < len; i++) {
+                    int c[4] = {0, 0, 0, 0};
+                    const uint8_t* dg = digits + (size_t)(NSEG == 1 ? 0 : cons.seg) * 4 * dstride + (size_t)r * dstride + (cons.g + i) * GS + t * (8 * W);
+#pragma unroll
+                    for (int j = 0; j < W; j++) {
+                        const uint32_t a = *reinterpret_cast<const uint32_t*>(wsl + (size_t)i * 256 * W + lane * 4 * W + 4 * j);
+                        const uint32_t b = *reinterpret_cast<const uint32_t*>(wsl + (size_t)i * 256 * W + 128 * W + lane * 4 * W + 4 * j);
+                        uint2 bb = make_uint2(0u, 0u);
+                        if (r < 4) bb = *reinterpret_cast<const uint2*>(dg + 8 * j);
+                        mma_u8s8(c, a & 0x0F0F0F0Fu, b & 0x0F0F0F0Fu, (a >> 4) & 0x0F0F0F0Fu, (b >> 4) & 0x0F0F0F0Fu, bb.x, bb.y);
+                    }
+                    unit_finish(msl, i, cons.seg, cons.g + i, c);
+                }
+            } else {
+                // two units at a time: their MMA chains are independent and interleave in the pipe
+                const uint8_t* dgb = digits + (size_t)(NSEG == 1 ? 0 : cons.seg) * 4 * dstride + (size_t)r * dstride + cons.g * GS + t * 32;
+                for (int i = 0; i < len; i += 2) {
+                    const bool two = i + 1 < len;
+                    const uint8_t* wu = wsl + (size_t)i * 1024 + lane * 16;
+                    const uint4 a0 = *reinterpret_cast<const uint4*>(wu), b0 = *reinterpret_cast<const uint4*>(wu + 512);
+                    const uint4 a1 = *reinterpret_cast<const uint4*>(wu + (two ? 1024 : 0)), b1 = *reinterpret_cast<const uint4*>(wu + (two ? 1536 : 512));
+                    uint4 d00 = make_uint4(0, 0, 0, 0), d01 = d00, d10 = d00, d11 = d00;
+                    if (r < 4) {
+                        const uint4* dp = reinterpret_cast<const uint4*>(dgb + (size_t)i * GS);
+                        d00 = dp[0]; d01 = dp[1];
+                        if (two) { d10 = dp[GS / 16]; d11 = dp[GS / 16 + 1]; }
+                    }
+                    int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+                    constexpr uint32_t M = 0x0F0F0F0Fu;
+                    mma_u8s8(c0, a0.x & M, b0.x & M, (a0.x >> 4) & M, (b0.x >> 4) & M, d00.x, d00.y);
+                    mma_u8s8(c1, a1.x & M, b1.x & M, (a1.x >> 4) & M, (b1.x >> 4) & M, d10.x, d10.y);
+                    mma_u8s8(c0, a0.y & M, b0.y & M, (a0.y >> 4) & M, (b0.y >> 4) & M, d00.z, d00.w);
+                    mma_u8s8(c1, a1.y & M, b1.y & M, (a1.y >> 4) & M, (b1.y >> 4) & M, d10.z, d10.w);
+                    mma_u8s8(c0, a0.z & M, b0.z & M, (a0.z >> 4) & M, (b0.z >> 4) & M, d01.x, d01.y);
+                    mma_u8s8(c1, a1.z & M, b1.z & M, (a1.z >> 4) & M, (b1.z >> 4) & M, d11.x, d11.y);
+                    mma_u8s8(c0, a0.w & M, b0.w & M, (a0.w >> 4) & M, (b0.w >> 4) & M, d01.z, d01.w);
+                    mma_u8s8(c1, a1.w & M, b1.w & M, (a1.w >> 4) & M, (b1.w >> 4) & M, d11.z, d11.w);
+                    unit_finish(msl, i, cons.seg, cons.g + i, c0);
+                    if (two) unit_finish(msl, i + 1, cons.seg, cons.g + i + 1, c1);
+                }
+            }
+        }
+        __syncwarp();  // every lane has read the slot: it may be refilled
+        if (lane == 0 && ok && prod.u < wb) {
+            const int plen = chunk_len(prod);
+            issue(slot, prod, plen);
+            advance(prod, plen);
+        }
+        // a chunk never crosses a (tile, segment) boundary: flush the row sums when it ends one
+        if (cons.g + len == G || cons.u + len == wb) {
+            // lanes t = 0 hold digits 0,1 (weight 2^14 relative to digits 2,3 held by lanes t = 1)
+            float a = t == 0 ? tot0 * 16384.0f : tot0, b = t == 0 ? tot1 * 16384.0f : tot1;
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            b += __shfl_xor_sync(0xffffffffu, b, 1);
+            if (t == 0) {
+                float* dst = partial + ((size_t)cons.tl * SK_WARPS + warp) * ROWS + cons.seg * 16;
+                dst[r] = a;
+                dst[r + 8] = b;
+            }
+            tot0 = tot1 = 0.f;
+        }
+        advance(cons, len);
+    }
+    if (!ok) {
+        // copies may still be in flight into this CTA's shared memory: give them a bounded time
+        // to land before the CTA exits, without using their data
+        for (int i = 0; i < NS; i++) mbar_wait(bar + i, 0);
+        for (int i = 0; i < NS; i++) mbar_wait(bar + i, 1);
+    }
+    SK_STAMP(4);
+    __syncthreads();
+    SK_STAMP(5);
+
+    // ---- per tile: sum the warps in order, then the epilogue
+    for (int tl = warp; tl < nt; tl += SK_WARPS) {
+        const int tau = tau_first + tl;
+        float v = 0.f;
+        if (lane < ROWS)
+            for (int w = 0; w < SK_WARPS; w++) v += partial[((size_t)tl * SK_WARPS + w) * ROWS + lane];
+        const float y = v * oscale[lane >> 4 & (NSEG - 1)];
+        const int row = tau * 16 + (lane & 15);
+        if (NSEG == 2) {  // SwiGLU: lanes 0-15 hold w1 rows, lanes 16-31 the same rows of w3 (src/models.rs:92-98)
+            const float y3 = __shfl_down_sync(0xffffffffu, y, 16);
+            if (lane < 16 && row < J.rows) {
+                const float sg = y * (1.0f / (1.0f + expf(-y)));
+                J.out[row] = sg * y3;
+            }
+        } else if (lane < 16 && row < J.rows) {
+            if (J.epi == EPI_STORE) {
+                J.out[row] = y;
+            } else {  // residual add (src/models.rs:47-51) + copies in the next consumers' K orders
+                const bool pre = e_pre && tl == warp;
+                const float xv = (pre ? e_out : J.out[row]) + y;
+                J.out[row] = xv;
+                for (int s = 0; s < 3; s++)
+                    if (s < J.nscatter) J.sdst[s][pre ? e_idx[s] : J.sidx[s][row]] = xv;
+            }
+        }
+    }
+    SK_STAMP(6);
+}
+
+size_t sk_smem_fixed(int in, int G, int nseg, int ptiles) {
+    return (size_t)nseg * 4 * (in + 16) + (size_t)nseg * G * 2 * 4 + (size_t)ptiles * SK_WARPS * 16 * nseg * 4;
+}
+
+size_t sk_slot_bytes(int group_size, int chunk) { return (size_t)chunk * (8 * (size_t)group_size + 80); }
+
+template <int W, int NSEG>
+static cudaError_t launch_sk_t(const SkParams* p, int grid, size_t smem, cudaStream_t st, bool pdl) {
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(SK_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    g_launches++;
+    return cudaLaunchKernelEx(&cfg, gemv_sk_kernel<W, NSEG>, p);
+}
+
+cudaError_t launch_sk(const SkParams* p, int group_size, int nseg, int grid, size_t smem, cudaStream_t st, bool pdl) {
+    const int w = group_size / 32;
+    if (nseg == 1) {
+        if (w == 4) return launch_sk_t<4, 1>(p, grid, smem, st, pdl);
+        if (w == 2) return launch_sk_t<2, 1>(p, grid, smem, st, pdl);
+        return launch_sk_t<1, 1>(p, grid, smem, st, pdl);
+    }
+    if (w == 4) return launch_sk_t<4, 2>(p, grid, smem, st, pdl);
+    if (w == 2) return launch_sk_t<2, 2>(p, grid, smem, st, pdl);
+    return launch_sk_t<1, 2>(p, grid, smem, st, pdl);
+}
+
+cudaError_t sk_init(int max_smem) {
+    cudaError_t e;
+#define L2_SK_ATTR(W, N) \
+    if ((e = cudaFuncSetAttribute(gemv_sk_kernel<W, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem)) != cudaSuccess) return e;
+    L2_SK_ATTR(4, 1) L2_SK_ATTR(2, 1) L2_SK_ATTR(1, 1) L2_SK_ATTR(4, 2) L2_SK_ATTR(2, 2) L2_SK_ATTR(1, 2)
+#undef L2_SK_ATTR
+    return cudaSuccess;
+}
+
+}  // namespace l2

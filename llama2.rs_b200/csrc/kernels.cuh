@@ -24,30 +24,44 @@ struct Ctl {
 
 enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
 
-constexpr int GEMV_THREADS = 256;
-constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr int GEMV_R = 4;  // output rows a warp accumulates at once (x registers are shared by them)
+constexpr int SK_THREADS = 512;            // one CTA per SM
+constexpr int SK_WARPS = SK_THREADS / 32;
+constexpr int SK_MAX_SLOTS = 8;            // ring slots per warp (upper bound)
 
-// One fused dequant+GEMV problem: out = W x for a 4-bit act-order QLinear in device layout.
-// The input vector is already in the layer's permuted K order (the producer scatters it).
-struct GemvJob {
-    const uint4* qw;  const float* sc;  const uint32_t* zr;   // matrix A
-    const uint4* qw2; const float* sc2; const uint32_t* zr2;  // matrix B (w3 of the SwiGLU pair) or null
-    const float* x;   const float* nw;   // A's input in A's K order; rmsnorm weight in the same order or null
-    const float* x2;  const float* nw2;  // B's input / norm weight in B's K order
-    float* out;                          // STORE/SWIGLU: result vector; RESID: residual stream, natural order
-    float* sdst[3];                      // RESID: copies of the new residual value ...
-    const int* sidx[3];                  // ... written at these positions (inverse act-order permutations)
-    int rows, in, gp, gshift;            // gshift = log2(group_size / 32)
-    int cta0, ncta;                      // CTAs [cta0, cta0+ncta) of the launch work on this job
-    int epi, nscatter;
-    int ks;                              // warps that split K of one row block (power of two <= 8)
+// One 4-bit matrix in device layout (see repack.cpp) with its input vector.
+struct SkSeg {
+    const uint32_t* qw;   // [tile][group][2][32][W]
+    const uint32_t* meta; // [tile][group][20]: 16 f32 scales, 2 zero-nibble words, 2 pad
+    const float* x;       // input in this matrix's K order (the producer scatters it)
+    const float* nw;      // rmsnorm weight in the same order, or null
 };
 
-struct GemvParams {
-    GemvJob job[3];
+// One fused dequant+GEMV problem of a launch.  nseg == 2 pairs w1 with w3 for SwiGLU.
+struct SkJob {
+    SkSeg seg[2];
+    float* out;            // STORE/SWIGLU: result vector; RESID: residual stream, natural order
+    float* sdst[3];        // RESID: copies of the new residual value ...
+    const int* sidx[3];    // ... written at these positions (inverse act-order permutations)
+    int rows, tiles, in, G;
+    int cta0, ncta;        // CTAs [cta0, cta0+ncta) of the launch work on this job
+    int tq, trem;          // tiles / ncta and tiles % ncta
+    float rGs;             // 1 / (nseg * G)
+    int epi, nscatter;
+};
+
+struct alignas(16) SkParams {
+    SkJob job[3];
     int njobs;
     float eps;
+    // weights of the kernel that runs after this one: fetched into L2 while this one computes
+    const void* next_ptr[6];
+    size_t next_bytes[6];
+    size_t next_slice[6];   // bytes of each range one CTA asks for (multiple of 16)
+    int n_next;
+    unsigned long long* trace;  // debug: 8 clock stamps per CTA, or null
+    int* status;                // set non-zero when a bounded wait gives up, or null
+    int chunk, slots;           // units per ring slot, ring slots per warp
+    int ptiles;                 // tiles the per-CTA sum buffer holds
 };
 
 struct EmbedParams {
@@ -92,9 +106,12 @@ struct SelectParams {
 };
 
 void launch_embed(const EmbedParams& p, cudaStream_t st, bool pdl);
-void launch_gemv(const GemvParams& p, int grid, size_t smem, bool dual, cudaStream_t st, bool pdl);
-size_t gemv_smem_bytes(int in, bool dual);
-int gemv_ctas_per_sm(int in, bool dual);
+// `p` points to device memory: the kernel copies the record into shared memory with one cooperative load
+cudaError_t launch_sk(const SkParams* p, int group_size, int nseg, int grid, size_t smem, cudaStream_t st, bool pdl);
+size_t sk_smem_fixed(int in, int G, int nseg, int ptiles);  // digits, group sums, tile sums
+size_t sk_slot_bytes(int group_size, int chunk);           // one ring slot of one warp
+cudaError_t sk_init(int max_smem);
+extern unsigned long long* g_sk_trace;  // device buffer for SkParams::trace when tracing is on
 void launch_attn(const AttnParams& p, cudaStream_t st, bool pdl);
 void launch_cls(const ClsParams& p, int grid, cudaStream_t st, bool pdl);
 void launch_select(const SelectParams& p, cudaStream_t st, bool pdl);

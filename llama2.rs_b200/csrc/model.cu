@@ -30,17 +30,10 @@ static int dev_upload(T** p, const void* src, size_t count, std::vector<void*>& 
     return L2_OK;
 }
 
-static int ilog2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }
-
 int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vector<void*>& allocs, size_t* bytes) {
-    d.in = p.in; d.out = p.out; d.gp = p.gp;
-    d.gshift = ilog2((p.in / p.groups) / 32);
-    const int slabs = (p.in / 32 + 31) / 32;  // warp-wide 128-bit loads per row
-    d.ks = 1;
-    while (d.ks * 2 <= slabs && d.ks < GEMV_WARPS) d.ks *= 2;
-    if (int rc = dev_upload(&d.qw, p.qw.data(), p.qw.size() / 4, allocs, bytes)) return rc;
-    if (int rc = dev_upload(&d.sc, p.sc.data(), p.sc.size(), allocs, bytes)) return rc;
-    if (int rc = dev_upload(&d.zr, p.zr.data(), p.zr.size(), allocs, bytes)) return rc;
+    d.in = p.in; d.out = p.out; d.tiles = p.tiles; d.G = p.groups; d.gs = p.w * 32;
+    if (int rc = dev_upload(&d.qw, p.qw.data(), p.qw.size(), allocs, bytes)) return rc;
+    if (int rc = dev_upload(&d.meta, p.meta.data(), p.meta.size(), allocs, bytes)) return rc;
     if (g_index) {
         if (int rc = dev_upload(&d.perm, g_index, (size_t)p.in, allocs, bytes)) return rc;
         std::vector<int32_t> inv = inverse_permutation(g_index, p.in);
@@ -59,42 +52,78 @@ void launch_permute(const float* x, const int* perm, float* xp, int n, cudaStrea
     g_launches++;
 }
 
-static void fill_job(GemvJob& j, const DevQ& a, const float* x, const float* nw, float* out, int epi) {
-    j = GemvJob{};
-    j.qw = a.qw; j.sc = a.sc; j.zr = a.zr;
-    j.x = x; j.nw = nw; j.out = out;
-    j.rows = a.out; j.in = a.in; j.gp = a.gp; j.gshift = a.gshift; j.ks = a.ks;
-    j.epi = epi;
+void sk_set_matrix(SkJob& j, int seg, const DevQ& q, const float* x, const float* nw) {
+    j.seg[seg].qw = q.qw; j.seg[seg].meta = q.meta;
+    j.seg[seg].x = x; j.seg[seg].nw = nw;
+    j.rows = q.out; j.tiles = q.tiles; j.in = q.in; j.G = q.G;
 }
 
-// Splits `grid` CTAs over the jobs in proportion to their rows (all jobs of a launch share IN).
-static void split_ctas(GemvParams& p, int grid) {
+// Deals the CTAs of a launch to its jobs in proportion to their tiles (every CTA owns whole tiles;
+// inside a job the first tiles % ncta CTAs own one tile more) and sizes the shared memory.
+int sk_plan(SkLaunch& L, int sms) {
+    SkParams& p = L.p;
     long long total = 0;
-    for (int i = 0; i < p.njobs; i++) total += p.job[i].rows;
-    int used = 0;
+    for (int i = 0; i < p.njobs; i++) total += p.job[i].tiles;
+    const int want = (int)std::min<long long>(sms, total);
+    int used = 0, ptiles = 1, max_g = 0;
     for (int i = 0; i < p.njobs; i++) {
-        int n = i + 1 == p.njobs ? grid - used : (int)((long long)grid * p.job[i].rows / total);
-        if (n < 1) n = 1;
-        p.job[i].cta0 = used;
-        p.job[i].ncta = n;
-        used += n;
+        SkJob& j = p.job[i];
+        long long n = i + 1 == p.njobs ? want - used : (long long)want * j.tiles / total;
+        n = std::max<long long>(1, std::min<long long>(n, j.tiles));
+        j.cta0 = used;
+        j.ncta = (int)n;
+        used += (int)n;
+        j.tq = j.tiles / j.ncta;
+        j.trem = j.tiles % j.ncta;
+        j.rGs = 1.0f / (float)(L.nseg * j.G);
+        ptiles = std::max(ptiles, (j.tiles + j.ncta - 1) / j.ncta);
+        max_g = std::max(max_g, j.G);
     }
+    L.grid = used;
+    for (int i = 0; i < p.n_next; i++) p.next_slice[i] = ((p.next_bytes[i] / used) + 15) & ~(size_t)15;
+    // shared memory: digits, group sums and tile sums are fixed; the rest goes to the weight rings
+    const size_t fixed = (sk_smem_fixed(p.job[0].in, max_g, L.nseg, ptiles) + 127) & ~(size_t)127;
+    const size_t budget = 224 * 1024;
+    if (fixed >= budget) return fail(L2_EINVAL, "IN %d needs %zu bytes of shared memory before the weight rings", p.job[0].in, fixed);
+    // ring geometry: small chunks (refilled early), as many slots as fit, no more than a warp's range needs
+    const int chunk = L.gs == 128 ? 2 : 4;
+    const size_t per_warp = (budget - fixed) / SK_WARPS;
+    int slots = (int)std::min<size_t>(SK_MAX_SLOTS, per_warp / sk_slot_bytes(L.gs, chunk));
+    if (slots < 2) return fail(L2_EINVAL, "IN %d leaves no shared memory for the weight rings", p.job[0].in);
+    long long max_units = 0;
+    for (int i = 0; i < p.njobs; i++)
+        max_units = std::max<long long>(max_units, ((long long)((p.job[i].tiles + p.job[i].ncta - 1) / p.job[i].ncta) * L.nseg * p.job[i].G + SK_WARPS - 1) / SK_WARPS + 1);
+    const int needed = (int)((max_units + chunk - 1) / chunk) + 1;
+    slots = std::max(2, std::min(slots, needed));
+    p.chunk = chunk;
+    p.slots = slots;
+    p.ptiles = ptiles;
+    L.smem = fixed + (size_t)SK_WARPS * slots * sk_slot_bytes(L.gs, chunk);
+    return L2_OK;
 }
 
-static int gemv_grid(int sms, int in, bool dual, int njobs) {
-    int g = sms * gemv_ctas_per_sm(in, dual);
-    return g < njobs ? njobs : g;
+// Registers the weights of `q` as the next kernel's, to be fetched into L2 by launch L.
+void sk_prefetch_next(SkLaunch& L, const DevQ& q) {
+    SkParams& p = L.p;
+    if (p.n_next + 2 > 6) return;
+    p.next_ptr[p.n_next] = q.qw;
+    p.next_bytes[p.n_next++] = (size_t)q.tiles * q.G * (q.gs / 32) * 256;
+    p.next_ptr[p.n_next] = q.meta;
+    p.next_bytes[p.n_next++] = (size_t)q.tiles * q.G * 80;
 }
 
-int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, cudaStream_t st) {
-    GemvParams p{};
-    p.njobs = 1;
-    p.eps = 0.f;
-    fill_job(p.job[0], q, xp, nullptr, y, EPI_STORE);
-    const int grid = gemv_grid(sms, q.in, false, 1);
-    split_ctas(p, grid);
-    launch_gemv(p, grid, gemv_smem_bytes(q.in, false), false, st, false);
-    L2_CUDA(cudaGetLastError());
+int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, SkParams* d_plan, cudaStream_t st) {
+    SkLaunch L;
+    L.p.njobs = 1;
+    L.nseg = 1;
+    L.gs = q.gs;
+    sk_set_matrix(L.p.job[0], 0, q, xp, nullptr);
+    L.p.job[0].out = y;
+    L.p.job[0].epi = EPI_STORE;
+    if (int rc = sk_plan(L, sms)) return rc;
+    L.p.trace = g_sk_trace;
+    L2_CUDA(cudaMemcpyAsync(d_plan, &L.p, sizeof(SkParams), cudaMemcpyHostToDevice, st));  // pageable source: staged before return
+    L2_CUDA(launch_sk(d_plan, L.gs, 1, L.grid, L.smem, st, false));
     return L2_OK;
 }
 
@@ -196,10 +225,6 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
         if (int rc = load_q(T_W3, l, y.w3, gi2.data(), &gi)) return rc;
         if (int rc = permuted_norm(nw.data(), gi, &y.nw_3)) return rc;
     }
-    // warm the occupancy cache outside of any stream capture
-    gemv_grid(m->sms, D, false, 1);
-    gemv_grid(m->sms, D, true, 1);
-    gemv_grid(m->sms, c.hidden_dim, false, 1);
     m->decode_bytes = qbytes + (uint64_t)V * D * 4 + (uint64_t)(2 * L + 1) * D * 4;
     if (m->opt.debug) {
         printf("Configuration: Config { dim: %d, hidden_dim: %d, n_layers: %d, n_heads: %d, n_kv_heads: %d, vocab_size: %d, seq_len: %d, group_size: %d }\n",
@@ -225,20 +250,65 @@ static void set_scatter3(float** sdst, const int** sidx, int* n, l2_state* s, co
     *n = 3;
 }
 
-// rmsnorm + wq/wk/wv (src/models.rs:217-226)
-static void launch_qkv(l2_state* s, int l, cudaStream_t st, bool pdl) {
+// The four GEMV launches of a layer; each also prefetches the next GEMV's weights into L2.
+static int plan_layer_gemv(l2_state* s, int l, int which, SkLaunch& L) {
     l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
     const DevLayer& y = m->layers[l];
-    const int D = m->shape.c.dim;
-    GemvParams p{};
-    p.njobs = 3; p.eps = m->eps;
-    fill_job(p.job[0], y.wq, s->xq, y.nw_q, s->q, EPI_STORE);
-    fill_job(p.job[1], y.wk, s->xk, y.nw_k, s->k, EPI_STORE);
-    fill_job(p.job[2], y.wv, s->xv, y.nw_v, s->v, EPI_STORE);
-    const int grid = gemv_grid(m->sms, D, false, 3);
-    split_ctas(p, grid);
-    launch_gemv(p, grid, gemv_smem_bytes(D, false), false, st, pdl);
+    L = SkLaunch{};
+    L.gs = c.group_size;
+    L.p.eps = m->eps;
+    SkJob* j = L.p.job;
+    switch (which) {
+        case 0:  // rmsnorm + wq/wk/wv (src/models.rs:217-226)
+            L.p.njobs = 3;
+            sk_set_matrix(j[0], 0, y.wq, s->xq, y.nw_q); j[0].out = s->q; j[0].epi = EPI_STORE;
+            sk_set_matrix(j[1], 0, y.wk, s->xk, y.nw_k); j[1].out = s->k; j[1].epi = EPI_STORE;
+            sk_set_matrix(j[2], 0, y.wv, s->xv, y.nw_v); j[2].out = s->v; j[2].epi = EPI_STORE;
+            sk_prefetch_next(L, y.wo);
+            break;
+        case 1:  // wo + residual (:260-264); the new x goes to w1's and w3's K order as well
+            L.p.njobs = 1;
+            sk_set_matrix(j[0], 0, y.wo, s->att, nullptr); j[0].out = s->x; j[0].epi = EPI_RESID;
+            j[0].sdst[0] = s->x1; j[0].sidx[0] = y.w1.inv;
+            j[0].sdst[1] = s->x3; j[0].sidx[1] = y.w3.inv;
+            j[0].nscatter = 2;
+            sk_prefetch_next(L, y.w1);
+            sk_prefetch_next(L, y.w3);
+            break;
+        case 2:  // rmsnorm + w1/w3 + SwiGLU (:266-276); rows are in w2's K order
+            L.p.njobs = 1;
+            L.nseg = 2;
+            sk_set_matrix(j[0], 0, y.w1, s->x1, y.nw_1);
+            sk_set_matrix(j[0], 1, y.w3, s->x3, y.nw_3);
+            j[0].out = s->hb; j[0].epi = EPI_SWIGLU;
+            sk_prefetch_next(L, y.w2);
+            break;
+        default:  // w2 + residual (:279-285); the new x goes to the next layer's q/k/v K orders
+            L.p.njobs = 1;
+            sk_set_matrix(j[0], 0, y.w2, s->hb, nullptr); j[0].out = s->x; j[0].epi = EPI_RESID;
+            set_scatter3(j[0].sdst, j[0].sidx, &j[0].nscatter, s, l + 1 < c.n_layers ? &m->layers[l + 1] : nullptr);
+            if (l + 1 < c.n_layers) {
+                sk_prefetch_next(L, m->layers[l + 1].wq);
+                sk_prefetch_next(L, m->layers[l + 1].wk);
+                sk_prefetch_next(L, m->layers[l + 1].wv);
+            }
+            break;
+    }
+    if (m->opt.flags & L2_FLAG_NO_L2_PREFETCH) L.p.n_next = 0;
+    L.p.trace = g_sk_trace;
+    L.p.status = &s->ctl->status;
+    return sk_plan(L, m->sms);
 }
+
+static void launch_layer_gemv(l2_state* s, int l, int which, cudaStream_t st, bool pdl) {
+    const SkLaunch& L = s->plans[(size_t)l * 4 + which];
+    launch_sk(s->d_plans + (size_t)l * 4 + which, L.gs, L.nseg, L.grid, L.smem, st, pdl);
+}
+static void launch_qkv(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_layer_gemv(s, l, 0, st, pdl); }
+static void launch_wo(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_layer_gemv(s, l, 1, st, pdl); }
+static void launch_w13(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_layer_gemv(s, l, 2, st, pdl); }
+static void launch_w2(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_layer_gemv(s, l, 3, st, pdl); }
 
 // rope + cache append + attention (src/models.rs:228-256)
 static void launch_attention(l2_state* s, int l, cudaStream_t st, bool pdl) {
@@ -256,51 +326,6 @@ static void launch_attention(l2_state* s, int l, cudaStream_t st, bool pdl) {
     a.max_split = s->max_split; a.split_min = 64;
     a.pos_fixed = -1;
     launch_attn(a, st, pdl);
-}
-
-// wo + residual (src/models.rs:260-264); the new x goes to w1's and w3's K order as well
-static void launch_wo(l2_state* s, int l, cudaStream_t st, bool pdl) {
-    l2_model* m = s->m;
-    const DevLayer& y = m->layers[l];
-    const int D = m->shape.c.dim;
-    GemvParams p{};
-    p.njobs = 1; p.eps = m->eps;
-    fill_job(p.job[0], y.wo, s->att, nullptr, s->x, EPI_RESID);
-    p.job[0].sdst[0] = s->x1; p.job[0].sidx[0] = y.w1.inv;
-    p.job[0].sdst[1] = s->x3; p.job[0].sidx[1] = y.w3.inv;
-    p.job[0].nscatter = 2;
-    const int grid = gemv_grid(m->sms, D, false, 1);
-    split_ctas(p, grid);
-    launch_gemv(p, grid, gemv_smem_bytes(D, false), false, st, pdl);
-}
-
-// rmsnorm + w1/w3 + SwiGLU (src/models.rs:266-276)
-static void launch_w13(l2_state* s, int l, cudaStream_t st, bool pdl) {
-    l2_model* m = s->m;
-    const DevLayer& y = m->layers[l];
-    const int D = m->shape.c.dim;
-    GemvParams p{};
-    p.njobs = 1; p.eps = m->eps;
-    fill_job(p.job[0], y.w1, s->x1, y.nw_1, s->hb, EPI_SWIGLU);
-    p.job[0].qw2 = y.w3.qw; p.job[0].sc2 = y.w3.sc; p.job[0].zr2 = y.w3.zr;
-    p.job[0].x2 = s->x3; p.job[0].nw2 = y.nw_3;
-    const int grid = gemv_grid(m->sms, D, true, 1);
-    split_ctas(p, grid);
-    launch_gemv(p, grid, gemv_smem_bytes(D, true), true, st, pdl);
-}
-
-// w2 + residual (src/models.rs:279-285); the new x goes to the next layer's q/k/v K orders
-static void launch_w2(l2_state* s, int l, cudaStream_t st, bool pdl) {
-    l2_model* m = s->m;
-    const l2_config& c = m->shape.c;
-    const DevLayer& y = m->layers[l];
-    GemvParams p{};
-    p.njobs = 1; p.eps = m->eps;
-    fill_job(p.job[0], y.w2, s->hb, nullptr, s->x, EPI_RESID);
-    set_scatter3(p.job[0].sdst, p.job[0].sidx, &p.job[0].nscatter, s, l + 1 < c.n_layers ? &m->layers[l + 1] : nullptr);
-    const int grid = gemv_grid(m->sms, c.hidden_dim, false, 1);
-    split_ctas(p, grid);
-    launch_gemv(p, grid, gemv_smem_bytes(c.hidden_dim, false), false, st, pdl);
 }
 
 static void launch_classifier(l2_state* s, cudaStream_t st, bool pdl) {
@@ -540,6 +565,21 @@ extern "C" int l2_state_new(l2_model* m, l2_state** out) {
         free_allocs(s->allocs);
         return rc;
     }
+    {   // plan the four GEMV launches of every layer once and keep their records on the device
+        const int L = c.n_layers;
+        s->plans.resize((size_t)L * 4);
+        std::vector<SkParams> host((size_t)L * 4);
+        if ((rc = dev_alloc(reinterpret_cast<void**>(&s->d_plans), sizeof(SkParams) * L * 4, s->allocs))) { free_allocs(s->allocs); return rc; }
+        for (int l = 0; l < L; l++)
+            for (int which = 0; which < 4; which++) {
+                if ((rc = plan_layer_gemv(s.get(), l, which, s->plans[(size_t)l * 4 + which]))) { free_allocs(s->allocs); return rc; }
+                host[(size_t)l * 4 + which] = s->plans[(size_t)l * 4 + which].p;
+            }
+        if (cudaMemcpy(s->d_plans, host.data(), sizeof(SkParams) * host.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
+            free_allocs(s->allocs);
+            return fail(L2_ECUDA, "uploading the launch records failed");
+        }
+    }
     if (cudaMallocHost(reinterpret_cast<void**>(&s->h_ctl), sizeof(Ctl) * CTL_RING) != cudaSuccess) {
         free_allocs(s->allocs);
         return fail(L2_ECUDA, "cudaMallocHost failed");
@@ -767,6 +807,20 @@ extern "C" int l2_bench_projection(l2_model* m, l2_state* s, int which, int laye
     return L2_OK;
 }
 
+// Debug: turns on per-CTA clock stamps in the GEMV kernels (n_ctas * 8 values: kernel entry, loads
+// issued, dependency wait over, digits staged, main loop done, barrier passed, exit) or reads them back.
+extern "C" int l2_debug_trace(int enable, unsigned long long* host_out, int n_ctas) {
+    if (enable && !g_sk_trace) {
+        L2_CUDA(cudaMalloc(&g_sk_trace, sizeof(unsigned long long) * 8 * 1024));
+        L2_CUDA(cudaMemset(g_sk_trace, 0, sizeof(unsigned long long) * 8 * 1024));
+    }
+    if (host_out && g_sk_trace) {
+        L2_CUDA(cudaDeviceSynchronize());
+        L2_CUDA(cudaMemcpy(host_out, g_sk_trace, sizeof(unsigned long long) * 8 * std::min(n_ctas, 1024), cudaMemcpyDeviceToHost));
+    }
+    return L2_OK;
+}
+
 // Algorithmic bytes one launch of l2_bench_projection's kernel streams: the checkpoint's
 // qweight + qzeros + scales of the projection(s), or the f32 classifier matrix.
 extern "C" uint64_t l2_projection_bytes(const l2_model* m, int which) {
@@ -857,6 +911,7 @@ extern "C" int l2_qlinear_create(int in, int out, int group_size, const int32_t*
     PackedQ p;
     repack_qlinear(in, out, group_size, qweight, qzeros, scales, nullptr, p);
     if (int rc = upload_qlinear(p, g_index, q->q, q->allocs, nullptr)) { free_allocs(q->allocs); return rc; }
+    if (int rc = dev_alloc(reinterpret_cast<void**>(&q->d_plan), sizeof(SkParams), q->allocs)) { free_allocs(q->allocs); return rc; }
     L2_CUDA(cudaStreamCreateWithFlags(&q->stream, cudaStreamNonBlocking));
     *h = q.release();
     return L2_OK;
@@ -880,7 +935,7 @@ extern "C" int l2_qlinear_matvec_dev(l2_qlinear* h, const float* x_dev, float* x
     if (int rc = qlinear_reserve(h, B)) return rc;
     for (int b = 0; b < B; b++) {
         launch_permute(x_dev + (size_t)b * h->q.in, h->q.perm, h->xp_dev + (size_t)b * h->q.in, h->q.in, st);
-        if (int rc = run_gemv_single(h->q, h->xp_dev + (size_t)b * h->q.in, xout_dev + (size_t)b * h->q.out, h->sms, st)) return rc;
+        if (int rc = run_gemv_single(h->q, h->xp_dev + (size_t)b * h->q.in, xout_dev + (size_t)b * h->q.out, h->sms, h->d_plan, st)) return rc;
     }
     return L2_OK;
 }

@@ -21,12 +21,18 @@ namespace l2 {
 
 // One QLinear in device layout (see repack.cpp) plus what its producers/consumers need.
 struct DevQ {
-    uint4* qw = nullptr;
-    float* sc = nullptr;
-    uint32_t* zr = nullptr;
+    uint32_t* qw = nullptr;    // [tiles][G][2][32][W]
+    uint32_t* meta = nullptr;  // [tiles][G][20]: scales, zero nibbles, padding
     int* perm = nullptr;  // g_index: permuted position j reads input perm[j]
     int* inv = nullptr;   // inverse: input o is written to permuted position inv[o]
-    int in = 0, out = 0, gp = 0, gshift = 0, ks = 1;
+    int in = 0, out = 0, tiles = 0, G = 0, gs = 0;
+};
+
+// A planned GEMV launch: parameters, grid and shared memory.
+struct SkLaunch {
+    SkParams p{};
+    int grid = 0, nseg = 1, gs = 128;
+    size_t smem = 0;
 };
 
 struct DevLayer {
@@ -75,6 +81,8 @@ struct l2_state {
     int* prompt = nullptr;
     int* out_tokens = nullptr;
     int max_split = 1;
+    std::vector<l2::SkLaunch> plans;     // [layer][4] GEMV launches, planned once
+    l2::SkParams* d_plans = nullptr;     // their parameter records on the device
     cudaGraphExec_t graphs[l2::G_COUNT] = {nullptr, nullptr, nullptr, nullptr};
     int graph_nodes[l2::G_COUNT] = {0, 0, 0, 0};
     std::vector<void*> allocs;
@@ -86,6 +94,7 @@ struct l2_qlinear {
     int sms = 148;
     int group_size = 128;
     float *x_dev = nullptr, *xp_dev = nullptr, *y_dev = nullptr;
+    l2::SkParams* d_plan = nullptr;
     int cap_b = 0;
     cudaStream_t stream = nullptr;
     std::vector<void*> allocs;
@@ -96,5 +105,8 @@ int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vecto
 void launch_permute(const float* x, const int* perm, float* xp, int n, cudaStream_t st);
 int check_attention_args(int n_heads, int n_kv_heads, int pos, const void* q, const void* k, const void* v, const void* kc,
                          const void* vc, const void* rc, const void* rs, const void* out);
-int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, cudaStream_t st);
+int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, SkParams* d_plan, cudaStream_t st);
+int sk_plan(SkLaunch& L, int sms);
+void sk_prefetch_next(SkLaunch& L, const DevQ& q);
+void sk_set_matrix(SkJob& j, int seg, const DevQ& q, const float* x, const float* nw);
 }  // namespace l2

@@ -8,14 +8,18 @@
 
 namespace l2 {
 
+// Device layout of one QLinear (IN, OUT, GS): the matrix is cut into tiles of 16 output rows and
+// units of (tile, group).  W = GS/32 is the number of 32-bit weight words a lane holds per row.
 struct PackedQ {
-    int in = 0, out = 0, groups = 0, gp = 0;
-    std::vector<uint32_t> qw;  // [OUT][IN/8]
-    std::vector<float> sc;     // [OUT][gp]
-    std::vector<uint32_t> zr;  // [OUT/8][gp]
+    int in = 0, out = 0, groups = 0, tiles = 0, w = 0;
+    std::vector<uint32_t> qw;  // [tiles][groups][2][32][W]: half h, lane L=(r,t): words t*W..t*W+W-1 of row 16*tile+8h+r in the group
+    // [tiles][groups][20] words: 16 f32 scales (row 16*tile+i), 2 zero words (nibble r of word h is
+    // the zero nibble of row 16*tile+8h+r), 2 words of padding: 80 bytes, a multiple of 16
+    std::vector<uint32_t> meta;
 };
 
-// rows_order[j] = checkpoint row that becomes device row j (NULL = identity).
+// rows_order[j] = checkpoint row that becomes device row j (NULL = identity).  Rows beyond OUT in
+// the last tile are zero (weights, scales and zero nibbles), so they contribute nothing.
 void repack_qlinear(int in, int out, int gs, const int32_t* qweight, const int32_t* qzeros,
                     const float* scales, const int32_t* rows_order, PackedQ& dst);
 std::vector<int32_t> inverse_permutation(const int32_t* perm, int n);

@@ -76,6 +76,7 @@ SIGNATURES = {
     "l2_attention_decode_noalloc": (C.c_int, [C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "l2_bench_projection": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int]),
     "l2_projection_bytes": (C.c_uint64, [_vp, C.c_int]),
+    "l2_debug_trace": (C.c_int, [C.c_int, _p(C.c_uint64), C.c_int]),
     "l2_random_u32": (C.c_uint32, [_u64p]),
     "l2_random_f32": (C.c_float, [_u64p]),
     "l2_tokenizer_open": (C.c_int, [C.c_char_p, C.c_int, _p(_vp)]),
@@ -84,7 +85,7 @@ SIGNATURES = {
     "l2_tokenizer_vocab": (C.c_char_p, [_vp, C.c_int32]),
     "l2_tokenizer_piece": (C.c_char_p, [_vp, C.c_int32, C.c_int32]),
     "l2_debug_repack": (C.c_int, [C.c_int, C.c_int, C.c_int, _i32p, _i32p, _f32p, _i32p,
-                                  _p(_p(C.c_uint32)), _p(_f32p), _p(_p(C.c_uint32)), _p(C.c_int)]),
+                                  _p(_p(C.c_uint32)), _p(_p(C.c_uint32)), _p(C.c_int)]),
     "l2_host_free": (None, [_vp]),
 }
 for _name, (_res, _args) in SIGNATURES.items():
@@ -106,3 +107,4 @@ def as_i32p(a):
 
 def as_f32p(a):
     return a.ctypes.data_as(_f32p)
+FLAG_NO_L2_PREFETCH = 4

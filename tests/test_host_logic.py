@@ -20,16 +20,28 @@ def test_every_declared_symbol_is_exported(l2):
     assert declared == set(l2._lib.SIGNATURES), declared ^ set(l2._lib.SIGNATURES)
 
 
-def emulate_device_gemv(qw, sc, zr, gp, in_f, out_f, gs, x_perm):
-    """numpy model of the kernel's view of the device layout: y[o] = sum_g scale * sum_k (q - z) x."""
+def emulate_device_gemv(qw, meta, tiles, in_f, out_f, gs, x_perm):
+    """numpy model of the kernel's view of the device layout (tiles of 16 rows, units of one group):
+    y[o] = sum_g scale * sum_k (q - z) x."""
+    G, W = in_f // gs, gs // 32
+    qw = qw.reshape(tiles, G, 2, 32, W)
+    meta = meta.reshape(tiles, G, 20)
+    sc = meta[:, :, :16].copy().view(np.float32)
+    zr = meta[:, :, 16:18]
+    assert not meta[:, :, 18:].any()
     y = np.zeros(out_f)
-    nib = np.stack([(qw.reshape(out_f, in_f // 8) >> np.uint32(4 * j)) & 15 for j in range(8)], axis=2).reshape(out_f, in_f)
     for o in range(out_f):
-        zw = zr.reshape(out_f // 8, gp)[o // 8]
-        z = ((zw >> np.uint32(4 * (o % 8))) & 15).astype(np.int64) + 1
-        for g in range(in_f // gs):
-            q = nib[o, g * gs:(g + 1) * gs].astype(np.int64)
-            y[o] += float(sc.reshape(out_f, gp)[o, g]) * float(((q - z[g]) * x_perm[g * gs:(g + 1) * gs].astype(np.float64)).sum())
+        tile, h, r = o // 16, (o % 16) // 8, o % 8
+        for g in range(G):
+            z = int((zr[tile, g, h] >> np.uint32(4 * r)) & 15) + 1
+            acc = 0.0
+            for t in range(4):
+                for i in range(W):
+                    word = int(qw[tile, g, h, r * 4 + t, i])
+                    k0 = g * gs + (t * W + i) * 8
+                    for j in range(8):
+                        acc += (((word >> (4 * j)) & 15) - z) * float(x_perm[k0 + j])
+            y[o] += float(sc[tile, g, o % 16]) * acc
     return y
 
 
@@ -39,36 +51,34 @@ def test_repack_is_exact(l2, orc, gs, in_f, out_f):
     qweight, qzeros, scales, g_index = random_qlinear(rng, in_f, out_f, gs)
     order = rng.permutation(out_f).astype(np.int32)
     for rows in (None, order):
-        pq, ps, pz = C.POINTER(C.c_uint32)(), C.POINTER(C.c_float)(), C.POINTER(C.c_uint32)()
-        gp = C.c_int(0)
+        pq, pm = C.POINTER(C.c_uint32)(), C.POINTER(C.c_uint32)()
+        tiles = C.c_int(0)
         l2.check(l2.lib.l2_debug_repack(in_f, out_f, gs, l2._lib.as_i32p(qweight), l2._lib.as_i32p(qzeros), l2._lib.as_f32p(scales),
                                         l2._lib.as_i32p(rows) if rows is not None else None,
-                                        C.byref(pq), C.byref(ps), C.byref(pz), C.byref(gp)))
+                                        C.byref(pq), C.byref(pm), C.byref(tiles)))
         g = in_f // gs
-        assert gp.value % 4 == 0 and gp.value >= g
-        qw = np.ctypeslib.as_array(pq, shape=(out_f * in_f // 8,)).copy()
-        sc = np.ctypeslib.as_array(ps, shape=(out_f * gp.value,)).copy()
-        zr = np.ctypeslib.as_array(pz, shape=(out_f // 8 * gp.value,)).copy()
-        for p in (pq, ps, pz):
+        assert tiles.value == (out_f + 15) // 16
+        qw = np.ctypeslib.as_array(pq, shape=(tiles.value * g * 64 * (gs // 32),)).copy()
+        meta = np.ctypeslib.as_array(pm, shape=(tiles.value * g * 20,)).copy()
+        for p in (pq, pm):
             l2.lib.l2_host_free(p)
         x = rng.standard_normal(in_f).astype(np.float32)
-        y = emulate_device_gemv(qw, sc, zr, gp.value, in_f, out_f, gs, x[g_index])
+        y = emulate_device_gemv(qw, meta, tiles.value, in_f, out_f, gs, x[g_index])
         want = orc.qlinear_matvec(qweight, qzeros, scales, g_index, gs, x).astype(np.float64)
         if rows is not None:
             want = want[rows]
         np.testing.assert_allclose(y, want, rtol=2e-5, atol=2e-5)
-        # the nibbles themselves are carried over bit for bit
-        src_rows = rows if rows is not None else np.arange(out_f)
-        assert np.array_equal(qw.reshape(out_f, -1), qweight.view(np.uint32)[src_rows])
+        # the nibbles are carried over bit for bit: the multiset of words is unchanged, padding rows are zero
+        assert np.array_equal(np.sort(qw[qw != 0]), np.sort(qweight.view(np.uint32)[qweight.view(np.uint32) != 0]))
 
 
 def test_repack_rejects_bad_arguments(l2):
     rng = np.random.default_rng(0)
     qweight, qzeros, scales, g_index = random_qlinear(rng, 64, 8, 32)
     bad = np.zeros(8, np.int32)
-    pq, ps, pz, gp = C.POINTER(C.c_uint32)(), C.POINTER(C.c_float)(), C.POINTER(C.c_uint32)(), C.c_int(0)
+    pq, pm, gp = C.POINTER(C.c_uint32)(), C.POINTER(C.c_uint32)(), C.c_int(0)
     rc = l2.lib.l2_debug_repack(64, 8, 32, l2._lib.as_i32p(qweight), l2._lib.as_i32p(qzeros), l2._lib.as_f32p(scales),
-                                l2._lib.as_i32p(bad), C.byref(pq), C.byref(ps), C.byref(pz), C.byref(gp))
+                                l2._lib.as_i32p(bad), C.byref(pq), C.byref(pm), C.byref(gp))
     assert rc == -1 and b"permutation" in l2.lib.l2_last_error()
 
 
