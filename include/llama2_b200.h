@@ -207,13 +207,13 @@ const char* l2_tokenizer_vocab(const l2_tokenizer* t, int32_t id);
 const char* l2_tokenizer_piece(const l2_tokenizer* t, int32_t prev, int32_t next);
 
 /* ---- host-side repack, exposed so that it can be checked without a GPU --------------- */
-/* Device layout of one QLinear as built at load time (tiles of 16 rows, units of one group):
- * qw [tiles][groups][2][32][GS/32] u32 and meta [tiles][groups][20] u32 (16 f32 scales, 2 words of
- * zero nibbles, 2 words of padding).  Returns malloc'ed arrays the caller frees with
- * l2_host_free.  rows_order (NULL or [OUT]) re-orders output rows. */
+/* Device layout of one QLinear as built at load time: [tiles][groups] unit records of unit_words
+ * 32-bit words each (tiles of 16 rows, one quantisation group): 2*32*(GS/32) weight words in lane
+ * order, 16 f32 scales, 2 words of zero nibbles, 2 words of padding.  Returns a malloc'ed array the
+ * caller frees with l2_host_free.  rows_order (NULL or [OUT]) re-orders output rows. */
 int l2_debug_repack(int in, int out, int group_size, const int32_t* qweight, const int32_t* qzeros,
-                    const float* scales, const int32_t* rows_order, uint32_t** qw_dev, uint32_t** meta_dev,
-                    int* tiles);
+                    const float* scales, const int32_t* rows_order, uint32_t** rec_dev, int* tiles,
+                    int* unit_words);
 void l2_host_free(void* p);
 
 #ifdef __cplusplus

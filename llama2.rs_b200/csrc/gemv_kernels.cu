@@ -64,8 +64,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Waits for a phase of the barrier, but never forever: after SK_WAIT_LIMIT polls it gives up and
 // reports failure (the caller records it in the status word and stops using the data).
 constexpr uint32_t SK_WAIT_LIMIT = 1u << 24;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SK_WAIT_LIMIT; i++)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = SK_WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; i++)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
@@ -75,6 +75,9 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// barrier of the SK_THREADS consumer threads only (the producer warp runs on its own)
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SK_THREADS) : "memory"); }
+
 __device__ __forceinline__ float block_reduce_2(float& mx, float sq, float* red /* 2*SK_WARPS+2 floats */) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
@@ -83,7 +86,7 @@ __device__ __forceinline__ float block_reduce_2(float& mx, float sq, float* red 
         sq += __shfl_xor_sync(0xffffffffu, sq, o);
     }
     if (lane == 0) { red[warp] = mx; red[SK_WARPS + warp] = sq; }
-    __syncthreads();
+    consumer_sync();
     if (warp == 0) {
         float m = lane < SK_WARPS ? red[lane] : 0.f;
         float s = lane < SK_WARPS ? red[SK_WARPS + lane] : 0.f;
@@ -94,10 +97,10 @@ __device__ __forceinline__ float block_reduce_2(float& mx, float sq, float* red 
         }
         if (lane == 0) { red[2 * SK_WARPS] = m; red[2 * SK_WARPS + 1] = s; }
     }
-    __syncthreads();
+    consumer_sync();
     mx = red[2 * SK_WARPS];
     const float total = red[2 * SK_WARPS + 1];
-    __syncthreads();
+    consumer_sync();
     return total;
 }
 
@@ -226,13 +229,14 @@ __device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
 }
 
 template <int W, int NSEG>
-__global__ void __launch_bounds__(SK_THREADS, 1) gemv_sk_kernel(const SkParams* __restrict__ gp) {
+__global__ void __launch_bounds__(SK_THREADS + 32, 1) gemv_sk_kernel(const SkParams* __restrict__ gp) {
     constexpr int GS = 32 * W;
     constexpr int ROWS = 16 * NSEG;  // rows of a (super) tile
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ float red[2 * SK_WARPS + 2];
     __shared__ float oscale[2];
-    __shared__ __align__(8) uint64_t bars[SK_WARPS * SK_MAX_SLOTS];
+    __shared__ __align__(8) uint64_t full[SK_MAX_SLOTS], empty[SK_MAX_SLOTS];
+    __shared__ volatile int abort_flag;
     __shared__ SkParams sp;
 
     // The launch record lives in global memory: one cooperative 128-bit load per thread brings it into
@@ -257,58 +261,69 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemv_sk_kernel(const SkParams* 
     const int nt = J.tq + (cta < J.trem ? 1 : 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = nt * Gs;                      // units of this CTA
-    const int wa = n * warp / SK_WARPS, wb = n * (warp + 1) / SK_WARPS;  // this warp's units, relative to the CTA's first
-    // position of the warp's first unit: tile, segment, group (division by reciprocal, corrected)
-    int w_tl = (int)((float)wa * J.rGs);
-    if (w_tl * Gs > wa) w_tl--; else if ((w_tl + 1) * Gs <= wa) w_tl++;
-    int w_seg = 0, w_g = wa - w_tl * Gs;
-    if (NSEG == 2 && w_g >= G) { w_seg = 1; w_g -= G; }
 
     // shared memory carve-up
     const int dstride = J.in + 16;
     uint8_t* digits = smem;                                              // [NSEG][4][in + 16]
     int* ss = reinterpret_cast<int*>(smem + (size_t)NSEG * 4 * dstride);  // [NSEG][G][2]
     float* partial = reinterpret_cast<float*>(ss + NSEG * G * 2);        // [ptiles][SK_WARPS][ROWS]
-    const int CH = P.chunk, NS = P.slots;
-    const uint32_t slot_bytes = (uint32_t)CH * (256u * W + 80u);
+    constexpr uint32_t UB = 256u * W + 80u;  // bytes of one unit record
+    const int SU = P.chunk, NS = P.slots;    // units per ring slot, ring slots
+    const uint32_t slot_bytes = (uint32_t)SU * UB;
     const size_t fixed_bytes = ((size_t)NSEG * 4 * dstride + (size_t)NSEG * G * 8 + (size_t)P.ptiles * SK_WARPS * ROWS * 4 + 127) & ~(size_t)127;
-    uint8_t* ring = smem + fixed_bytes + (size_t)warp * NS * slot_bytes;  // 128-byte aligned (bulk copies need 16)
-    uint64_t* bar = bars + warp * SK_MAX_SLOTS;
+    uint8_t* ring = smem + fixed_bytes;      // 128-byte aligned (bulk copies need 16)
+    const int nslots = (n + SU - 1) / SU;    // slot fills this CTA goes through
 
-    // ---- weight stream of this warp: chunks of up to CH units that stay inside one (tile, segment)
-    // run, copied into the ring slots round-robin.  Independent of the previous kernel: start now.
-    struct ChunkIt { int u, tl, seg, g; };
-    auto chunk_len = [&](const ChunkIt& it) { return min(min(CH, wb - it.u), G - it.g); };
-    auto advance = [&](ChunkIt& it, int len) {
-        it.u += len;
-        it.g += len;
-        if (it.g == G) { it.g = 0; if (++it.seg == NSEG) { it.seg = 0; it.tl++; } }
-    };
-    auto issue = [&](int slot, const ChunkIt& it, int len) {  // lane 0 only
-        const SkSeg& S = J.seg[NSEG == 1 ? 0 : it.seg];
-        const size_t mu = (size_t)(tau_first + it.tl) * G + it.g;
-        const uint32_t bw = (uint32_t)len * 256u * W, bm = (uint32_t)len * 80u;
-        uint8_t* dst = ring + (size_t)slot * slot_bytes;
-        mbar_expect_tx(bar + slot, bw + bm);
-        bulk_g2s(dst, S.qw + mu * (64 * W), bw, bar + slot);
-        bulk_g2s(dst + (size_t)CH * 256 * W, S.meta + mu * 20, bm, bar + slot);
-    };
-    ChunkIt prod{wa, w_tl, w_seg, w_g}, cons = prod;
-    if (lane == 0) {
-        for (int i = 0; i < NS; i++) mbar_init(bar + i, 1);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS; i++) { mbar_init(full + i, 1); mbar_init(empty + i, SK_WARPS); }
+        abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int i = 0; i < NS && prod.u < wb; i++) {
-            const int len = chunk_len(prod);
-            issue(i, prod, len);
-            advance(prod, len);
+    }
+    __syncthreads();
+
+    // ================= producer warp: streams the CTA's units through the ring ===================
+    // Slot fill k holds units [k*SU, min((k+1)*SU, n)) of the CTA's range.  Units are contiguous in
+    // memory inside one (tile, segment) run, and from tile to tile when there is a single segment, so
+    // a fill is one large bulk copy (or one per run it touches).  Large copies matter: the copy
+    // engine spends a fixed time per request.  The first fills do not depend on the previous kernel
+    // and are issued before the dependency wait.
+    if (warp == SK_WARPS) {
+        if (lane == 0) {
+            // the next kernel's weights: every CTA asks the L2 for an equal slice of each range
+            for (int i = 0; i < P.n_next; i++) {
+                const size_t per = P.next_slice[i], off = per * blockIdx.x;
+                if (off < P.next_bytes[i]) prefetch_l2(static_cast<const char*>(P.next_ptr[i]) + off, (uint32_t)min(per, P.next_bytes[i] - off));
+            }
+            int tl = 0, seg = 0, g = 0;  // position of the next unit to copy
+            for (int k = 0; k < nslots; k++) {
+                const int slot = k % NS;
+                if (k >= NS && !mbar_wait(empty + slot, (uint32_t)(k / NS - 1) & 1u)) {
+                    if (P.status) atomicExch(P.status, 1002);
+                    abort_flag = 1;
+                    break;
+                }
+                if (abort_flag) break;
+                int left = min(SU, n - k * SU);
+                mbar_expect_tx(full + slot, (uint32_t)left * UB);
+                uint8_t* dst = ring + (size_t)slot * slot_bytes;
+                while (left > 0) {
+                    // NSEG == 1: consecutive tiles are consecutive in memory, one copy covers them all
+                    const int run = NSEG == 1 ? left : min(left, G - g);
+                    const SkSeg& S = J.seg[NSEG == 1 ? 0 : seg];
+                    const size_t mu = (size_t)(tau_first + tl) * G + g;
+                    bulk_g2s(dst, S.rec + mu * (UB / 4), (uint32_t)run * UB, full + slot);
+                    dst += (size_t)run * UB;
+                    left -= run;
+                    g += run;
+                    while (g >= G) { g -= G; if (++seg == NSEG) { seg = 0; tl++; } }
+                }
+            }
         }
+        grid_launch_dependents();
+        return;
     }
-    __syncwarp();
-    // the next kernel's weights: every CTA asks the L2 for an equal slice of each range
-    if (lane == 0 && warp < P.n_next) {
-        const size_t per = P.next_slice[warp], off = per * blockIdx.x;
-        if (off < P.next_bytes[warp]) prefetch_l2(static_cast<const char*>(P.next_ptr[warp]) + off, (uint32_t)min(per, P.next_bytes[warp] - off));
-    }
+
+    // ================= consumer warps ================================================================
     // epilogue operands of this warp's first tile that do not depend on the previous kernel
     const int e_row = (tau_first + warp) * 16 + (lane & 15);
     const bool e_pre = NSEG == 1 && warp < nt && lane < 16 && e_row < J.rows && J.epi == EPI_RESID;
@@ -333,16 +348,33 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemv_sk_kernel(const SkParams* 
             if (threadIdx.x == 0) oscale[s] = f;
         }
     }
-    __syncthreads();
+    consumer_sync();
 
     SK_STAMP(3);
-    // ---- main loop over this warp's chunks
+    // ---- main loop: in every slot fill this warp takes units 2*warp and 2*warp + 1 (+ 2*SK_WARPS ...)
     const int r = lane >> 2, t = lane & 3;
     float tot0 = 0.f, tot1 = 0.f;
+    int cur_tl = -1, cur_seg = 0;  // (tile, segment) the row sums belong to
     bool ok = true;
-    auto unit_finish = [&](const uint8_t* msl, int i, int seg, int g, const int (&c)[4]) {
+    auto flush = [&]() {
+        if (cur_tl >= 0) {
+            // lanes t = 0 hold digits 0,1 (weight 2^14 relative to digits 2,3 held by lanes t = 1)
+            float a = t == 0 ? tot0 * 16384.0f : tot0, b = t == 0 ? tot1 * 16384.0f : tot1;
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            b += __shfl_xor_sync(0xffffffffu, b, 1);
+            if (t == 0) {
+                float* dst = partial + ((size_t)cur_tl * SK_WARPS + warp) * ROWS + cur_seg * 16;
+                dst[r] = a;
+                dst[r + 8] = b;
+            }
+        }
+        tot0 = tot1 = 0.f;
+    };
+    // scale, zero point and digit sums of one finished unit (exact integers up to the final FMA)
+    auto unit_finish = [&](const uint8_t* rec, int tl, int seg, int g, const int (&c)[4]) {
+        if (tl != cur_tl || seg != cur_seg) { flush(); cur_tl = tl; cur_seg = seg; }  // warp-uniform
         if (t < 2) {
-            const uint32_t* mt = reinterpret_cast<const uint32_t*>(msl + (size_t)i * 80);
+            const uint32_t* mt = reinterpret_cast<const uint32_t*>(rec + 256 * W);
             const float s0 = __uint_as_float(mt[r]), s1 = __uint_as_float(mt[8 + r]);
             const int z0 = (int)((mt[16] >> (4 * r)) & 15u) + 1, z1 = (int)((mt[17] >> (4 * r)) & 15u) + 1;  // src/gptq.rs:148
             const int sv = ss[((NSEG == 1 ? 0 : seg) * G + g) * 2 + t];
@@ -350,89 +382,75 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemv_sk_kernel(const SkParams* 
             tot1 = fmaf(s1, (float)(c[2] * 128 + c[3] - z1 * sv), tot1);
         }
     };
-    for (int chunk_no = 0; cons.u < wb; chunk_no++) {
-        const int slot = chunk_no % NS;
-        const int len = chunk_len(cons);
-        if (ok && !mbar_wait(bar + slot, (uint32_t)(chunk_no / NS) & 1u)) {
+    constexpr uint32_t M = 0x0F0F0F0Fu;
+    // MMAs of one unit whose record starts at rec; dg points at this lane's digits of the unit's group
+    auto unit_mma = [&](const uint8_t* rec, const uint8_t* dg, int (&c)[4]) {
+        c[0] = c[1] = c[2] = c[3] = 0;
+        if constexpr (W == 4) {
+            const uint4 a = *reinterpret_cast<const uint4*>(rec + lane * 16), b = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
+            uint4 d0 = make_uint4(0, 0, 0, 0), d1 = d0;
+            if (r < 4) { d0 = reinterpret_cast<const uint4*>(dg)[0]; d1 = reinterpret_cast<const uint4*>(dg)[1]; }
+            mma_u8s8(c, a.x & M, b.x & M, (a.x >> 4) & M, (b.x >> 4) & M, d0.x, d0.y);
+            mma_u8s8(c, a.y & M, b.y & M, (a.y >> 4) & M, (b.y >> 4) & M, d0.z, d0.w);
+            mma_u8s8(c, a.z & M, b.z & M, (a.z >> 4) & M, (b.z >> 4) & M, d1.x, d1.y);
+            mma_u8s8(c, a.w & M, b.w & M, (a.w >> 4) & M, (b.w >> 4) & M, d1.z, d1.w);
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; j++) {
+                const uint32_t a = *reinterpret_cast<const uint32_t*>(rec + lane * 4 * W + 4 * j);
+                const uint32_t b = *reinterpret_cast<const uint32_t*>(rec + 128 * W + lane * 4 * W + 4 * j);
+                uint2 bb = make_uint2(0u, 0u);
+                if (r < 4) bb = *reinterpret_cast<const uint2*>(dg + 8 * j);
+                mma_u8s8(c, a & M, b & M, (a >> 4) & M, (b >> 4) & M, bb.x, bb.y);
+            }
+        }
+    };
+    auto locate = [&](int u, int& tl, int& seg, int& g) {  // unit index in the CTA -> tile, segment, group
+        tl = (int)((float)u * J.rGs);
+        if (tl * Gs > u) tl--; else if ((tl + 1) * Gs <= u) tl++;
+        g = u - tl * Gs;
+        seg = 0;
+        if (NSEG == 2 && g >= G) { seg = 1; g -= G; }
+    };
+    auto digits_of = [&](int seg, int g) {
+        return digits + (size_t)(NSEG == 1 ? 0 : seg) * 4 * dstride + (size_t)r * dstride + g * GS + t * (8 * W);
+    };
+    for (int k = 0; k < nslots; k++) {
+        const int slot = k % NS;
+        const int m = min(SU, n - k * SU);  // units in this fill
+        if (ok && (abort_flag || !mbar_wait(full + slot, (uint32_t)(k / NS) & 1u))) {
             ok = false;
             if (P.status) atomicExch(P.status, 1001);
+            abort_flag = 1;
         }
         ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            const uint8_t* wsl = ring + (size_t)slot * slot_bytes;
-            const uint8_t* msl = wsl + (size_t)CH * 256 * W;
-            if constexpr (W < 4) {  // smaller units: weights are 8 or 4 bytes per lane and row
-                for (int i = 0; i < len; i++) {
-                    int c[4] = {0, 0, 0, 0};
-                    const uint8_t* dg = digits + (size_t)(NSEG == 1 ? 0 : cons.seg) * 4 * dstride + (size_t)r * dstride + (cons.g + i) * GS + t * (8 * W);
-#pragma unroll
-                    for (int j = 0; j < W; j++) {
-                        const uint32_t a = *reinterpret_cast<const uint32_t*>(wsl + (size_t)i * 256 * W + lane * 4 * W + 4 * j);
-                        const uint32_t b = *reinterpret_cast<const uint32_t*>(wsl + (size_t)i * 256 * W + 128 * W + lane * 4 * W + 4 * j);
-                        uint2 bb = make_uint2(0u, 0u);
-                        if (r < 4) bb = *reinterpret_cast<const uint2*>(dg + 8 * j);
-                        mma_u8s8(c, a & 0x0F0F0F0Fu, b & 0x0F0F0F0Fu, (a >> 4) & 0x0F0F0F0Fu, (b >> 4) & 0x0F0F0F0Fu, bb.x, bb.y);
-                    }
-                    unit_finish(msl, i, cons.seg, cons.g + i, c);
-                }
-            } else {
-                // two units at a time: their MMA chains are independent and interleave in the pipe
-                const uint8_t* dgb = digits + (size_t)(NSEG == 1 ? 0 : cons.seg) * 4 * dstride + (size_t)r * dstride + cons.g * GS + t * 32;
-                for (int i = 0; i < len; i += 2) {
-                    const bool two = i + 1 < len;
-                    const uint8_t* wu = wsl + (size_t)i * 1024 + lane * 16;
-                    const uint4 a0 = *reinterpret_cast<const uint4*>(wu), b0 = *reinterpret_cast<const uint4*>(wu + 512);
-                    const uint4 a1 = *reinterpret_cast<const uint4*>(wu + (two ? 1024 : 0)), b1 = *reinterpret_cast<const uint4*>(wu + (two ? 1536 : 512));
-                    uint4 d00 = make_uint4(0, 0, 0, 0), d01 = d00, d10 = d00, d11 = d00;
-                    if (r < 4) {
-                        const uint4* dp = reinterpret_cast<const uint4*>(dgb + (size_t)i * GS);
-                        d00 = dp[0]; d01 = dp[1];
-                        if (two) { d10 = dp[GS / 16]; d11 = dp[GS / 16 + 1]; }
-                    }
-                    int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
-                    constexpr uint32_t M = 0x0F0F0F0Fu;
-                    mma_u8s8(c0, a0.x & M, b0.x & M, (a0.x >> 4) & M, (b0.x >> 4) & M, d00.x, d00.y);
-                    mma_u8s8(c1, a1.x & M, b1.x & M, (a1.x >> 4) & M, (b1.x >> 4) & M, d10.x, d10.y);
-                    mma_u8s8(c0, a0.y & M, b0.y & M, (a0.y >> 4) & M, (b0.y >> 4) & M, d00.z, d00.w);
-                    mma_u8s8(c1, a1.y & M, b1.y & M, (a1.y >> 4) & M, (b1.y >> 4) & M, d10.z, d10.w);
-                    mma_u8s8(c0, a0.z & M, b0.z & M, (a0.z >> 4) & M, (b0.z >> 4) & M, d01.x, d01.y);
-                    mma_u8s8(c1, a1.z & M, b1.z & M, (a1.z >> 4) & M, (b1.z >> 4) & M, d11.x, d11.y);
-                    mma_u8s8(c0, a0.w & M, b0.w & M, (a0.w >> 4) & M, (b0.w >> 4) & M, d01.z, d01.w);
-                    mma_u8s8(c1, a1.w & M, b1.w & M, (a1.w >> 4) & M, (b1.w >> 4) & M, d11.z, d11.w);
-                    unit_finish(msl, i, cons.seg, cons.g + i, c0);
-                    if (two) unit_finish(msl, i + 1, cons.seg, cons.g + i + 1, c1);
-                }
+        if (!ok) break;
+        if (!P.debug_skip) {
+            const uint8_t* base = ring + (size_t)slot * slot_bytes;
+            for (int j = 2 * warp; j < m; j += 2 * SK_WARPS) {
+                const bool two = j + 1 < m;
+                int tl0, seg0, g0, tl1 = 0, seg1 = 0, g1 = 0;
+                locate(k * SU + j, tl0, seg0, g0);
+                if (two) { g1 = g0 + 1; seg1 = seg0; tl1 = tl0; if (g1 == G) locate(k * SU + j + 1, tl1, seg1, g1); }
+                int c0[4], c1[4];
+                const uint8_t* rec0 = base + (size_t)j * UB;
+                unit_mma(rec0, digits_of(seg0, g0), c0);
+                if (two) unit_mma(rec0 + UB, digits_of(seg1, g1), c1);
+                unit_finish(rec0, tl0, seg0, g0, c0);
+                if (two) unit_finish(rec0 + UB, tl1, seg1, g1, c1);
             }
         }
-        __syncwarp();  // every lane has read the slot: it may be refilled
-        if (lane == 0 && ok && prod.u < wb) {
-            const int plen = chunk_len(prod);
-            issue(slot, prod, plen);
-            advance(prod, plen);
-        }
-        // a chunk never crosses a (tile, segment) boundary: flush the row sums when it ends one
-        if (cons.g + len == G || cons.u + len == wb) {
-            // lanes t = 0 hold digits 0,1 (weight 2^14 relative to digits 2,3 held by lanes t = 1)
-            float a = t == 0 ? tot0 * 16384.0f : tot0, b = t == 0 ? tot1 * 16384.0f : tot1;
-            a += __shfl_xor_sync(0xffffffffu, a, 1);
-            b += __shfl_xor_sync(0xffffffffu, b, 1);
-            if (t == 0) {
-                float* dst = partial + ((size_t)cons.tl * SK_WARPS + warp) * ROWS + cons.seg * 16;
-                dst[r] = a;
-                dst[r + 8] = b;
-            }
-            tot0 = tot1 = 0.f;
-        }
-        advance(cons, len);
+        __syncwarp();  // every lane has read the slot
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + slot)) : "memory");
     }
+    flush();
     if (!ok) {
-        // copies may still be in flight into this CTA's shared memory: give them a bounded time
-        // to land before the CTA exits, without using their data
-        for (int i = 0; i < NS; i++) mbar_wait(bar + i, 0);
-        for (int i = 0; i < NS; i++) mbar_wait(bar + i, 1);
+        // copies may still be in flight into this CTA's shared memory: give them a bounded time to land
+        // before the CTA exits, without using their data
+        for (int i = 0; i < NS; i++) { mbar_wait(full + i, 0, 1u << 16); mbar_wait(full + i, 1, 1u << 16); }
     }
     SK_STAMP(4);
-    __syncthreads();
+    consumer_sync();
     SK_STAMP(5);
 
     // ---- per tile: sum the warps in order, then the epilogue
@@ -475,7 +493,7 @@ static cudaError_t launch_sk_t(const SkParams* p, int grid, size_t smem, cudaStr
     cudaLaunchConfig_t cfg{};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(SK_THREADS);
+    cfg.blockDim = dim3(SK_THREADS + 32);  // 16 consumer warps + 1 producer warp
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     if (pdl) {

@@ -30,8 +30,7 @@ constexpr int SK_MAX_SLOTS = 8;            // ring slots per warp (upper bound)
 
 // One 4-bit matrix in device layout (see repack.cpp) with its input vector.
 struct SkSeg {
-    const uint32_t* qw;   // [tile][group][2][32][W]
-    const uint32_t* meta; // [tile][group][20]: 16 f32 scales, 2 zero-nibble words, 2 pad
+    const uint32_t* rec;  // [tile][group] unit records of 64*W + 20 words (see repack.cpp)
     const float* x;       // input in this matrix's K order (the producer scatters it)
     const float* nw;      // rmsnorm weight in the same order, or null
 };
@@ -61,6 +60,7 @@ struct alignas(16) SkParams {
     unsigned long long* trace;  // debug: 8 clock stamps per CTA, or null
     int* status;                // set non-zero when a bounded wait gives up, or null
     int chunk, slots;           // units per ring slot, ring slots per warp
+    int debug_skip;             // debug: wait for the copies but skip the arithmetic
     int ptiles;                 // tiles the per-CTA sum buffer holds
 };
 

@@ -8,6 +8,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "model.h"
@@ -32,8 +33,7 @@ static int dev_upload(T** p, const void* src, size_t count, std::vector<void*>& 
 
 int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vector<void*>& allocs, size_t* bytes) {
     d.in = p.in; d.out = p.out; d.tiles = p.tiles; d.G = p.groups; d.gs = p.w * 32;
-    if (int rc = dev_upload(&d.qw, p.qw.data(), p.qw.size(), allocs, bytes)) return rc;
-    if (int rc = dev_upload(&d.meta, p.meta.data(), p.meta.size(), allocs, bytes)) return rc;
+    if (int rc = dev_upload(&d.rec, p.rec.data(), p.rec.size(), allocs, bytes)) return rc;
     if (g_index) {
         if (int rc = dev_upload(&d.perm, g_index, (size_t)p.in, allocs, bytes)) return rc;
         std::vector<int32_t> inv = inverse_permutation(g_index, p.in);
@@ -53,7 +53,7 @@ void launch_permute(const float* x, const int* perm, float* xp, int n, cudaStrea
 }
 
 void sk_set_matrix(SkJob& j, int seg, const DevQ& q, const float* x, const float* nw) {
-    j.seg[seg].qw = q.qw; j.seg[seg].meta = q.meta;
+    j.seg[seg].rec = q.rec;
     j.seg[seg].x = x; j.seg[seg].nw = nw;
     j.rows = q.out; j.tiles = q.tiles; j.in = q.in; j.G = q.G;
 }
@@ -85,31 +85,36 @@ int sk_plan(SkLaunch& L, int sms) {
     const size_t fixed = (sk_smem_fixed(p.job[0].in, max_g, L.nseg, ptiles) + 127) & ~(size_t)127;
     const size_t budget = 224 * 1024;
     if (fixed >= budget) return fail(L2_EINVAL, "IN %d needs %zu bytes of shared memory before the weight rings", p.job[0].in, fixed);
-    // ring geometry: small chunks (refilled early), as many slots as fit, no more than a warp's range needs
-    const int chunk = L.gs == 128 ? 2 : 4;
-    const size_t per_warp = (budget - fixed) / SK_WARPS;
-    int slots = (int)std::min<size_t>(SK_MAX_SLOTS, per_warp / sk_slot_bytes(L.gs, chunk));
-    if (slots < 2) return fail(L2_EINVAL, "IN %d leaves no shared memory for the weight rings", p.job[0].in);
+    // ring geometry: large slots (the copy engine spends a fixed time per request), as many as fit,
+    // no more than the longest CTA range needs
+    int su = 32;
+    if (const char* e = getenv("L2_SK_CHUNK")) su = std::max(2, atoi(e) & ~1);  // tuning knob
     long long max_units = 0;
     for (int i = 0; i < p.njobs; i++)
-        max_units = std::max<long long>(max_units, ((long long)((p.job[i].tiles + p.job[i].ncta - 1) / p.job[i].ncta) * L.nseg * p.job[i].G + SK_WARPS - 1) / SK_WARPS + 1);
-    const int needed = (int)((max_units + chunk - 1) / chunk) + 1;
-    slots = std::max(2, std::min(slots, needed));
+        max_units = std::max<long long>(max_units, (long long)((p.job[i].tiles + p.job[i].ncta - 1) / p.job[i].ncta) * L.nseg * p.job[i].G);
+    int slots = 0;
+    for (; su >= 2; su /= 2) {
+        slots = (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(L.gs, su));
+        if (slots >= 2) break;
+    }
+    if (slots < 2) return fail(L2_EINVAL, "IN %d leaves no shared memory for the weight ring", p.job[0].in);
+    slots = std::max(2, std::min<int>(slots, (int)((max_units + su - 1) / su)));
+    const int chunk = su;
+    if (const char* e = getenv("L2_SK_SLOTS")) slots = std::max(2, std::min(slots, atoi(e)));
+    p.debug_skip = getenv("L2_SK_SKIP") ? 1 : 0;
     p.chunk = chunk;
     p.slots = slots;
     p.ptiles = ptiles;
-    L.smem = fixed + (size_t)SK_WARPS * slots * sk_slot_bytes(L.gs, chunk);
+    L.smem = fixed + (size_t)slots * sk_slot_bytes(L.gs, chunk);
     return L2_OK;
 }
 
 // Registers the weights of `q` as the next kernel's, to be fetched into L2 by launch L.
 void sk_prefetch_next(SkLaunch& L, const DevQ& q) {
     SkParams& p = L.p;
-    if (p.n_next + 2 > 6) return;
-    p.next_ptr[p.n_next] = q.qw;
-    p.next_bytes[p.n_next++] = (size_t)q.tiles * q.G * (q.gs / 32) * 256;
-    p.next_ptr[p.n_next] = q.meta;
-    p.next_bytes[p.n_next++] = (size_t)q.tiles * q.G * 80;
+    if (p.n_next + 1 > 6) return;
+    p.next_ptr[p.n_next] = q.rec;
+    p.next_bytes[p.n_next++] = (size_t)q.tiles * q.G * ((q.gs / 32) * 256 + 80);
 }
 
 int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, SkParams* d_plan, cudaStream_t st) {

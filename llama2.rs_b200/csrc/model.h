@@ -21,8 +21,7 @@ namespace l2 {
 
 // One QLinear in device layout (see repack.cpp) plus what its producers/consumers need.
 struct DevQ {
-    uint32_t* qw = nullptr;    // [tiles][G][2][32][W]
-    uint32_t* meta = nullptr;  // [tiles][G][20]: scales, zero nibbles, padding
+    uint32_t* rec = nullptr;   // [tiles][G] unit records: weights, scales, zero nibbles (see repack.cpp)
     int* perm = nullptr;  // g_index: permuted position j reads input perm[j]
     int* inv = nullptr;   // inverse: input o is written to permuted position inv[o]
     int in = 0, out = 0, tiles = 0, G = 0, gs = 0;

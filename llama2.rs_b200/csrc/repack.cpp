@@ -6,11 +6,10 @@
 // of word i is the weight of permuted input 8i+j, as in the checkpoint) are stored in the order
 // in which the 32 lanes of a warp consume them, so that a warp reads one unit with two fully
 // coalesced loads per lane and the units of a tile are contiguous:
-//   qw     [tile][group][half h][lane L][W]   row = 16*tile + 8*h + L/4, words (L%4)*W .. +W-1 of the group
-//   meta   [tile][group][20]                  words 0-15: f32 scales of rows 16*tile + i; words 16,17:
-//                                             zero nibbles (nibble r of word 16+h = row 16*tile + 8*h + r);
-//                                             words 18,19 pad the record to 80 bytes (bulk copies move
-//                                             multiples of 16 bytes)
+//   rec [tile][group] = { words[half h][lane L][W]   row = 16*tile + 8*h + L/4, words (L%4)*W .. +W-1 of the group
+//                         scales[16]                  f32, rows 16*tile + i
+//                         zeros[2]                    nibble r of word h = zero nibble of row 16*tile + 8*h + r
+//                         pad[2] }                    the record is a multiple of 16 bytes (bulk copies need that)
 #include <cstdlib>
 #include <cstring>
 
@@ -26,8 +25,8 @@ void repack_qlinear(int in, int out, int gs, const int32_t* qweight, const int32
     const int wpg = gs / 8;        // words per group
     const int tiles = (out + 15) / 16;
     dst.in = in; dst.out = out; dst.groups = g; dst.tiles = tiles; dst.w = w;
-    dst.qw.assign((size_t)tiles * g * 64 * w, 0);
-    dst.meta.assign((size_t)tiles * g * 20, 0);
+    const size_t uw = (size_t)dst.unit_words();
+    dst.rec.assign((size_t)tiles * g * uw, 0);
     const uint32_t* qws = reinterpret_cast<const uint32_t*>(qweight);
     const uint32_t* qzs = reinterpret_cast<const uint32_t*>(qzeros);
     for (int j = 0; j < out; j++) {
@@ -37,10 +36,10 @@ void repack_qlinear(int in, int out, int gs, const int32_t* qweight, const int32
             const size_t unit = (size_t)tile * g + k;
             for (int t = 0; t < 4; t++)
                 for (int i = 0; i < w; i++)
-                    dst.qw[(unit * 2 + h) * 32 * w + (size_t)(r * 4 + t) * w + i] = qws[(size_t)src * wpr + (size_t)k * wpg + t * w + i];
-            memcpy(&dst.meta[unit * 20 + (j % 16)], &scales[(size_t)src * g + k], 4);
+                    dst.rec[unit * uw + (size_t)h * 32 * w + (size_t)(r * 4 + t) * w + i] = qws[(size_t)src * wpr + (size_t)k * wpg + t * w + i];
+            memcpy(&dst.rec[unit * uw + 64 * w + (j % 16)], &scales[(size_t)src * g + k], 4);
             const uint32_t nib = (qzs[(size_t)(src / 8) * g + k] >> (4 * (src % 8))) & 15u;
-            dst.meta[unit * 20 + 16 + h] |= nib << (4 * r);
+            dst.rec[unit * uw + 64 * w + 16 + h] |= nib << (4 * r);
         }
     }
 }
@@ -65,19 +64,18 @@ bool is_permutation(const int32_t* perm, int n) {
 using namespace l2;
 
 extern "C" int l2_debug_repack(int in, int out, int group_size, const int32_t* qweight, const int32_t* qzeros,
-                               const float* scales, const int32_t* rows_order, uint32_t** qw_dev,
-                               uint32_t** meta_dev, int* tiles) {
+                               const float* scales, const int32_t* rows_order, uint32_t** rec_dev,
+                               int* tiles, int* unit_words) {
     clear_error();
-    if (!qweight || !qzeros || !scales || !qw_dev || !meta_dev || !tiles)
+    if (!qweight || !qzeros || !scales || !rec_dev || !tiles || !unit_words)
         return fail(L2_EINVAL, "l2_debug_repack: null argument");
     if (in % 32 || out % 8 || in % group_size) return fail(L2_EINVAL, "l2_debug_repack: bad shape");
     if (rows_order && !is_permutation(rows_order, out)) return fail(L2_EINVAL, "l2_debug_repack: rows_order is not a permutation");
     PackedQ p;
     repack_qlinear(in, out, group_size, qweight, qzeros, scales, rows_order, p);
-    *qw_dev = (uint32_t*)malloc(p.qw.size() * 4);
-    *meta_dev = (uint32_t*)malloc(p.meta.size() * 4);
-    memcpy(*qw_dev, p.qw.data(), p.qw.size() * 4);
-    memcpy(*meta_dev, p.meta.data(), p.meta.size() * 4);
+    *rec_dev = (uint32_t*)malloc(p.rec.size() * 4);
+    memcpy(*rec_dev, p.rec.data(), p.rec.size() * 4);
     *tiles = p.tiles;
+    *unit_words = p.unit_words();
     return L2_OK;
 }

@@ -12,10 +12,12 @@ namespace l2 {
 // units of (tile, group).  W = GS/32 is the number of 32-bit weight words a lane holds per row.
 struct PackedQ {
     int in = 0, out = 0, groups = 0, tiles = 0, w = 0;
-    std::vector<uint32_t> qw;  // [tiles][groups][2][32][W]: half h, lane L=(r,t): words t*W..t*W+W-1 of row 16*tile+8h+r in the group
-    // [tiles][groups][20] words: 16 f32 scales (row 16*tile+i), 2 zero words (nibble r of word h is
-    // the zero nibble of row 16*tile+8h+r), 2 words of padding: 80 bytes, a multiple of 16
-    std::vector<uint32_t> meta;
+    // [tiles][groups] unit records of 64*W + 20 words, contiguous so that one bulk copy moves a run:
+    //   words [h][L][W]  half h, lane L=(r,t): weight words t*W..t*W+W-1 of row 16*tile+8h+r in the group
+    //   16 f32 scales (row 16*tile+i), 2 zero words (nibble r of word h = zero nibble of row 16*tile+8h+r),
+    //   2 words of padding (the record is a multiple of 16 bytes)
+    std::vector<uint32_t> rec;
+    int unit_words() const { return 64 * w + 20; }
 };
 
 // rows_order[j] = checkpoint row that becomes device row j (NULL = identity).  Rows beyond OUT in

@@ -85,7 +85,7 @@ SIGNATURES = {
     "l2_tokenizer_vocab": (C.c_char_p, [_vp, C.c_int32]),
     "l2_tokenizer_piece": (C.c_char_p, [_vp, C.c_int32, C.c_int32]),
     "l2_debug_repack": (C.c_int, [C.c_int, C.c_int, C.c_int, _i32p, _i32p, _f32p, _i32p,
-                                  _p(_p(C.c_uint32)), _p(_p(C.c_uint32)), _p(C.c_int)]),
+                                  _p(_p(C.c_uint32)), _p(C.c_int), _p(C.c_int)]),
     "l2_host_free": (None, [_vp]),
 }
 for _name, (_res, _args) in SIGNATURES.items():

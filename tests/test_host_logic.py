@@ -20,12 +20,13 @@ def test_every_declared_symbol_is_exported(l2):
     assert declared == set(l2._lib.SIGNATURES), declared ^ set(l2._lib.SIGNATURES)
 
 
-def emulate_device_gemv(qw, meta, tiles, in_f, out_f, gs, x_perm):
+def emulate_device_gemv(rec, tiles, in_f, out_f, gs, x_perm):
     """numpy model of the kernel's view of the device layout (tiles of 16 rows, units of one group):
     y[o] = sum_g scale * sum_k (q - z) x."""
     G, W = in_f // gs, gs // 32
-    qw = qw.reshape(tiles, G, 2, 32, W)
-    meta = meta.reshape(tiles, G, 20)
+    rec = rec.reshape(tiles, G, 64 * W + 20)
+    qw = rec[:, :, :64 * W].reshape(tiles, G, 2, 32, W)
+    meta = rec[:, :, 64 * W:]
     sc = meta[:, :, :16].copy().view(np.float32)
     zr = meta[:, :, 16:18]
     assert not meta[:, :, 18:].any()
@@ -51,19 +52,19 @@ def test_repack_is_exact(l2, orc, gs, in_f, out_f):
     qweight, qzeros, scales, g_index = random_qlinear(rng, in_f, out_f, gs)
     order = rng.permutation(out_f).astype(np.int32)
     for rows in (None, order):
-        pq, pm = C.POINTER(C.c_uint32)(), C.POINTER(C.c_uint32)()
-        tiles = C.c_int(0)
+        pq = C.POINTER(C.c_uint32)()
+        tiles, uw = C.c_int(0), C.c_int(0)
         l2.check(l2.lib.l2_debug_repack(in_f, out_f, gs, l2._lib.as_i32p(qweight), l2._lib.as_i32p(qzeros), l2._lib.as_f32p(scales),
                                         l2._lib.as_i32p(rows) if rows is not None else None,
-                                        C.byref(pq), C.byref(pm), C.byref(tiles)))
+                                        C.byref(pq), C.byref(tiles), C.byref(uw)))
         g = in_f // gs
         assert tiles.value == (out_f + 15) // 16
-        qw = np.ctypeslib.as_array(pq, shape=(tiles.value * g * 64 * (gs // 32),)).copy()
-        meta = np.ctypeslib.as_array(pm, shape=(tiles.value * g * 20,)).copy()
-        for p in (pq, pm):
-            l2.lib.l2_host_free(p)
+        assert uw.value == 64 * (gs // 32) + 20
+        rec = np.ctypeslib.as_array(pq, shape=(tiles.value * g * uw.value,)).copy()
+        l2.lib.l2_host_free(pq)
+        qw = rec.reshape(-1, uw.value)[:, :64 * (gs // 32)].ravel()
         x = rng.standard_normal(in_f).astype(np.float32)
-        y = emulate_device_gemv(qw, meta, tiles.value, in_f, out_f, gs, x[g_index])
+        y = emulate_device_gemv(rec, tiles.value, in_f, out_f, gs, x[g_index])
         want = orc.qlinear_matvec(qweight, qzeros, scales, g_index, gs, x).astype(np.float64)
         if rows is not None:
             want = want[rows]
@@ -76,9 +77,9 @@ def test_repack_rejects_bad_arguments(l2):
     rng = np.random.default_rng(0)
     qweight, qzeros, scales, g_index = random_qlinear(rng, 64, 8, 32)
     bad = np.zeros(8, np.int32)
-    pq, pm, gp = C.POINTER(C.c_uint32)(), C.POINTER(C.c_uint32)(), C.c_int(0)
+    pq, gp, uw = C.POINTER(C.c_uint32)(), C.c_int(0), C.c_int(0)
     rc = l2.lib.l2_debug_repack(64, 8, 32, l2._lib.as_i32p(qweight), l2._lib.as_i32p(qzeros), l2._lib.as_f32p(scales),
-                                l2._lib.as_i32p(bad), C.byref(pq), C.byref(pm), C.byref(gp))
+                                l2._lib.as_i32p(bad), C.byref(pq), C.byref(gp), C.byref(uw))
     assert rc == -1 and b"permutation" in l2.lib.l2_last_error()
 
 
