@@ -64,6 +64,45 @@ struct alignas(16) SkParams {
     int ptiles;                 // tiles the per-CTA sum buffer holds
 };
 
+// Batched QLinear on tcgen05 (gemm_tc.cu): out[m][o] for m < M tokens, 128 output rows per CTA.
+struct TcParams {
+    const uint32_t* rec;   // unit records of the matrix (see repack.cpp)
+    const uint8_t* bimg;   // [G][n][gs] signed digit bytes of the activations, swizzled (act_quant_kernel)
+    const int* sv;         // [G][mpad][2] digit sums per token and group: 128*S0+S1, 128*S2+S3
+    const float* oscale;   // [mpad] factor of the integer result per token
+    float* out;            // [M][ldo]
+    int* status;
+    int tiles16, G, gs, rows;
+    int m, mpad, n;        // tokens, tokens padded to a multiple of 4, n = 4 * mpad
+    int ldo, epi;
+};
+
+struct QuantParams {
+    const float* x;        // [M][ldx] activations, natural order
+    const int* perm;       // consumer's K order (g_index) or null
+    const float* nw;       // rmsnorm weight in the consumer's K order, or null (no norm)
+    uint8_t* bimg;         // [G][n][gs]
+    int* sv;               // [G][mpad][2]
+    float* oscale;         // [mpad]
+    int in, gs, ldx, mpad, n;
+    float eps;
+};
+
+struct RopeParams {
+    float* q; const float* k; const float* v;   // [M][ldq], [M][ldkv]
+    float* kc; float* vc;                        // this layer's caches
+    const float* rope_cos; const float* rope_sin;
+    const int* pos;                              // [M]
+    int n_kv_heads, ldq, ldkv;
+};
+
+struct AttnBatchParams {
+    const float* q; const float* kc; const float* vc;
+    const int* pos;
+    float* out;                                  // [M][ldo], natural order
+    int n_kv_heads, ag, ldq, ldo;
+};
+
 struct EmbedParams {
     const float* table;   // [VOCAB][DIM]
     const Ctl* ctl;
@@ -111,6 +150,14 @@ cudaError_t launch_sk(const SkParams* p, int group_size, int nseg, int grid, siz
 size_t sk_smem_fixed(int in, int G, int nseg, int ptiles);  // digits, group sums, tile sums
 size_t sk_slot_bytes(int group_size, int chunk);           // one ring slot of one warp
 cudaError_t sk_init(int max_smem);
+void launch_embed_batch(const float* table, const int* tokens, float* x, int dim, int M, cudaStream_t st);
+void launch_act_quant(const QuantParams& p, int M, cudaStream_t st);
+void launch_rope_append(const RopeParams& p, int n_heads, int M, cudaStream_t st);
+void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_t st);
+void launch_swiglu(const float* h1, const float* h3, float* hb, size_t n, cudaStream_t st);
+cudaError_t launch_gemm_tc(const TcParams& p, cudaStream_t st);
+cudaError_t gemm_tc_init(int max_smem);
+size_t gemm_tc_smem_bytes(int gs, int n);
 extern unsigned long long* g_sk_trace;  // device buffer for SkParams::trace when tracing is on
 void launch_attn(const AttnParams& p, cudaStream_t st, bool pdl);
 void launch_cls(const ClsParams& p, int grid, cudaStream_t st, bool pdl);

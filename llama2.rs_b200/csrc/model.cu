@@ -430,15 +430,6 @@ static int upload_prompt(l2_state* s, const int32_t* prompt, int n_prompt) {
     return L2_OK;
 }
 
-// Positions the prefill ladder covers for a prompt of n tokens (src/inference.rs:24, 78-127).
-static int ladder_positions(int n, int chunk) {
-    static const int ladder[6] = {64, 32, 16, 8, 4, 2};
-    int pos = 0;
-    if (chunk > 0) { while (pos + chunk < n) pos += chunk; return pos; }
-    for (int a : ladder) while (pos + a < n) pos += a;
-    return pos;
-}
-
 }  // namespace l2
 
 // ---- C ABI: model -------------------------------------------------------------------------------
@@ -616,6 +607,7 @@ extern "C" void l2_state_free(l2_state* s) {
     for (auto& g : s->graphs) if (g) cudaGraphExecDestroy(g);
     free_allocs(s->allocs);
     if (s->h_ctl) cudaFreeHost(s->h_ctl);
+    if (s->batch) { if (s->batch->h_stage) cudaFreeHost(s->batch->h_stage); delete s->batch; }
     if (s->m->gen_state == s) s->m->gen_state = nullptr;
     delete s;
 }
@@ -640,37 +632,66 @@ static int check_state(l2_model* m, l2_state* s, const char* who) {
     return L2_OK;
 }
 
+static int check_status(l2_state* s);
+
 extern "C" int l2_forward(l2_model* m, l2_state* s, const int32_t* tokens, const int32_t* pos, int B, float* logits) {
     clear_error();
     if (int rc = check_state(m, s, "l2_forward")) return rc;
     const l2_config& c = m->shape.c;
-    const int maxb = m->opt.max_batch > 0 ? m->opt.max_batch : 64;
+    const int maxb = m->opt.max_batch > 0 ? std::min(m->opt.max_batch, (int)MAX_BATCH) : (int)MAX_BATCH;
     if (!tokens || !pos || B < 1 || B > maxb) return fail(L2_EINVAL, "l2_forward: bad batch (B=%d, max %d)", B, maxb);
     for (int b = 0; b < B; b++) {
         if (pos[b] < 0 || pos[b] >= c.seq_len) return fail(L2_ERANGE, "l2_forward: position %d outside 0..%d", pos[b], c.seq_len - 1);
         if (tokens[b] < 0 || tokens[b] >= c.vocab_size) return fail(L2_ERANGE, "l2_forward: token %d outside the vocabulary", tokens[b]);
-        // Rows are evaluated in order, each seeing the cache rows written before it; that equals the
-        // reference (all rows stored, then attention over 0..=pos[b]) when positions ascend.
-        if (b && pos[b] <= pos[b - 1]) return fail(L2_EINVAL, "l2_forward: positions of a batch must be strictly ascending");
+        for (int a = 0; a < b; a++)
+            if (pos[a] == pos[b]) return fail(L2_EINVAL, "l2_forward: two rows of a batch share position %d", pos[b]);
     }
-    for (int b = 0; b < B; b++) {
-        if (int rc = write_ctl(s, pos[b], tokens[b], 0, -1, 0.f, 0)) return rc;
-        if (int rc = run_forward(s, (B == 1 && logits) ? G_FWD_CLS : G_FWD)) return rc;
+    if (B == 1) {
+        if (int rc = write_ctl(s, pos[0], tokens[0], 0, -1, 0.f, 0)) return rc;
+        if (int rc = run_forward(s, logits ? G_FWD_CLS : G_FWD)) return rc;
+    } else if (int rc = forward_batch(s, B, tokens, pos)) {  // all rows stored, then attention over 0..=pos[b]
+        return rc;
     }
     if (B == 1 && logits) L2_CUDA(cudaMemcpyAsync(logits, s->logits, sizeof(float) * c.vocab_size, cudaMemcpyDeviceToHost, m->stream));
+    if (B > 1) return check_status(s);
     L2_CUDA(cudaStreamSynchronize(m->stream));
     return L2_OK;
 }
 
 static int prefill_async(l2_model* m, l2_state* s, const int32_t* prompt, int n_prompt, int chunk, int32_t* pos_out) {
     if (int rc = upload_prompt(s, prompt, n_prompt)) return rc;
-    const int covered = ladder_positions(n_prompt, chunk);
-    if (covered > 0) {
-        if (int rc = write_ctl(s, 0, L2_START, n_prompt, -1, 0.f, 0)) return rc;
-        for (int p = 0; p < covered; p++)
-            if (int rc = run_forward(s, G_FEED)) return rc;
+    // Positions the reference's ladder 64/32/16/8/4/2 covers (src/inference.rs:24, 78-127): the B=1 loop
+    // must start where it starts there.  How those positions are cut into batches does not change the
+    // cache ("should lead to identical results", src/inference.rs:12-15), so they go in batches of up to
+    // MAX_BATCH rows.
+    static const int ladder[6] = {64, 32, 16, 8, 4, 2};
+    int target = 0;
+    if (chunk > 0) { while (target + chunk < n_prompt) target += chunk; }
+    else for (int a : ladder) while (target + a < n_prompt) target += a;
+    int pos = 0;
+    int32_t tokens[MAX_BATCH], positions[MAX_BATCH];
+    while (pos < target) {
+        const int A = std::min<int>(MAX_BATCH, target - pos);
+        for (int i = 0; i < A; i++) {
+            tokens[i] = pos == 0 ? L2_START : prompt[pos - 1];  // src/inference.rs:29-35
+            positions[i] = pos++;
+        }
+        if (A == 1) {
+            if (int rc = write_ctl(s, positions[0], tokens[0], 0, -1, 0.f, 0)) return rc;
+            if (int rc = run_forward(s, G_FWD)) return rc;
+        } else if (int rc = forward_batch(s, A, tokens, positions)) {
+            return rc;
+        }
     }
-    *pos_out = covered;
+    *pos_out = pos;
+    return L2_OK;
+}
+
+// Synchronises the stream and reports a device-side bounded wait that gave up.
+static int check_status(l2_state* s) {
+    L2_CUDA(cudaMemcpyAsync(s->h_ctl, s->ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, s->m->stream));
+    L2_CUDA(cudaStreamSynchronize(s->m->stream));
+    if (s->h_ctl->status) return fail(L2_ESTATUS, "device status %d", s->h_ctl->status);
     return L2_OK;
 }
 
@@ -679,8 +700,7 @@ extern "C" int l2_prefill(l2_model* m, l2_state* s, const int32_t* prompt, int n
     if (int rc = check_state(m, s, "l2_prefill")) return rc;
     if ((!prompt && n_prompt) || !pos_out || chunk < 0) return fail(L2_EINVAL, "l2_prefill: bad argument");
     if (int rc = prefill_async(m, s, prompt, n_prompt, chunk, pos_out)) return rc;
-    L2_CUDA(cudaStreamSynchronize(m->stream));
-    return L2_OK;
+    return check_status(s);
 }
 
 extern "C" int l2_decode_step(l2_model* m, l2_state* s, int32_t token, int32_t pos, float temperature, uint64_t* rng_seed,
@@ -752,7 +772,7 @@ extern "C" int l2_generate_ids(l2_model* m, const int32_t* prompt, int n_prompt,
     do {
         if ((rc = upload_prompt(s, prompt, n_prompt))) break;
         cudaEventRecord(e0, m->stream);  // src/inference.rs:72
-        if (use_prefill && (rc = prefill_async(m, s, prompt, n_prompt, 0, &pos0))) break;
+        if (use_prefill && ((rc = prefill_async(m, s, prompt, n_prompt, 0, &pos0)) || (pos0 > 0 && (rc = check_status(s))))) break;
         cudaEventRecord(e1, m->stream);
         n_out = steps > pos0 ? steps - pos0 : 0;
         if (!logits_trace) {
@@ -928,6 +948,13 @@ static int qlinear_reserve(l2_qlinear* h, int B) {
     if ((rc = dev_alloc(reinterpret_cast<void**>(&h->x_dev), sizeof(float) * h->q.in * B, h->allocs))) return rc;
     if ((rc = dev_alloc(reinterpret_cast<void**>(&h->xp_dev), sizeof(float) * h->q.in * B, h->allocs))) return rc;
     if ((rc = dev_alloc(reinterpret_cast<void**>(&h->y_dev), sizeof(float) * h->q.out * B, h->allocs))) return rc;
+    if (!h->img) {  // buffers of the batched (tcgen05) path, one chunk of MAX_BATCH tokens
+        if ((rc = dev_alloc(reinterpret_cast<void**>(&h->img), (size_t)4 * MAX_BATCH * h->q.in, h->allocs))) return rc;
+        if ((rc = dev_alloc(reinterpret_cast<void**>(&h->sv), sizeof(int) * 2 * MAX_BATCH * h->q.G, h->allocs))) return rc;
+        if ((rc = dev_alloc(reinterpret_cast<void**>(&h->osc), sizeof(float) * MAX_BATCH, h->allocs))) return rc;
+        if ((rc = dev_alloc(reinterpret_cast<void**>(&h->status), sizeof(int), h->allocs))) return rc;
+        L2_CUDA(cudaMemset(h->status, 0, sizeof(int)));
+    }
     h->cap_b = B;
     return L2_OK;
 }
@@ -938,6 +965,14 @@ extern "C" int l2_qlinear_matvec_dev(l2_qlinear* h, const float* x_dev, float* x
     L2_CUDA(cudaSetDevice(h->device));
     cudaStream_t st = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : h->stream;
     if (int rc = qlinear_reserve(h, B)) return rc;
+    if (B >= 2) {  // batched: tensor-core GEMM, MAX_BATCH tokens at a time
+        for (int b0 = 0; b0 < B; b0 += MAX_BATCH) {
+            const int M = std::min<int>(MAX_BATCH, B - b0);
+            if (int rc = gemm_batched(h->q, x_dev + (size_t)b0 * h->q.in, h->q.in, true, nullptr, 0.f, M, h->img, h->sv, h->osc,
+                                      xout_dev + (size_t)b0 * h->q.out, h->q.out, EPI_STORE, h->status, st)) return rc;
+        }
+        return L2_OK;
+    }
     for (int b = 0; b < B; b++) {
         launch_permute(x_dev + (size_t)b * h->q.in, h->q.perm, h->xp_dev + (size_t)b * h->q.in, h->q.in, st);
         if (int rc = run_gemv_single(h->q, h->xp_dev + (size_t)b * h->q.in, xout_dev + (size_t)b * h->q.out, h->sms, h->d_plan, st)) return rc;
@@ -953,7 +988,10 @@ extern "C" int l2_qlinear_matvec(l2_qlinear* h, const float* x, float* xout, int
     L2_CUDA(cudaMemcpyAsync(h->x_dev, x, sizeof(float) * h->q.in * B, cudaMemcpyHostToDevice, h->stream));
     if (int rc = l2_qlinear_matvec_dev(h, h->x_dev, h->y_dev, B, h->stream)) return rc;
     L2_CUDA(cudaMemcpyAsync(xout, h->y_dev, sizeof(float) * h->q.out * B, cudaMemcpyDeviceToHost, h->stream));
+    int status = 0;
+    if (h->status) L2_CUDA(cudaMemcpyAsync(&status, h->status, sizeof(int), cudaMemcpyDeviceToHost, h->stream));
     L2_CUDA(cudaStreamSynchronize(h->stream));
+    if (status) return fail(L2_ESTATUS, "device status %d", status);
     return L2_OK;
 }
 

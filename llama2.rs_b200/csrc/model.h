@@ -41,6 +41,18 @@ struct DevLayer {
 };
 
 constexpr int CTL_RING = 128;
+constexpr int MAX_BATCH = 64;  // tokens of one batched forward (one tcgen05 tile holds 4 digits x 64 tokens)
+
+// Device buffers of the batched forward pass (transformer<B>, B >= 2).
+struct BatchBuffers {
+    float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *h1 = nullptr, *h3 = nullptr, *hb = nullptr;
+    uint8_t* img[3] = {nullptr, nullptr, nullptr};  // digit images of up to three consumers
+    int* sv[3] = {nullptr, nullptr, nullptr};
+    float* osc[3] = {nullptr, nullptr, nullptr};
+    int *tok = nullptr, *pos = nullptr;             // device token ids / positions of the batch
+    int* h_stage = nullptr;                         // pinned ring for their upload
+    int stage_slot = 0;
+};
 
 enum GraphKind : int { G_DECODE = 0, G_FEED, G_FWD_CLS, G_FWD, G_COUNT };
 
@@ -82,6 +94,7 @@ struct l2_state {
     int max_split = 1;
     std::vector<l2::SkLaunch> plans;     // [layer][4] GEMV launches, planned once
     l2::SkParams* d_plans = nullptr;     // their parameter records on the device
+    l2::BatchBuffers* batch = nullptr;   // activations of the batched forward, allocated on first use
     cudaGraphExec_t graphs[l2::G_COUNT] = {nullptr, nullptr, nullptr, nullptr};
     int graph_nodes[l2::G_COUNT] = {0, 0, 0, 0};
     std::vector<void*> allocs;
@@ -94,6 +107,10 @@ struct l2_qlinear {
     int group_size = 128;
     float *x_dev = nullptr, *xp_dev = nullptr, *y_dev = nullptr;
     l2::SkParams* d_plan = nullptr;
+    uint8_t* img = nullptr;   // batched path: digit image, sums and factors
+    int* sv = nullptr;
+    float* osc = nullptr;
+    int* status = nullptr;
     int cap_b = 0;
     cudaStream_t stream = nullptr;
     std::vector<void*> allocs;
@@ -107,5 +124,9 @@ int check_attention_args(int n_heads, int n_kv_heads, int pos, const void* q, co
 int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, SkParams* d_plan, cudaStream_t st);
 int sk_plan(SkLaunch& L, int sms);
 void sk_prefetch_next(SkLaunch& L, const DevQ& q);
+int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos);
+int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const float* nw, float eps, int M, uint8_t* img, int* sv, float* osc,
+                 float* out, int ldo, int epi, int* status, cudaStream_t st);
+int dev_alloc_bytes(void** p, size_t bytes, std::vector<void*>& allocs);
 void sk_set_matrix(SkJob& j, int seg, const DevQ& q, const float* x, const float* nw);
 }  // namespace l2

@@ -1,0 +1,106 @@
+// Host side of the batched forward pass transformer<B>, B >= 2 (src/models.rs:178-298): the
+// sequence of launches for a chunk of M <= 64 tokens.  Every QLinear is a tcgen05 GEMM on exact
+// integer digits of the activations (gemm_tc.cu); no logits are produced, as in the reference.
+#include <cstring>
+
+#include "model.h"
+
+namespace l2 {
+
+int dev_alloc_bytes(void** p, size_t bytes, std::vector<void*>& allocs) {
+    L2_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+    allocs.push_back(*p);
+    return L2_OK;
+}
+
+// out[m][:] = QLinear(x[m][:]) for m < M.  gather: x is in natural order and is brought into the
+// matrix's K order through its g_index; nw (K order) folds an rmsnorm in.
+int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const float* nw, float eps, int M, uint8_t* img, int* sv,
+                 float* osc, float* out, int ldo, int epi, int* status, cudaStream_t st) {
+    const int mpad = (M + 3) & ~3;
+    QuantParams a{};
+    a.x = x; a.perm = gather ? q.perm : nullptr; a.nw = nw;
+    a.bimg = img; a.sv = sv; a.oscale = osc;
+    a.in = q.in; a.gs = q.gs; a.ldx = ldx; a.mpad = mpad; a.n = 4 * mpad; a.eps = eps;
+    launch_act_quant(a, M, st);
+    TcParams t{};
+    t.rec = q.rec; t.bimg = img; t.sv = sv; t.oscale = osc; t.out = out; t.status = status;
+    t.tiles16 = q.tiles; t.G = q.G; t.gs = q.gs; t.rows = q.out;
+    t.m = M; t.mpad = mpad; t.n = 4 * mpad; t.ldo = ldo; t.epi = epi;
+    L2_CUDA(launch_gemm_tc(t, st));
+    return L2_OK;
+}
+
+static int ensure_batch(l2_state* s) {
+    if (s->batch) return L2_OK;
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    const size_t B = MAX_BATCH, D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
+    const size_t kmax = std::max(D, H), gmax = kmax / c.group_size;
+    BatchBuffers* b = new BatchBuffers;
+    int rc = 0;
+    auto F = [&](float** p, size_t n) { return dev_alloc_bytes(reinterpret_cast<void**>(p), n * sizeof(float), s->allocs); };
+    if ((rc = F(&b->x, B * D)) || (rc = F(&b->q, B * D)) || (rc = F(&b->k, B * KV)) || (rc = F(&b->v, B * KV)) ||
+        (rc = F(&b->att, B * D)) || (rc = F(&b->h1, B * H)) || (rc = F(&b->h3, B * H)) || (rc = F(&b->hb, B * H))) { delete b; return rc; }
+    for (int i = 0; i < 3; i++) {
+        if ((rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->img[i]), 4 * B * kmax, s->allocs)) ||
+            (rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->sv[i]), gmax * B * 2 * sizeof(int), s->allocs)) ||
+            (rc = F(&b->osc[i], B))) { delete b; return rc; }
+        L2_CUDA(cudaMemset(b->img[i], 0, 4 * B * kmax));
+        L2_CUDA(cudaMemset(b->sv[i], 0, gmax * B * 2 * sizeof(int)));
+    }
+    if ((rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->tok), B * sizeof(int), s->allocs)) ||
+        (rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->pos), B * sizeof(int), s->allocs))) { delete b; return rc; }
+    if (cudaMallocHost(reinterpret_cast<void**>(&b->h_stage), sizeof(int) * 2 * B * CTL_RING) != cudaSuccess) { delete b; return fail(L2_ECUDA, "cudaMallocHost failed"); }
+    s->batch = b;
+    return L2_OK;
+}
+
+int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos) {
+    if (int rc = ensure_batch(s)) return rc;
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    BatchBuffers* b = s->batch;
+    cudaStream_t st = m->stream;
+    const int D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
+    int* status = &s->ctl->status;
+    // token ids and positions: own pinned slot per call until the copy has run
+    if (++b->stage_slot >= CTL_RING) { L2_CUDA(cudaStreamSynchronize(st)); b->stage_slot = 0; }
+    int* hs = b->h_stage + (size_t)b->stage_slot * 2 * MAX_BATCH;
+    memcpy(hs, tokens, sizeof(int) * M);
+    memcpy(hs + MAX_BATCH, pos, sizeof(int) * M);
+    L2_CUDA(cudaMemcpyAsync(b->tok, hs, sizeof(int) * M, cudaMemcpyHostToDevice, st));
+    L2_CUDA(cudaMemcpyAsync(b->pos, hs + MAX_BATCH, sizeof(int) * M, cudaMemcpyHostToDevice, st));
+    launch_embed_batch(m->tok_emb, b->tok, b->x, D, M, st);  // src/models.rs:189-191
+    const size_t ls = (size_t)c.seq_len * KV;
+    for (int l = 0; l < c.n_layers; l++) {
+        const DevLayer& y = m->layers[l];
+        int rc;
+        // rmsnorm + wq/wk/wv (:217-226)
+        if ((rc = gemm_batched(y.wq, b->x, D, true, y.nw_q, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->q, D, EPI_STORE, status, st))) return rc;
+        if ((rc = gemm_batched(y.wk, b->x, D, true, y.nw_k, m->eps, M, b->img[1], b->sv[1], b->osc[1], b->k, KV, EPI_STORE, status, st))) return rc;
+        if ((rc = gemm_batched(y.wv, b->x, D, true, y.nw_v, m->eps, M, b->img[2], b->sv[2], b->osc[2], b->v, KV, EPI_STORE, status, st))) return rc;
+        // rope, all rows into the cache, then attention (:228-256)
+        RopeParams r{};
+        r.q = b->q; r.k = b->k; r.v = b->v; r.kc = s->kc + (size_t)l * ls; r.vc = s->vc + (size_t)l * ls;
+        r.rope_cos = m->rope_cos; r.rope_sin = m->rope_sin; r.pos = b->pos;
+        r.n_kv_heads = c.n_kv_heads; r.ldq = D; r.ldkv = KV;
+        launch_rope_append(r, c.n_heads, M, st);
+        AttnBatchParams a{};
+        a.q = b->q; a.kc = r.kc; a.vc = r.vc; a.pos = b->pos; a.out = b->att;
+        a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups(); a.ldq = D; a.ldo = D;
+        launch_attn_batch(a, c.n_heads, M, st);
+        // wo + residual (:260-264)
+        if ((rc = gemm_batched(y.wo, b->att, D, true, nullptr, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->x, D, EPI_RESID, status, st))) return rc;
+        // rmsnorm + w1/w3 + SwiGLU (:266-276); their rows are stored in w2's K order
+        if ((rc = gemm_batched(y.w1, b->x, D, true, y.nw_1, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->h1, H, EPI_STORE, status, st))) return rc;
+        if ((rc = gemm_batched(y.w3, b->x, D, true, y.nw_3, m->eps, M, b->img[1], b->sv[1], b->osc[1], b->h3, H, EPI_STORE, status, st))) return rc;
+        launch_swiglu(b->h1, b->h3, b->hb, (size_t)M * H, st);
+        // w2 + residual (:279-285)
+        if ((rc = gemm_batched(y.w2, b->hb, H, false, nullptr, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->x, D, EPI_RESID, status, st))) return rc;
+    }
+    L2_CUDA(cudaGetLastError());
+    return L2_OK;
+}
+
+}  // namespace l2

@@ -1,0 +1,236 @@
+// Kernels of the batched forward pass transformer<B>, B >= 2 (src/models.rs:178-298), around the
+// tcgen05 GEMM of gemm_tc.cu: embedding rows, activation quantiser (rmsnorm folded in), RoPE +
+// cache append, causal attention over the cache, SwiGLU.  One CTA per token (and head).
+#include <cfloat>
+#include <cmath>
+
+#include "kernels.cuh"
+
+namespace l2 {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t kbyte, uint32_t gs) {
+    const uint32_t off = row * gs + kbyte;
+    return off ^ (((off >> 7) & ((gs >> 4) - 1)) << 4);
+}
+
+}  // namespace
+
+// ---- x[m] = token_embedding_table[tokens[m]] (src/models.rs:189-191) ---------------------------
+__global__ void embed_batch_kernel(const float* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int dim) {
+    const int m = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(table + (size_t)tokens[m] * dim);
+    float4* dst = reinterpret_cast<float4*>(x + (size_t)m * dim);
+    for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---- activation quantiser ---------------------------------------------------------------------
+// Token m of x (natural order) is gathered into the consumer's K order, multiplied by the rmsnorm
+// weight (linearity: the 1/sqrt(mean(x^2)+eps) factor goes into oscale), scaled by a power of two
+// so that |X| < 2^27 and written as four 7-bit digits (d0 = X >> 21 signed, d1..d3 in 0..127) into
+// the K-major, swizzled byte image the GEMM copies into shared memory: row 4*m + digit, inside a
+// block of 8 inputs the order (0,2,4,6,1,3,5,7) in which a weight word separates into nibbles.
+constexpr int AQ_THREADS = 256;
+
+__global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_constant__ QuantParams P) {
+    __shared__ float red[2 * (AQ_THREADS / 32) + 2];
+    const int m = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float* x = P.x + (size_t)m * P.ldx;
+    const int nblk = P.in / 8;
+    const uint32_t gs = P.gs, lanes_per_group = gs / 8;
+    auto fetch = [&](int blk, float (&v)[8], float& sq) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int k = blk * 8 + j;
+            const float xv = x[P.perm ? P.perm[k] : k];
+            sq += xv * xv;
+            v[j] = P.nw ? xv * P.nw[k] : xv;
+        }
+    };
+    float mx = 0.f, sq = 0.f;
+    for (int blk = tid; blk < nblk; blk += AQ_THREADS) {
+        float v[8];
+        fetch(blk, v, sq);
+#pragma unroll
+        for (int j = 0; j < 8; j++) mx = fmaxf(mx, fabsf(v[j]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    }
+    if (lane == 0) { red[warp] = mx; red[AQ_THREADS / 32 + warp] = sq; }
+    __syncthreads();
+    if (tid == 0) {
+        float a = 0.f, b = 0.f;
+        for (int w = 0; w < AQ_THREADS / 32; w++) { a = fmaxf(a, red[w]); b += red[AQ_THREADS / 32 + w]; }
+        red[2 * (AQ_THREADS / 32)] = a;
+        red[2 * (AQ_THREADS / 32) + 1] = b;
+    }
+    __syncthreads();
+    mx = red[2 * (AQ_THREADS / 32)];
+    const float total = red[2 * (AQ_THREADS / 32) + 1];
+    const float rs = P.nw ? 1.0f / sqrtf(total / (float)P.in + P.eps) : 1.0f;  // src/models.rs:58-60
+    int e = 0;
+    if (mx > 0.f && mx < INFINITY) e = 26 - (int)((__float_as_uint(mx) >> 23) & 255u) + 127;
+    e = max(-100, min(100, e));
+    const float scale = __uint_as_float((uint32_t)(127 + e) << 23);
+    if (tid == 0) P.oscale[m] = rs / scale;
+
+    const size_t img_group = (size_t)P.n * gs;  // bytes of one group's image
+    const int rounds = (nblk + AQ_THREADS - 1) / AQ_THREADS;
+    for (int k = 0; k < rounds; k++) {
+        const int blk = tid + k * AQ_THREADS;
+        if ((blk & ~31) >= nblk) break;  // warp-uniform
+        const bool valid = blk < nblk;
+        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        float dummy = 0.f;
+        if (valid) fetch(blk, v, dummy);
+        uint32_t E[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t X = (uint32_t)__float2int_rn(v[j] * scale);
+            E[j] = (X & 0x7Fu) | ((X << 1) & 0x7F00u) | ((X << 2) & 0x7F0000u) | ((X << 3) & 0xFF000000u);
+        }
+        uint32_t lo[4], hi[4];
+        {
+            const uint32_t a = __byte_perm(E[0], E[2], 0x5140), b = __byte_perm(E[0], E[2], 0x7362);
+            const uint32_t c = __byte_perm(E[4], E[6], 0x5140), d = __byte_perm(E[4], E[6], 0x7362);
+            lo[3] = __byte_perm(a, c, 0x5410); lo[2] = __byte_perm(a, c, 0x7632);
+            lo[1] = __byte_perm(b, d, 0x5410); lo[0] = __byte_perm(b, d, 0x7632);
+        }
+        {
+            const uint32_t a = __byte_perm(E[1], E[3], 0x5140), b = __byte_perm(E[1], E[3], 0x7362);
+            const uint32_t c = __byte_perm(E[5], E[7], 0x5140), d = __byte_perm(E[5], E[7], 0x7362);
+            hi[3] = __byte_perm(a, c, 0x5410); hi[2] = __byte_perm(a, c, 0x7632);
+            hi[1] = __byte_perm(b, d, 0x5410); hi[0] = __byte_perm(b, d, 0x7632);
+        }
+        const int g = valid ? (int)((uint32_t)(blk * 8) / gs) : 0;
+        const uint32_t kb = (uint32_t)(blk * 8) % gs;
+        int sum[4];
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            if (valid)
+                *reinterpret_cast<uint2*>(P.bimg + (size_t)g * img_group + swz((uint32_t)(4 * m + p), kb, gs)) = make_uint2(lo[p], hi[p]);
+            sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
+        }
+        int s01 = 128 * sum[0] + sum[1], s23 = 128 * sum[2] + sum[3];
+        for (uint32_t o = 1; o < lanes_per_group; o <<= 1) {
+            s01 += __shfl_xor_sync(0xffffffffu, s01, o);
+            s23 += __shfl_xor_sync(0xffffffffu, s23, o);
+        }
+        if (valid && (tid & (lanes_per_group - 1)) == 0) {
+            P.sv[((size_t)g * P.mpad + m) * 2] = s01;
+            P.sv[((size_t)g * P.mpad + m) * 2 + 1] = s23;
+        }
+    }
+}
+
+// ---- RoPE + cache append for M tokens (src/models.rs:100-129, 236-249) ----------------------------
+// grid (n_heads, M), 64 threads.  q is rotated in place; k (rotated) and v go to the cache rows.
+__global__ void __launch_bounds__(64) rope_append_kernel(const __grid_constant__ RopeParams P) {
+    const int h = blockIdx.x, m = blockIdx.y, i = threadIdx.x;
+    const int pos = P.pos[m];
+    const float c = P.rope_cos[(size_t)pos * (HS / 2) + i], s = P.rope_sin[(size_t)pos * (HS / 2) + i];
+    float* q = P.q + (size_t)m * P.ldq + (size_t)h * HS;
+    {
+        const float a = q[i], b = q[HS / 2 + i];
+        const float na = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+        const float nb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(na, s));  // second half uses the rotated first half
+        q[i] = na;
+        q[HS / 2 + i] = nb;
+    }
+    if (h < P.n_kv_heads) {
+        const int KV = P.n_kv_heads * HS;
+        const float* k = P.k + (size_t)m * P.ldkv + (size_t)h * HS;
+        const float* v = P.v + (size_t)m * P.ldkv + (size_t)h * HS;
+        const float a = k[i], b = k[HS / 2 + i];
+        const float na = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+        const float nb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(na, s));
+        float* kc = P.kc + (size_t)pos * KV + (size_t)h * HS;
+        float* vc = P.vc + (size_t)pos * KV + (size_t)h * HS;
+        kc[i] = na;
+        kc[HS / 2 + i] = nb;
+        vc[i] = v[i];
+        vc[HS / 2 + i] = v[HS / 2 + i];
+    }
+}
+
+// ---- attention of M tokens over the cache, causal through 0..=pos[m] (src/models.rs:131-176) ------
+// grid (n_heads, M), 128 threads: each warp walks the time steps t = warp, warp + 4, ... with an
+// online softmax; the four warps are merged in shared memory.
+__global__ void __launch_bounds__(128) attn_batch_kernel(const __grid_constant__ AttnBatchParams P) {
+    __shared__ __align__(16) float sm_acc[4][HS];
+    __shared__ float sm_m[4], sm_l[4];
+    const int h = blockIdx.x, m = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = h / P.ag, KV = P.n_kv_heads * HS;
+    const int T = P.pos[m] + 1;
+    const float4 q = reinterpret_cast<const float4*>(P.q + (size_t)m * P.ldq + (size_t)h * HS)[lane];
+    const float4* kc = reinterpret_cast<const float4*>(P.kc) + (size_t)kvh * (HS / 4) + lane;
+    const float4* vc = reinterpret_cast<const float4*>(P.vc) + (size_t)kvh * (HS / 4) + lane;
+    const size_t rs = (size_t)KV / 4;
+    const float div = sqrtf((float)HS);
+    float mx = -INFINITY, l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = warp; t < T; t += 4) {
+        const float4 k = kc[(size_t)t * rs], v = vc[(size_t)t * rs];
+        float d = warp_sum_f(q.x * k.x + q.y * k.y + q.z * k.z + q.w * k.w);
+        const float sc = __fdiv_rn(d, div);  // src/models.rs:158
+        const float mn = fmaxf(mx, sc);
+        const float corr = expf(mx - mn), pr = expf(sc - mn);
+        l = l * corr + pr;
+        acc.x = acc.x * corr + pr * v.x; acc.y = acc.y * corr + pr * v.y;
+        acc.z = acc.z * corr + pr * v.z; acc.w = acc.w * corr + pr * v.w;
+        mx = mn;
+    }
+    reinterpret_cast<float4*>(sm_acc[warp])[lane] = acc;
+    if (lane == 0) { sm_m[warp] = mx; sm_l[warp] = l; }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w = 0; w < 4; w++) M = fmaxf(M, sm_m[w]);
+    float L = 0.f, A = 0.f;
+    for (int w = 0; w < 4; w++) {
+        const float e = sm_m[w] == -INFINITY ? 0.f : expf(sm_m[w] - M);
+        L += sm_l[w] * e;
+        A += sm_acc[w][tid] * e;
+    }
+    P.out[(size_t)m * P.ldo + (size_t)h * HS + tid] = A / L;
+}
+
+// ---- hb = silu(h1) * h3 (src/models.rs:92-98) --------------------------------------------------------
+__global__ void swiglu_kernel(const float* __restrict__ h1, const float* __restrict__ h3, float* __restrict__ hb, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float a = h1[i];
+        hb[i] = (a * (1.0f / (1.0f + expf(-a)))) * h3[i];
+    }
+}
+
+void launch_embed_batch(const float* table, const int* tokens, float* x, int dim, int M, cudaStream_t st) {
+    g_launches++;
+    embed_batch_kernel<<<M, 256, 0, st>>>(table, tokens, x, dim);
+}
+void launch_act_quant(const QuantParams& p, int M, cudaStream_t st) {
+    g_launches++;
+    act_quant_kernel<<<M, AQ_THREADS, 0, st>>>(p);
+}
+void launch_rope_append(const RopeParams& p, int n_heads, int M, cudaStream_t st) {
+    g_launches++;
+    rope_append_kernel<<<dim3(n_heads, M), 64, 0, st>>>(p);
+}
+void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_t st) {
+    g_launches++;
+    attn_batch_kernel<<<dim3(n_heads, M), 128, 0, st>>>(p);
+}
+void launch_swiglu(const float* h1, const float* h3, float* hb, size_t n, cudaStream_t st) {
+    g_launches++;
+    swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(h1, h3, hb, n);
+}
+
+}  // namespace l2
