@@ -54,6 +54,8 @@ typedef struct l2_options {
     int32_t debug;          /* print the configuration, as LlamaModel::from_file(debug=true) does */
     int32_t max_batch;      /* largest B accepted by l2_forward / prefill chunk (0 = default 64) */
     int32_t flags;          /* L2_FLAG_* */
+    int32_t tp_rank;        /* tensor parallelism: this process's rank ... */
+    int32_t tp_world;       /* ... of tp_world processes, one per GPU of the box (0 or 1 = single GPU) */
 } l2_options;
 
 #define L2_FLAG_NO_GRAPH 1 /* launch kernels directly instead of replaying the per-token CUDA graph */
@@ -99,6 +101,17 @@ int l2_model_set_stream(l2_model* m, void* cuda_stream);
 /* Packed weight bytes one decode token must stream: all QLinear qweight+qzeros+scales,
  * the f32 classifier and the norm weights. */
 uint64_t l2_model_decode_bytes(const l2_model* m);
+
+/* ---- tensor parallelism (no counterpart in the reference, which is single-device) ------------
+ * One process per GPU.  Every QLinear is split by output rows (tp_world must divide the kv heads
+ * and leave whole 16-row tiles); vectors are re-assembled with NCCL all-gathers inside the token
+ * graph.  Rank 0 makes an id with l2_tp_unique_id, the host program hands the 128 bytes to every
+ * rank (torch.distributed, MPI, a file ...), and every rank calls l2_model_tp_connect on its model
+ * (opened with tp_rank / tp_world set) before the first forward. */
+int l2_tp_unique_id(void* id128);
+int l2_model_tp_connect(l2_model* m, const void* id128);
+/* Rows [row0, row0 + nrows) of a matrix of total_rows rows owned by `rank`. */
+int l2_tp_rows(int total_rows, int rank, int world, int* row0, int* nrows);
 
 /* ---- run state: RunState::new (src/models.rs:36-41) --------------------------------- */
 

@@ -13,7 +13,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 HOST_CXX = "/usr/bin/g++"
 
 CU_SOURCES = ["decode_kernels.cu", "gemv_kernels.cu", "gemm_tc.cu", "prefill_kernels.cu", "prefill.cu", "model.cu", "attention_noalloc.cu"]
-CPP_SOURCES = ["layout.cpp", "synth.cpp", "repack.cpp", "tokenizer.cpp"]
+CPP_SOURCES = ["layout.cpp", "synth.cpp", "repack.cpp", "tokenizer.cpp", "tp.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -47,7 +47,7 @@ def build(verbose=False, force=False):
             if r.returncode:
                 raise RuntimeError("nvcc failed on " + src)
     if force or _stale(OUT, objs):
-        cmd = [NVCC, "-shared", "-o", OUT] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-ccbin", HOST_CXX, "-lpthread"]
+        cmd = [NVCC, "-shared", "-o", OUT] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-ccbin", HOST_CXX, "-lpthread", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)

@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
 
     grid_dependency_wait();
     grid_launch_dependents();
-    const int kvh = blockIdx.x, split = blockIdx.y;
+    const int kvh = blockIdx.x + p.kvh0, split = blockIdx.y;
     const int pos = p.pos_fixed >= 0 ? p.pos_fixed : p.ctl->pos;
     const int T = pos + 1;
     int nsplit = (T + p.split_min - 1) / p.split_min;
@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_c
 void launch_attn(const AttnParams& p, cudaStream_t st, bool pdl) {
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
-    launch_cfg(cfg, attr, dim3(p.n_kv_heads, p.max_split), dim3(ATT_THREADS), 0, st, pdl);
+    launch_cfg(cfg, attr, dim3(p.n_kv_local > 0 ? p.n_kv_local : p.n_kv_heads, p.max_split), dim3(ATT_THREADS), 0, st, pdl);
     switch (p.ag) {
         case 1: cudaLaunchKernelEx(&cfg, attn_decode_kernel<1>, p); break;
         case 2: cudaLaunchKernelEx(&cfg, attn_decode_kernel<2>, p); break;
@@ -452,6 +452,28 @@ void launch_select(const SelectParams& p, cudaStream_t st, bool pdl) {
     cudaLaunchAttribute attr[1];
     launch_cfg(cfg, attr, dim3(1), dim3(SEL_THREADS), 0, st, pdl);
     cudaLaunchKernelEx(&cfg, select_kernel, p);
+}
+
+struct ScatterParams { const float* src; float* dst[3]; const int* idx[3]; int n, ndst; };
+
+__global__ void __launch_bounds__(256) scatter_kernel(const __grid_constant__ ScatterParams p) {
+    grid_dependency_wait();
+    grid_launch_dependents();
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < p.n) {
+        const float v = p.src[j];
+        for (int s = 0; s < p.ndst; s++) p.dst[s][p.idx[s][j]] = v;
+    }
+}
+
+void launch_scatter(const float* src, int n, float* const* dst, const int* const* idx, int ndst, cudaStream_t st, bool pdl) {
+    ScatterParams p{};
+    p.src = src; p.n = n; p.ndst = ndst;
+    for (int i = 0; i < ndst; i++) { p.dst[i] = dst[i]; p.idx[i] = idx[i]; }
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    launch_cfg(cfg, attr, dim3((n + 255) / 256), dim3(256), 0, st, pdl);
+    cudaLaunchKernelEx(&cfg, scatter_kernel, p);
 }
 
 __global__ void advance_kernel(Ctl* ctl) {

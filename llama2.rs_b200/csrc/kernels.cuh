@@ -125,6 +125,7 @@ struct AttnParams {
     float* out; const int* oidx;                     // attention output scattered into wo's K order (null: natural order)
     int n_kv_heads, ag, max_split, split_min;
     int pos_fixed;                                   // >= 0: use this position instead of ctl->pos
+    int kvh0, n_kv_local;                            // tensor parallelism: this launch covers kv heads [kvh0, kvh0 + n_kv_local); 0 local = all
 };
 
 struct ClsParams {
@@ -163,6 +164,8 @@ void launch_attn(const AttnParams& p, cudaStream_t st, bool pdl);
 void launch_cls(const ClsParams& p, int grid, cudaStream_t st, bool pdl);
 void launch_select(const SelectParams& p, cudaStream_t st, bool pdl);
 void launch_advance(Ctl* ctl, cudaStream_t st, bool pdl);
+// dst_i[idx_i[j]] = src[j] for j < n and up to three destinations (copies of a vector in consumers' K orders)
+void launch_scatter(const float* src, int n, float* const* dst, const int* const* idx, int ndst, cudaStream_t st, bool pdl);
 cudaError_t kernels_init();  // opt-in shared memory sizes; call once per device
 
 extern unsigned long long g_launches;

@@ -156,6 +156,11 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
     m->shape = shape;
     if (opt) m->opt = *opt;
     if (int rc = check_device(opt ? opt->device : -1, &m->device, &m->sms)) return rc;
+    m->tp_world = m->opt.tp_world > 1 ? m->opt.tp_world : 1;
+    m->tp_rank = m->tp_world > 1 ? m->opt.tp_rank : 0;
+    if (m->tp_rank < 0 || m->tp_rank >= m->tp_world) return fail(L2_EINVAL, "tp_rank %d outside 0..%d", m->tp_rank, m->tp_world - 1);
+    if (shape.c.n_kv_heads % m->tp_world || (shape.c.dim / m->tp_world) % 16 || (shape.c.hidden_dim / m->tp_world) % 16 || shape.c.hidden_dim % m->tp_world)
+        return fail(L2_EINVAL, "tp_world %d does not divide the kv heads / leave whole 16-row tiles", m->tp_world);
     m->use_graph = !(m->opt.flags & L2_FLAG_NO_GRAPH);
     m->use_pdl = !(m->opt.flags & L2_FLAG_NO_PDL);
     L2_CUDA(cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking));
@@ -196,11 +201,17 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
         const uint32_t* gx = src.get(t, l, S_GINDEX, s3);
         const int32_t* gidx = reinterpret_cast<const int32_t*>(gx);
         if (!is_permutation(gidx, in)) return fail(L2_EFORMAT, "tensor %d layer %d: g_index is not a permutation of 0..%d", t, l, in - 1);
+        // tensor parallelism: this process keeps rows [row0, row0 + nrows) of the (re-ordered) matrix
+        int row0 = 0, nrows = outn;
+        tp_rows(outn, m->tp_rank, m->tp_world, &row0, &nrows);
+        std::vector<int32_t> order(nrows);
+        for (int j = 0; j < nrows; j++) order[j] = rows_order ? rows_order[row0 + j] : row0 + j;
         PackedQ p;
-        repack_qlinear(in, outn, G, reinterpret_cast<const int32_t*>(qw), reinterpret_cast<const int32_t*>(qz),
-                       reinterpret_cast<const float*>(sc), rows_order, p);
+        repack_qlinear(in, nrows, G, reinterpret_cast<const int32_t*>(qw), reinterpret_cast<const int32_t*>(qz),
+                       reinterpret_cast<const float*>(sc), order.data(), p);
         if (keep_gi) keep_gi->assign(gidx, gidx + in);
-        qbytes += (shape.sub_words(t, S_QWEIGHT) + shape.sub_words(t, S_QZEROS) + shape.sub_words(t, S_SCALES)) * 4;
+        qbytes += (shape.sub_words(t, S_QWEIGHT) + shape.sub_words(t, S_QZEROS) + shape.sub_words(t, S_SCALES)) * 4 / m->tp_world;
+        d.row0 = row0;
         return upload_qlinear(p, gidx, d, m->allocs, tot);
     };
     auto permuted_norm = [&](const float* w, const std::vector<int32_t>& g, float** dst) -> int {
@@ -264,20 +275,23 @@ static int plan_layer_gemv(l2_state* s, int l, int which, SkLaunch& L) {
     L.gs = c.group_size;
     L.p.eps = m->eps;
     SkJob* j = L.p.job;
+    const bool tp = m->tp_world > 1;
     switch (which) {
         case 0:  // rmsnorm + wq/wk/wv (src/models.rs:217-226)
             L.p.njobs = 3;
-            sk_set_matrix(j[0], 0, y.wq, s->xq, y.nw_q); j[0].out = s->q; j[0].epi = EPI_STORE;
-            sk_set_matrix(j[1], 0, y.wk, s->xk, y.nw_k); j[1].out = s->k; j[1].epi = EPI_STORE;
-            sk_set_matrix(j[2], 0, y.wv, s->xv, y.nw_v); j[2].out = s->v; j[2].epi = EPI_STORE;
+            sk_set_matrix(j[0], 0, y.wq, s->xq, y.nw_q); j[0].out = s->q + y.wq.row0; j[0].epi = EPI_STORE;
+            sk_set_matrix(j[1], 0, y.wk, s->xk, y.nw_k); j[1].out = s->k + y.wk.row0; j[1].epi = EPI_STORE;
+            sk_set_matrix(j[2], 0, y.wv, s->xv, y.nw_v); j[2].out = s->v + y.wv.row0; j[2].epi = EPI_STORE;
             sk_prefetch_next(L, y.wo);
             break;
         case 1:  // wo + residual (:260-264); the new x goes to w1's and w3's K order as well
             L.p.njobs = 1;
-            sk_set_matrix(j[0], 0, y.wo, s->att, nullptr); j[0].out = s->x; j[0].epi = EPI_RESID;
-            j[0].sdst[0] = s->x1; j[0].sidx[0] = y.w1.inv;
-            j[0].sdst[1] = s->x3; j[0].sidx[1] = y.w3.inv;
-            j[0].nscatter = 2;
+            sk_set_matrix(j[0], 0, y.wo, s->att, nullptr); j[0].out = s->x + y.wo.row0; j[0].epi = EPI_RESID;
+            if (!tp) {  // with tensor parallelism the copies are made after the all-gather of x
+                j[0].sdst[0] = s->x1; j[0].sidx[0] = y.w1.inv;
+                j[0].sdst[1] = s->x3; j[0].sidx[1] = y.w3.inv;
+                j[0].nscatter = 2;
+            }
             sk_prefetch_next(L, y.w1);
             sk_prefetch_next(L, y.w3);
             break;
@@ -286,13 +300,13 @@ static int plan_layer_gemv(l2_state* s, int l, int which, SkLaunch& L) {
             L.nseg = 2;
             sk_set_matrix(j[0], 0, y.w1, s->x1, y.nw_1);
             sk_set_matrix(j[0], 1, y.w3, s->x3, y.nw_3);
-            j[0].out = s->hb; j[0].epi = EPI_SWIGLU;
+            j[0].out = s->hb + y.w1.row0; j[0].epi = EPI_SWIGLU;
             sk_prefetch_next(L, y.w2);
             break;
         default:  // w2 + residual (:279-285); the new x goes to the next layer's q/k/v K orders
             L.p.njobs = 1;
-            sk_set_matrix(j[0], 0, y.w2, s->hb, nullptr); j[0].out = s->x; j[0].epi = EPI_RESID;
-            set_scatter3(j[0].sdst, j[0].sidx, &j[0].nscatter, s, l + 1 < c.n_layers ? &m->layers[l + 1] : nullptr);
+            sk_set_matrix(j[0], 0, y.w2, s->hb, nullptr); j[0].out = s->x + y.w2.row0; j[0].epi = EPI_RESID;
+            if (!tp) set_scatter3(j[0].sdst, j[0].sidx, &j[0].nscatter, s, l + 1 < c.n_layers ? &m->layers[l + 1] : nullptr);
             if (l + 1 < c.n_layers) {
                 sk_prefetch_next(L, m->layers[l + 1].wq);
                 sk_prefetch_next(L, m->layers[l + 1].wk);
@@ -326,8 +340,9 @@ static void launch_attention(l2_state* s, int l, cudaStream_t st, bool pdl) {
     a.kc = s->kc + (size_t)l * ls; a.vc = s->vc + (size_t)l * ls;
     a.rope_cos = m->rope_cos; a.rope_sin = m->rope_sin;
     a.ctl = s->ctl; a.part = s->part; a.counter = s->counter;
-    a.out = s->att; a.oidx = y.wo.inv;
+    a.out = m->tp_world > 1 ? s->att_nat : s->att; a.oidx = m->tp_world > 1 ? nullptr : y.wo.inv;  // tensor parallel: natural order, gathered and permuted afterwards
     a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups();
+    a.n_kv_local = c.n_kv_heads / m->tp_world; a.kvh0 = m->tp_rank * a.n_kv_local;
     a.max_split = s->max_split; a.split_min = 64;
     a.pos_fixed = -1;
     launch_attn(a, st, pdl);
@@ -354,12 +369,38 @@ static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
         set_scatter3(e.sdst, e.sidx, &e.nscatter, s, &m->layers[0]);
         launch_embed(e, st, false);  // first node of the token: plain stream order
     }
+    const int T = m->tp_world;
     for (int l = 0; l < L; l++) {
+        const DevLayer& y = m->layers[l];
         launch_qkv(s, l, st, pdl);
         launch_attention(s, l, st, pdl);
+        if (T > 1) {  // every rank holds its heads' outputs: gather, then bring into wo's K order
+            if (int rc = tp_all_gather(m, s->att_nat, (size_t)D / T, st)) return rc;
+            float* dst[1] = {s->att};
+            const int* idx[1] = {y.wo.inv};
+            launch_scatter(s->att_nat, D, dst, idx, 1, st, false);
+        }
         launch_wo(s, l, st, pdl);
+        if (T > 1) {
+            if (int rc = tp_all_gather(m, s->x, (size_t)D / T, st)) return rc;
+            float* dst[2] = {s->x1, s->x3};
+            const int* idx[2] = {y.w1.inv, y.w3.inv};
+            launch_scatter(s->x, D, dst, idx, 2, st, false);
+        }
         launch_w13(s, l, st, pdl);
-        launch_w2(s, l, st, pdl);
+        if (T > 1) {
+            if (int rc = tp_all_gather(m, s->hb, (size_t)c.hidden_dim / T, st)) return rc;
+        }
+        launch_w2(s, l, st, T > 1 ? false : pdl);
+        if (T > 1) {
+            if (int rc = tp_all_gather(m, s->x, (size_t)D / T, st)) return rc;
+            if (l + 1 < L) {
+                const DevLayer& nx = m->layers[l + 1];
+                float* dst[3] = {s->xq, s->xk, s->xv};
+                const int* idx[3] = {nx.wq.inv, nx.wk.inv, nx.wv.inv};
+                launch_scatter(s->x, D, dst, idx, 3, st, false);
+            }
+        }
     }
     if (kind == G_DECODE || kind == G_FWD_CLS) launch_classifier(s, st, pdl);  // final rmsnorm + classifier (:288-297)
     if (kind == G_DECODE) {
@@ -374,7 +415,9 @@ static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
 }
 
 static int nodes_per_forward(const l2_model* m, int kind) {
-    int n = 1 + 5 * m->shape.c.n_layers;
+    const int L = m->shape.c.n_layers;
+    int n = 1 + 5 * L;
+    if (m->tp_world > 1) n += 3 * L - 1;  // the copies into the consumers' K orders after each all-gather
     if (kind == G_DECODE) n += 2;
     if (kind == G_FWD_CLS || kind == G_FEED) n += 1;
     return n;
@@ -511,6 +554,7 @@ extern "C" void l2_model_close(l2_model* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     if (m->gen_state) l2_state_free(m->gen_state);
+    tp_disconnect(m);
     free_allocs(m->allocs);
     if (m->own_stream) cudaStreamDestroy(m->own_stream);
     delete m;
@@ -546,7 +590,7 @@ extern "C" int l2_state_new(l2_model* m, l2_state** out) {
     auto A = [&](float** p, size_t n) { return dev_alloc(reinterpret_cast<void**>(p), n * sizeof(float), s->allocs); };
     int rc = 0;
     if ((rc = A(&s->kc, kvn)) || (rc = A(&s->vc, kvn)) || (rc = A(&s->x, D)) || (rc = A(&s->xq, D)) || (rc = A(&s->xk, D)) ||
-        (rc = A(&s->xv, D)) || (rc = A(&s->q, D)) || (rc = A(&s->k, KV)) || (rc = A(&s->v, KV)) || (rc = A(&s->att, D)) ||
+        (rc = A(&s->xv, D)) || (rc = A(&s->q, D)) || (rc = A(&s->k, KV)) || (rc = A(&s->v, KV)) || (rc = A(&s->att, D)) || (rc = A(&s->att_nat, D)) ||
         (rc = A(&s->x1, D)) || (rc = A(&s->x3, D)) || (rc = A(&s->hb, H)) || (rc = A(&s->logits, c.vocab_size))) {
         free_allocs(s->allocs);
         return rc;
@@ -649,6 +693,13 @@ extern "C" int l2_forward(l2_model* m, l2_state* s, const int32_t* tokens, const
     if (B == 1) {
         if (int rc = write_ctl(s, pos[0], tokens[0], 0, -1, 0.f, 0)) return rc;
         if (int rc = run_forward(s, logits ? G_FWD_CLS : G_FWD)) return rc;
+    } else if (m->tp_world > 1) {
+        // one row at a time, each seeing the rows before it: equal to the reference when positions ascend
+        for (int b = 0; b < B; b++) {
+            if (b && pos[b] <= pos[b - 1]) return fail(L2_EINVAL, "l2_forward: tensor parallel batches need ascending positions");
+            if (int rc = write_ctl(s, pos[b], tokens[b], 0, -1, 0.f, 0)) return rc;
+            if (int rc = run_forward(s, G_FWD)) return rc;
+        }
     } else if (int rc = forward_batch(s, B, tokens, pos)) {  // all rows stored, then attention over 0..=pos[b]
         return rc;
     }
@@ -671,7 +722,8 @@ static int prefill_async(l2_model* m, l2_state* s, const int32_t* prompt, int n_
     int pos = 0;
     int32_t tokens[MAX_BATCH], positions[MAX_BATCH];
     while (pos < target) {
-        const int A = std::min<int>(MAX_BATCH, target - pos);
+        // tensor parallel models take the prompt one position at a time (the batched GEMM is single-GPU)
+        const int A = m->tp_world > 1 ? 1 : std::min<int>(MAX_BATCH, target - pos);
         for (int i = 0; i < A; i++) {
             tokens[i] = pos == 0 ? L2_START : prompt[pos - 1];  // src/inference.rs:29-35
             positions[i] = pos++;

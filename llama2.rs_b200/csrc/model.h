@@ -24,7 +24,8 @@ struct DevQ {
     uint32_t* rec = nullptr;   // [tiles][G] unit records: weights, scales, zero nibbles (see repack.cpp)
     int* perm = nullptr;  // g_index: permuted position j reads input perm[j]
     int* inv = nullptr;   // inverse: input o is written to permuted position inv[o]
-    int in = 0, out = 0, tiles = 0, G = 0, gs = 0;
+    int in = 0, out = 0, tiles = 0, G = 0, gs = 0;  // out / tiles: the rows held by this process
+    int row0 = 0;                                   // first row held (tensor parallelism), else 0
 };
 
 // A planned GEMV launch: parameters, grid and shared memory.
@@ -76,6 +77,8 @@ struct l2_model {
     size_t device_bytes = 0;
     l2_state* gen_state = nullptr;  // reused by l2_generate_ids
     bool use_graph = true, use_pdl = true;
+    int tp_rank = 0, tp_world = 1;   // tensor parallelism: this process owns 1/tp_world of every matrix's rows
+    void* nccl_comm = nullptr;
 };
 
 struct l2_state {
@@ -83,6 +86,7 @@ struct l2_state {
     float *kc = nullptr, *vc = nullptr;  // [L][SEQ][KVH][HS]
     float *x = nullptr, *xq = nullptr, *xk = nullptr, *xv = nullptr;
     float *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr;
+    float* att_nat = nullptr;  // tensor parallelism: attention output in natural order before it is gathered
     float *x1 = nullptr, *x3 = nullptr, *hb = nullptr, *logits = nullptr;
     float* part = nullptr;
     unsigned* counter = nullptr;
@@ -125,6 +129,10 @@ int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, SkParams*
 int sk_plan(SkLaunch& L, int sms);
 void sk_prefetch_next(SkLaunch& L, const DevQ& q);
 int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos);
+struct NcclId { char bytes[128]; };  // ncclUniqueId
+int tp_all_gather(l2_model* m, float* buf, size_t count, cudaStream_t st);
+void tp_disconnect(l2_model* m);
+void tp_rows(int total_rows, int rank, int world, int* row0, int* nrows);
 int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const float* nw, float eps, int M, uint8_t* img, int* sv, float* osc,
                  float* out, int ldo, int epi, int* status, cudaStream_t st);
 int dev_alloc_bytes(void** p, size_t bytes, std::vector<void*>& allocs);

@@ -25,6 +25,13 @@ __all__ = ["LlamaModel", "Tokenizer", "Random", "Config", "generate", "generate_
            "START", "RET", "preset_config", "checkpoint_bytes", "synth_fill", "synth_write_file", "L2Error"]
 
 
+def tp_unique_id():
+    """128-byte NCCL id made on rank 0, to be handed to every rank's LlamaModel.tp_connect."""
+    buf = C.create_string_buffer(128)
+    check(lib.l2_tp_unique_id(buf))
+    return buf.raw
+
+
 def preset_config(model_size, group_size):
     c = Config()
     check(lib.l2_preset_config(model_size.encode(), group_size, C.byref(c)))
@@ -47,7 +54,7 @@ def synth_write_file(config, seed, path, threads=0):
     check(lib.l2_synth_write_file(C.byref(config), seed, str(path).encode(), threads))
 
 
-def _options(model_size, group_size, attn_groups, device, debug, max_batch, flags):
+def _options(model_size, group_size, attn_groups, device, debug, max_batch, flags, tp=(0, 1)):
     o = Options()
     o.model_size = model_size.encode() if model_size else None
     o.group_size = group_size
@@ -56,6 +63,7 @@ def _options(model_size, group_size, attn_groups, device, debug, max_batch, flag
     o.debug = int(bool(debug))
     o.max_batch = max_batch
     o.flags = flags
+    o.tp_rank, o.tp_world = tp
     return o
 
 
@@ -63,12 +71,12 @@ class LlamaModel:
     """LlamaModel (src/lib.rs:28-77): LlamaModel(checkpoint, debug=False)."""
 
     def __init__(self, checkpoint=None, debug=False, *, model_size=None, group_size=128, attn_groups=1, device=-1,
-                 max_batch=0, flags=0, _handle=None):
+                 max_batch=0, flags=0, tp=(0, 1), _handle=None):
         self._h = C.c_void_p()
         if _handle is not None:
             self._h = _handle
         else:
-            o = _options(model_size, group_size, attn_groups, device, debug, max_batch, flags)
+            o = _options(model_size, group_size, attn_groups, device, debug, max_batch, flags, tp)
             check(lib.l2_model_open(str(checkpoint).encode(), C.byref(o), C.byref(self._h)))
         self.config = Config()
         check(lib.l2_model_config(self._h, C.byref(self.config)))
@@ -78,23 +86,28 @@ class LlamaModel:
         return cls(checkpoint, debug, **kw)
 
     @classmethod
-    def from_blob(cls, config, payload, *, device=-1, debug=False, max_batch=0, flags=0):
+    def from_blob(cls, config, payload, *, device=-1, debug=False, max_batch=0, flags=0, tp=(0, 1)):
         """The same on the bytes after the header (numpy uint8 array in the export.py layout)."""
         h = C.c_void_p()
-        o = _options(None, config.group_size, config.n_heads // config.n_kv_heads, device, debug, max_batch, flags)
+        o = _options(None, config.group_size, config.n_heads // config.n_kv_heads, device, debug, max_batch, flags, tp)
         check(lib.l2_model_open_blob(C.byref(config), payload.ctypes.data_as(C.c_void_p), payload.nbytes, C.byref(o), C.byref(h)))
         return cls(_handle=h)
 
     @classmethod
-    def synthetic(cls, config, seed, *, device=-1, debug=False, max_batch=0, flags=0):
+    def synthetic(cls, config, seed, *, device=-1, debug=False, max_batch=0, flags=0, tp=(0, 1)):
         """Seeded synthetic checkpoint generated tensor by tensor straight onto the device."""
         h = C.c_void_p()
-        o = _options(None, config.group_size, config.n_heads // config.n_kv_heads, device, debug, max_batch, flags)
+        o = _options(None, config.group_size, config.n_heads // config.n_kv_heads, device, debug, max_batch, flags, tp)
         check(lib.l2_model_open_synthetic(C.byref(config), seed, C.byref(o), C.byref(h)))
         return cls(_handle=h)
 
     def prefill(self):
         return bool(lib.l2_model_prefill(self._h))
+
+    def tp_connect(self, id_bytes):
+        """Joins the NCCL communicator of a tensor-parallel model; id_bytes comes from tp_unique_id() on rank 0."""
+        buf = C.create_string_buffer(bytes(id_bytes), 128)
+        check(lib.l2_model_tp_connect(self._h, buf))
 
     def set_stream(self, cuda_stream):
         check(lib.l2_model_set_stream(self._h, C.c_void_p(cuda_stream)))

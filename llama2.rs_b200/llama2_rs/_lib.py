@@ -27,7 +27,8 @@ class Config(C.Structure):
 
 class Options(C.Structure):
     _fields_ = [("model_size", C.c_char_p), ("group_size", C.c_int32), ("attn_groups", C.c_int32),
-                ("device", C.c_int32), ("debug", C.c_int32), ("max_batch", C.c_int32), ("flags", C.c_int32)]
+                ("device", C.c_int32), ("debug", C.c_int32), ("max_batch", C.c_int32), ("flags", C.c_int32),
+                ("tp_rank", C.c_int32), ("tp_world", C.c_int32)]
 
 
 FLAG_NO_GRAPH = 1
@@ -56,6 +57,9 @@ SIGNATURES = {
     "l2_model_prefill": (C.c_int, [_vp]),
     "l2_model_set_stream": (C.c_int, [_vp, _vp]),
     "l2_model_decode_bytes": (C.c_uint64, [_vp]),
+    "l2_tp_unique_id": (C.c_int, [_vp]),
+    "l2_model_tp_connect": (C.c_int, [_vp, _vp]),
+    "l2_tp_rows": (C.c_int, [C.c_int, C.c_int, C.c_int, _p(C.c_int), _p(C.c_int)]),
     "l2_state_new": (C.c_int, [_vp, _p(_vp)]),
     "l2_state_reset": (C.c_int, [_vp]),
     "l2_state_free": (None, [_vp]),

@@ -1,0 +1,57 @@
+"""One rank of the tensor-parallel parity check; run under torch.distributed.run with N ranks.
+Each rank owns 1/N of every matrix's rows on its own GPU and must reproduce the CPU oracle's
+per-step logits and greedy stream, bit-identically across ranks."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "llama2.rs_b200"))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+import llama2_rs as l2  # noqa: E402
+import oracle as orc  # noqa: E402
+from conftest import assert_close, tiny_config  # noqa: E402
+
+
+def run_case(cfg, rank, world, steps, n_prompt, seed):
+    payload = l2.synth_fill(cfg, seed)
+    gpu = l2.LlamaModel.from_blob(cfg, payload, device=rank, tp=(rank, world))
+    ids = [l2.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    gpu.tp_connect(ids[0])
+    prompt = np.random.default_rng(seed).integers(0, cfg.vocab_size, n_prompt).astype(np.int32)
+    got = l2.generate_ids(gpu, prompt, steps, trace_logits=True)
+    fast = l2.generate_ids(gpu, prompt, steps)
+    want = orc.Model(cfg, payload).generate_ids(prompt, steps, trace_logits=True)
+    assert got["pos0"] == want["pos0"]
+    assert_close(got["logits"], want["logits"], what="rank %d logits" % rank)
+    assert np.array_equal(got["tokens"], want["tokens"]) and np.array_equal(fast["tokens"], want["tokens"])
+    # bit-identical on every rank: nothing is summed across ranks
+    mine = torch.from_numpy(got["logits"].copy())
+    ref = mine.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(mine, ref), "rank %d differs from rank 0" % rank
+    gpu.close()
+
+
+def main():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.cuda.set_device(rank)
+    cfg = tiny_config(l2, group_size=64, n_kv_heads=2, dim=512, hidden=1024, n_layers=2)
+    cfg.n_heads, cfg.n_kv_heads = 4, world if world in (1, 2, 4) else 4
+    run_case(cfg, rank, world, steps=40, n_prompt=21, seed=11)
+    big = l2.preset_config("70B", 64)  # the real 70B projection shapes and GQA, two layers, small vocabulary
+    big.n_layers, big.vocab_size, big.seq_len = 2, 2048, 128
+    run_case(big, rank, world, steps=24, n_prompt=9, seed=12)
+    dist.barrier()
+    if rank == 0:
+        print("tp parity ok on %d ranks" % world)
+
+
+if __name__ == "__main__":
+    main()
