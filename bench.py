@@ -124,19 +124,24 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="7b", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(WORKLOADS),
+                    help="auto: 7b on one GPU, 70b tensor-parallel over all ranks on several")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-warmup", type=int, default=3, help="profiling runs may lower the warm-up floor")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload == "auto":
+        args.workload = "7b" if world == 1 else "70b"
+    tp = world > 1 and args.workload == "70b"  # 70B is sharded over the ranks; smaller models run as replicas
     size, gs, n_prompt, n_decode = WORKLOADS[args.workload]
     config = {"workload": "Llama2-%s GPTQ 4-bit g%d act-order, %d-token random prompt, %d greedy decode tokens, batch 1"
                           % (size, gs, n_prompt, n_decode),
               "weights": "seeded synthetic checkpoint (seed %d) in the export.py .bin layout" % WEIGHT_SEED,
               "l2": "weights streamed per token (%s) exceed the 126 MB L2; no flush needed" % size,
-              "parallelism": "replicas" if world > 1 else "single GPU"}
+              "parallelism": ("tp%d: every QLinear split by output rows, NCCL all-gathers in the token graph" % world) if tp
+              else ("replicas" if world > 1 else "single GPU")}
 
     if args.impl == "reference":
         if rank != 0:
@@ -164,7 +169,14 @@ def main():
     cfg = l2.preset_config(size, gs)
     need_payload = rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "70b"
     payload = l2.synth_fill(cfg, WEIGHT_SEED) if need_payload else None
-    model = l2.LlamaModel.from_blob(cfg, payload, device=dev) if payload is not None else l2.LlamaModel.synthetic(cfg, WEIGHT_SEED, device=dev)
+    if payload is not None:
+        model = l2.LlamaModel.from_blob(cfg, payload, device=dev)
+    else:
+        model = l2.LlamaModel.synthetic(cfg, WEIGHT_SEED, device=dev, tp=(rank, world) if tp else (0, 1))
+    if tp:
+        ids = [l2.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        model.tp_connect(ids[0])
     stream = torch.cuda.Stream(device=dev)
     model.set_stream(stream.cuda_stream)
     state = l2.RunState(model)
@@ -216,7 +228,8 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     decode_ms, prefill_ms = t.tolist()
-    value = world * n_loop * args.steps / decode_ms * 1e3
+    streams = 1 if tp else world  # token streams running side by side: replicas add up, a tensor-parallel group is one
+    value = streams * n_loop * args.steps / decode_ms * 1e3
 
     # end to end: the host drives every token through l2_decode_step (host buffers in and out)
     state.reset()
@@ -228,7 +241,7 @@ def main():
         forced = int(prompt[p]) if p < n_prompt else -1
         tok, _ = l2.decode_step(model, state, tok, p, forced_next=forced)
     e2e_s = time.perf_counter() - t0
-    e2e = {"value": world * n_loop / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 40 * n_loop, "d2h_bytes_per_step": 40 * n_loop,
+    e2e = {"value": streams * n_loop / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 40 * n_loop, "d2h_bytes_per_step": 40 * n_loop,
            "note": "one l2_decode_step call per token: 40-byte loop record up, 40-byte record (chosen token) back"}
 
     if rank != 0:
@@ -236,12 +249,12 @@ def main():
     peak, peak_kind = measured_peaks()
     dom_bytes = int(l2.lib.l2_projection_bytes(model._h, 2))
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-    tok_s = value / world
+    tok_s = value / streams
     out = {
         "metric": "batch-1 decode tok/s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": max(args.min_warmup, args.warmup), "ms_per_step": (decode_ms + prefill_ms) / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations / int4 weights", "data": "synthetic", "config": config,
-        "prefill_tok_s": world * pos0 * args.steps / max(prefill_ms, 1e-9) * 1e3,
+        "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32 activations / int4 weights", "data": "synthetic", "config": config,
+        "prefill_tok_s": streams * pos0 * args.steps / max(prefill_ms, 1e-9) * 1e3,
         "decode_ms_per_token": decode_ms / (n_loop * args.steps),
         "roofline": {"bound": "hbm", "kernel": "gemv_q4 (w1/w3 + SwiGLU)", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,

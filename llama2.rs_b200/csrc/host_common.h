@@ -53,6 +53,8 @@ struct Source {
     virtual ~Source() {}
     // Returns a pointer to `words` words of (t, layer, sub); may use `scratch` as backing store.
     virtual const uint32_t* get(int t, int layer, int sub, std::vector<uint32_t>& scratch) = 0;
+    // Rows rows[0..n) of QLinear tensor t, compactly: qw [n][in/8], sc [n][groups], zn [n][groups] (zero nibbles).
+    virtual void get_rows(int t, int layer, const int32_t* rows, int n, uint32_t* qw, float* sc, uint8_t* zn) = 0;
 };
 
 struct BlobSource : Source {
@@ -62,6 +64,7 @@ struct BlobSource : Source {
     const uint32_t* get(int t, int layer, int sub, std::vector<uint32_t>&) override {
         return base + shape.offset_words(t, layer, sub);
     }
+    void get_rows(int t, int layer, const int32_t* rows, int n, uint32_t* qw, float* sc, uint8_t* zn) override;
 };
 
 struct SynthSource : Source {
@@ -70,10 +73,14 @@ struct SynthSource : Source {
     int threads;
     SynthSource(const Shape& s, uint64_t sd, int th) : shape(s), seed(sd), threads(th) {}
     const uint32_t* get(int t, int layer, int sub, std::vector<uint32_t>& scratch) override;
+    // generates only the requested rows (a tensor-parallel rank needs 1/T of every matrix)
+    void get_rows(int t, int layer, const int32_t* rows, int n, uint32_t* qw, float* sc, uint8_t* zn) override;
 };
 
 // Fills `dst` with field `sub` of layer `layer` of tensor `t` of the seeded synthetic checkpoint.
 void synth_tensor(const Shape& s, uint64_t seed, int t, int layer, int sub, uint32_t* dst, int threads);
+// Words [first, first + count) of a QLinear field (S_QWEIGHT, S_QZEROS or S_SCALES), single-threaded.
+void synth_range(const Shape& s, uint64_t seed, int t, int layer, int sub, size_t first, size_t count, uint32_t* dst);
 int default_threads();
 
 // Splits [0, n) into contiguous ranges and runs fn(begin, end) on `threads` host threads.

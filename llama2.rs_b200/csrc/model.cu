@@ -195,9 +195,6 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
     auto load_q = [&](int t, int l, DevQ& d, const int32_t* rows_order, std::vector<int32_t>* keep_gi) -> int {
         int in, outn;
         shape.qdims(t, &in, &outn);
-        const uint32_t* qw = src.get(t, l, S_QWEIGHT, s0);
-        const uint32_t* qz = src.get(t, l, S_QZEROS, s1);
-        const uint32_t* sc = src.get(t, l, S_SCALES, s2);
         const uint32_t* gx = src.get(t, l, S_GINDEX, s3);
         const int32_t* gidx = reinterpret_cast<const int32_t*>(gx);
         if (!is_permutation(gidx, in)) return fail(L2_EFORMAT, "tensor %d layer %d: g_index is not a permutation of 0..%d", t, l, in - 1);
@@ -206,9 +203,13 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
         tp_rows(outn, m->tp_rank, m->tp_world, &row0, &nrows);
         std::vector<int32_t> order(nrows);
         for (int j = 0; j < nrows; j++) order[j] = rows_order ? rows_order[row0 + j] : row0 + j;
+        const size_t g = Shape::groups(in, G);
+        s0.resize((size_t)nrows * (in / 8));
+        s1.resize((size_t)nrows * g);
+        std::vector<uint8_t> zn((size_t)nrows * g);
+        src.get_rows(t, l, order.data(), nrows, s0.data(), reinterpret_cast<float*>(s1.data()), zn.data());
         PackedQ p;
-        repack_qlinear(in, nrows, G, reinterpret_cast<const int32_t*>(qw), reinterpret_cast<const int32_t*>(qz),
-                       reinterpret_cast<const float*>(sc), order.data(), p);
+        repack_compact(in, nrows, G, s0.data(), reinterpret_cast<const float*>(s1.data()), zn.data(), p);
         if (keep_gi) keep_gi->assign(gidx, gidx + in);
         qbytes += (shape.sub_words(t, S_QWEIGHT) + shape.sub_words(t, S_QZEROS) + shape.sub_words(t, S_SCALES)) * 4 / m->tp_world;
         d.row0 = row0;
@@ -546,7 +547,8 @@ extern "C" int l2_model_open_synthetic(const l2_config* c, uint64_t seed, const 
     if (!c || !out) return fail(L2_EINVAL, "l2_model_open_synthetic: null argument");
     if (int rc = validate_config(*c)) return rc;
     Shape s{*c};
-    SynthSource src(s, seed, default_threads());
+    const int world = opt && opt->tp_world > 1 ? opt->tp_world : 1;
+    SynthSource src(s, seed, std::max(1, default_threads() / world));  // ranks of one box share the host cores
     return build_model(s, src, opt, out);
 }
 

@@ -17,31 +17,53 @@
 
 namespace l2 {
 
-void repack_qlinear(int in, int out, int gs, const int32_t* qweight, const int32_t* qzeros,
-                    const float* scales, const int32_t* rows_order, PackedQ& dst) {
+// Core: rows given compactly -- qw [n][in/8] words, sc [n][groups] scales, zn [n][groups] zero nibbles
+// (one byte each) -- in the order they take on the device.
+void repack_compact(int in, int n, int gs, const uint32_t* qw, const float* sc, const uint8_t* zn, PackedQ& dst) {
     const int g = (int)Shape::groups(in, gs);
     const int w = gs / 32;
-    const int wpr = in / 8;        // words per checkpoint row
+    const int wpr = in / 8;        // words per row
     const int wpg = gs / 8;        // words per group
-    const int tiles = (out + 15) / 16;
-    dst.in = in; dst.out = out; dst.groups = g; dst.tiles = tiles; dst.w = w;
+    const int tiles = (n + 15) / 16;
+    dst.in = in; dst.out = n; dst.groups = g; dst.tiles = tiles; dst.w = w;
     const size_t uw = (size_t)dst.unit_words();
     dst.rec.assign((size_t)tiles * g * uw, 0);
-    const uint32_t* qws = reinterpret_cast<const uint32_t*>(qweight);
-    const uint32_t* qzs = reinterpret_cast<const uint32_t*>(qzeros);
-    for (int j = 0; j < out; j++) {
-        const int src = rows_order ? rows_order[j] : j;
+    for (int j = 0; j < n; j++) {
         const int tile = j / 16, h = (j % 16) / 8, r = j % 8;
         for (int k = 0; k < g; k++) {
             const size_t unit = (size_t)tile * g + k;
             for (int t = 0; t < 4; t++)
                 for (int i = 0; i < w; i++)
-                    dst.rec[unit * uw + (size_t)h * 32 * w + (size_t)(r * 4 + t) * w + i] = qws[(size_t)src * wpr + (size_t)k * wpg + t * w + i];
-            memcpy(&dst.rec[unit * uw + 64 * w + (j % 16)], &scales[(size_t)src * g + k], 4);
-            const uint32_t nib = (qzs[(size_t)(src / 8) * g + k] >> (4 * (src % 8))) & 15u;
-            dst.rec[unit * uw + 64 * w + 16 + h] |= nib << (4 * r);
+                    dst.rec[unit * uw + (size_t)h * 32 * w + (size_t)(r * 4 + t) * w + i] = qw[(size_t)j * wpr + (size_t)k * wpg + t * w + i];
+            memcpy(&dst.rec[unit * uw + 64 * w + (j % 16)], &sc[(size_t)j * g + k], 4);
+            dst.rec[unit * uw + 64 * w + 16 + h] |= (uint32_t)(zn[(size_t)j * g + k] & 15u) << (4 * r);
         }
     }
+}
+
+// Rows `rows[0..n)` of a QLinear in checkpoint layout, compactly (see repack_compact).
+void gather_rows(int in, int gs, const uint32_t* qweight, const uint32_t* qzeros, const float* scales,
+                 const int32_t* rows, int n, uint32_t* qw, float* sc, uint8_t* zn) {
+    const int g = (int)Shape::groups(in, gs), wpr = in / 8;
+    for (int j = 0; j < n; j++) {
+        const int src = rows[j];
+        memcpy(qw + (size_t)j * wpr, qweight + (size_t)src * wpr, sizeof(uint32_t) * wpr);
+        memcpy(sc + (size_t)j * g, scales + (size_t)src * g, sizeof(float) * g);
+        for (int k = 0; k < g; k++) zn[(size_t)j * g + k] = (uint8_t)((qzeros[(size_t)(src / 8) * g + k] >> (4 * (src % 8))) & 15u);
+    }
+}
+
+void repack_qlinear(int in, int out, int gs, const int32_t* qweight, const int32_t* qzeros,
+                    const float* scales, const int32_t* rows_order, PackedQ& dst) {
+    const int g = (int)Shape::groups(in, gs);
+    std::vector<int32_t> rows(out);
+    for (int j = 0; j < out; j++) rows[j] = rows_order ? rows_order[j] : j;
+    std::vector<uint32_t> qw((size_t)out * (in / 8));
+    std::vector<float> sc((size_t)out * g);
+    std::vector<uint8_t> zn((size_t)out * g);
+    gather_rows(in, gs, reinterpret_cast<const uint32_t*>(qweight), reinterpret_cast<const uint32_t*>(qzeros), scales,
+                rows.data(), out, qw.data(), sc.data(), zn.data());
+    repack_compact(in, out, gs, qw.data(), sc.data(), zn.data(), dst);
 }
 
 std::vector<int32_t> inverse_permutation(const int32_t* perm, int n) {

@@ -24,6 +24,9 @@ struct PackedQ {
 // the last tile are zero (weights, scales and zero nibbles), so they contribute nothing.
 void repack_qlinear(int in, int out, int gs, const int32_t* qweight, const int32_t* qzeros,
                     const float* scales, const int32_t* rows_order, PackedQ& dst);
+void repack_compact(int in, int n, int gs, const uint32_t* qw, const float* sc, const uint8_t* zn, PackedQ& dst);
+void gather_rows(int in, int gs, const uint32_t* qweight, const uint32_t* qzeros, const float* scales,
+                 const int32_t* rows, int n, uint32_t* qw, float* sc, uint8_t* zn);
 std::vector<int32_t> inverse_permutation(const int32_t* perm, int n);
 bool is_permutation(const int32_t* perm, int n);
 

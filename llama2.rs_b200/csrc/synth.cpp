@@ -8,6 +8,7 @@
 #include <cstring>
 
 #include "host_common.h"
+#include "repack.h"
 
 namespace l2 {
 
@@ -52,6 +53,31 @@ static void fill_gindex(int32_t* dst, int in, int gs, uint64_t key) {
     for (int k = 0; k < in; k++) dst[count[perm[k] / gs]++] = k;
 }
 
+void synth_range(const Shape& s, uint64_t seed, int t, int layer, int sub, size_t first, size_t count, uint32_t* dst) {
+    (void)s;
+    const uint64_t key = stream_key(seed, t, layer, sub);
+    float* f = reinterpret_cast<float*>(dst);
+    switch (sub) {
+        case S_QWEIGHT:  // 8 i.i.d. nibbles per word
+            for (size_t i = 0; i < count; i++) dst[i] = (uint32_t)(draw(key, first + i) >> 16);
+            break;
+        case S_QZEROS:
+            for (size_t i = 0; i < count; i++) {
+                const uint64_t h = draw(key, first + i);
+                uint32_t w = 0;
+                for (int j = 0; j < 8; j++) w |= (uint32_t)(6 + ((h >> (2 * j + 20)) & 3)) << (4 * j);
+                dst[i] = w;
+            }
+            break;
+        case S_SCALES:
+            for (size_t i = 0; i < count; i++) {
+                const float u = (float)(draw(key, first + i) >> 40) * (1.0f / 16777216.0f);
+                f[i] = 0.002f + 0.018f * u;
+            }
+            break;
+    }
+}
+
 void synth_tensor(const Shape& s, uint64_t seed, int t, int layer, int sub, uint32_t* dst, int threads) {
     const size_t n = s.sub_words(t, is_qlinear(t) ? sub : S_DENSE);
     const uint64_t key = stream_key(seed, t, layer, sub);
@@ -60,28 +86,8 @@ void synth_tensor(const Shape& s, uint64_t seed, int t, int layer, int sub, uint
         int in, out;
         s.qdims(t, &in, &out);
         switch (sub) {
-            case S_QWEIGHT:  // 8 i.i.d. nibbles per word
-                parallel_for(n, threads, [=](size_t b, size_t e) {
-                    for (size_t i = b; i < e; i++) dst[i] = (uint32_t)(draw(key, i) >> 16);
-                });
-                break;
-            case S_QZEROS:
-                parallel_for(n, threads, [=](size_t b, size_t e) {
-                    for (size_t i = b; i < e; i++) {
-                        const uint64_t h = draw(key, i);
-                        uint32_t w = 0;
-                        for (int j = 0; j < 8; j++) w |= (uint32_t)(6 + ((h >> (2 * j + 20)) & 3)) << (4 * j);
-                        dst[i] = w;
-                    }
-                });
-                break;
-            case S_SCALES:
-                parallel_for(n, threads, [=](size_t b, size_t e) {
-                    for (size_t i = b; i < e; i++) {
-                        const float u = (float)(draw(key, i) >> 40) * (1.0f / 16777216.0f);
-                        f[i] = 0.002f + 0.018f * u;
-                    }
-                });
+            case S_QWEIGHT: case S_QZEROS: case S_SCALES:
+                parallel_for(n, threads, [=, &s](size_t b, size_t e) { synth_range(s, seed, t, layer, sub, b, e - b, dst + b); });
                 break;
             case S_GINDEX:
                 fill_gindex(reinterpret_cast<int32_t*>(dst), in, s.c.group_size, key);
@@ -122,6 +128,29 @@ const uint32_t* SynthSource::get(int t, int layer, int sub, std::vector<uint32_t
         return scratch.data() + (size_t)layer * shape.c.dim;
     }
     return scratch.data();
+}
+
+void BlobSource::get_rows(int t, int layer, const int32_t* rows, int n, uint32_t* qw, float* sc, uint8_t* zn) {
+    int in, out;
+    shape.qdims(t, &in, &out);
+    gather_rows(in, shape.c.group_size, base + shape.offset_words(t, layer, S_QWEIGHT), base + shape.offset_words(t, layer, S_QZEROS),
+                reinterpret_cast<const float*>(base + shape.offset_words(t, layer, S_SCALES)), rows, n, qw, sc, zn);
+}
+
+void SynthSource::get_rows(int t, int layer, const int32_t* rows, int n, uint32_t* qw, float* sc, uint8_t* zn) {
+    int in, out;
+    shape.qdims(t, &in, &out);
+    const size_t g = Shape::groups(in, shape.c.group_size), wpr = in / 8;
+    parallel_for((size_t)n, n * wpr >= 65536 ? threads : 1, [=](size_t b, size_t e) {
+        std::vector<uint32_t> zw(g);
+        for (size_t j = b; j < e; j++) {
+            const size_t src = (size_t)rows[j];
+            synth_range(shape, seed, t, layer, S_QWEIGHT, src * wpr, wpr, qw + j * wpr);
+            synth_range(shape, seed, t, layer, S_SCALES, src * g, g, reinterpret_cast<uint32_t*>(sc + j * g));
+            synth_range(shape, seed, t, layer, S_QZEROS, (src / 8) * g, g, zw.data());
+            for (size_t k = 0; k < g; k++) zn[j * g + k] = (uint8_t)((zw[k] >> (4 * (src % 8))) & 15u);
+        }
+    });
 }
 
 }  // namespace l2
