@@ -244,6 +244,9 @@ def main():
     e2e = {"value": streams * n_loop / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 40 * n_loop, "d2h_bytes_per_step": 40 * n_loop,
            "note": "one l2_decode_step call per token: 40-byte loop record up, 40-byte record (chosen token) back"}
 
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
     peak, peak_kind = measured_peaks()
@@ -268,7 +271,7 @@ def main():
             out["cpu_baseline"] = CpuArm(args.workload, payload=payload, cfg=cfg).run()
         except Exception as e:  # the GPU numbers stand even if the CPU leg cannot run
             out["cpu_baseline"] = {"error": str(e)}
-    print(json.dumps(out))
+    print(json.dumps(out), flush=True)
 
 
 if __name__ == "__main__":

@@ -905,7 +905,7 @@ extern "C" int l2_debug_trace(int enable, unsigned long long* host_out, int n_ct
 extern "C" uint64_t l2_projection_bytes(const l2_model* m, int which) {
     if (!m) return 0;
     const Shape& sh = m->shape;
-    auto q = [&](int t) { return (uint64_t)(sh.sub_words(t, S_QWEIGHT) + sh.sub_words(t, S_QZEROS) + sh.sub_words(t, S_SCALES)) * 4; };
+    auto q = [&](int t) { return (uint64_t)(sh.sub_words(t, S_QWEIGHT) + sh.sub_words(t, S_QZEROS) + sh.sub_words(t, S_SCALES)) * 4 / m->tp_world; };  // this process's rows
     switch (which) {
         case 0: return q(T_WQ) + q(T_WK) + q(T_WV);
         case 1: return q(T_WO);
