@@ -61,6 +61,7 @@ typedef struct l2_options {
 #define L2_FLAG_NO_GRAPH 1 /* launch kernels directly instead of replaying the per-token CUDA graph */
 #define L2_FLAG_NO_PDL 2   /* do not use programmatic dependent launch between the kernels of a token */
 #define L2_FLAG_NO_L2_PREFETCH 4 /* do not prefetch the next kernel's weights into L2 */
+#define L2_FLAG_NO_TOKEN_KERNEL 8 /* one launch per operator instead of one persistent kernel per token */
 
 typedef struct l2_model l2_model;     /* LlamaModel (src/lib.rs:28-36, 68-77) */
 typedef struct l2_state l2_state;     /* RunState (src/models.rs:29-42) */
@@ -204,6 +205,14 @@ uint64_t l2_projection_bytes(const l2_model* m, int which);
 /* Debug: per-CTA clock stamps of the GEMV kernels (8 per CTA); enable != 0 turns tracing on for
  * launches planned afterwards, host_out (may be NULL) receives the stamps of the last launch. */
 int l2_debug_trace(int enable, unsigned long long* host_out, int n_ctas);
+
+/* Debug: clock stamps of the one-kernel-per-token path.  enable = 1 arms recording into a device
+ * buffer of `count` stamps (needs SMs x phases x 16); enable = 0 copies the first `count` stamps
+ * to host_out, laid out [CTA][phase][16]: SM clock at phase start, digits staged, main loop done,
+ * barrier passed; global nanosecond timer at phase start, barrier arrival, barrier passed; SM
+ * clock at barrier arrival; cycles warp 0 waited for weights; slot fills; rest unused.
+ * No counterpart in the reference. */
+int l2_debug_token_trace(l2_state* s, int enable, unsigned long long* host_out, size_t count);
 
 /* ---- sampling helpers (src/util.rs:39-46, 71-113) ----------------------------------- */
 uint32_t l2_random_u32(uint64_t* seed);

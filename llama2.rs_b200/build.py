@@ -12,7 +12,7 @@ OUT = os.path.join(HERE, "libllama2_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 HOST_CXX = "/usr/bin/g++"
 
-CU_SOURCES = ["decode_kernels.cu", "gemv_kernels.cu", "gemm_tc.cu", "prefill_kernels.cu", "prefill.cu", "model.cu", "attention_noalloc.cu"]
+CU_SOURCES = ["decode_kernels.cu", "gemv_kernels.cu", "token_kernel.cu", "gemm_tc.cu", "prefill_kernels.cu", "prefill.cu", "model.cu", "attention_noalloc.cu"]
 CPP_SOURCES = ["layout.cpp", "synth.cpp", "repack.cpp", "tokenizer.cpp", "tp.cpp"]
 
 NVCC_FLAGS = [

@@ -1,0 +1,265 @@
+// Device-side building blocks shared by the stand-alone GEMV kernel (gemv_kernels.cu) and the
+// one-kernel-per-token path (token_kernel.cu): integer MMA, mbarriers, bulk copies, the barrier of
+// the consumer warps, and the staging of an activation vector as 7-bit digits.
+#pragma once
+
+#include <cfloat>
+#include <cmath>
+
+#include "kernels.cuh"
+
+namespace l2 {
+
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The first MMA of a chain: the accumulator input is the constant zero, no register has to be cleared.
+__device__ __forceinline__ void mma_u8s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One poll of a barrier phase.  The time hint lets the hardware park the thread until the phase
+// completes (or the time has passed) instead of returning at once: a warp that polls in a tight
+// loop floods the shared-memory pipe and slows every other warp of the SM down.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns = 0) {
+    uint32_t ok;
+    if (hint_ns)
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns) : "memory");
+    else
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for a phase of the barrier, but never forever: after `limit` polls (each parked for up to
+// 20 microseconds, with a pause between two) it gives up and reports failure; the caller records
+// it in the status word and stops using the data.
+constexpr uint32_t SK_WAIT_LIMIT = 1u << 17;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = SK_WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; i++) {
+        if (mbar_try_wait(bar, parity, 20000u)) return true;
+        __nanosleep(200);
+    }
+    return false;
+}
+// Bulk asynchronous copy global -> shared of this CTA; bytes and both addresses are multiples of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// barrier of the SK_THREADS consumer threads only (the producer warp runs on its own)
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SK_THREADS) : "memory"); }
+
+__device__ __forceinline__ float block_reduce_2(float& mx, float sq, float* red /* 2*SK_WARPS+2 floats */) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    }
+    if (lane == 0) { red[warp] = mx; red[SK_WARPS + warp] = sq; }
+    consumer_sync();
+    if (warp == 0) {
+        float m = lane < SK_WARPS ? red[lane] : 0.f;
+        float s = lane < SK_WARPS ? red[SK_WARPS + lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            s += __shfl_xor_sync(0xffffffffu, s, o);
+        }
+        if (lane == 0) { red[2 * SK_WARPS] = m; red[2 * SK_WARPS + 1] = s; }
+    }
+    consumer_sync();
+    mx = red[2 * SK_WARPS];
+    const float total = red[2 * SK_WARPS + 1];
+    consumer_sync();
+    return total;
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 255) | ((uint32_t)(b & 255) << 8) | ((uint32_t)(c & 255) << 16) | ((uint32_t)(d & 255) << 24);
+}
+
+// ---- staging of an activation vector as digits ------------------------------------------------------
+// Thread i owns the 8-input blocks i, i + 512, ...; the first SK_KEEP of them stay in registers
+// between the two passes (max / sum of squares, then digits).
+constexpr int SK_KEEP = 3;
+
+// Loads block `blk` of the segment's vector times its norm weight; with `stats` also folds the block
+// into the running max |v| and sum of x^2.
+__device__ __forceinline__ void stage_fetch(const SkSeg& sg, int blk, float4& v0, float4& v1, bool stats, float& mx, float& sq) {
+    const float4* x4 = reinterpret_cast<const float4*>(sg.x);
+    const float4* n4 = reinterpret_cast<const float4*>(sg.nw);
+    v0 = __ldcg(x4 + 2 * blk);  // written by other CTAs shortly before: read at the L2, never from a stale L1 line
+    v1 = __ldcg(x4 + 2 * blk + 1);
+    if (stats) sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+    if (sg.nw) {
+        const float4 w0 = __ldg(n4 + 2 * blk), w1 = __ldg(n4 + 2 * blk + 1);
+        v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
+        v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
+    }
+    if (stats) {
+        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))));
+        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+    }
+}
+
+// P = 2^(26 - E) with 2^E <= mx < 2^(E+1): |v * P| < 2^27 for every |v| <= mx
+__device__ __forceinline__ float stage_scale(float mx) {
+    int e = 0;
+    if (mx > 0.f && mx < INFINITY) e = 26 - (int)((__float_as_uint(mx) >> 23) & 255u) + 127;
+    e = max(-100, min(100, e));
+    return __uint_as_float((uint32_t)(127 + e) << 23);
+}
+
+// Writes the digits of block `blk` (8 values v0, v1 scaled by P) and adds them to the group sums.
+// Called by whole warps; lanes whose block lies beyond the vector pass zeros and valid = false.
+template <int W>
+__device__ __forceinline__ void stage_emit(uint8_t* digits, int* ss, int stride, int blk, const float4& v0, const float4& v1, bool valid, float P) {
+    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    uint32_t E[8];  // per element: bytes d3, d2, d1, d0 (d0 signed, the others 0..127)
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const uint32_t X = (uint32_t)__float2int_rn(v[j] * P);
+        E[j] = (X & 0x7Fu) | ((X << 1) & 0x7F00u) | ((X << 2) & 0x7F0000u) | ((X << 3) & 0xFF000000u);
+    }
+    // 4x4 byte transposes: words of one digit for inputs (0,2,4,6) and (1,3,5,7), the order in
+    // which the nibbles of a weight word separate into its low and high halves
+    uint32_t lo[4], hi[4];
+    {
+        const uint32_t a = __byte_perm(E[0], E[2], 0x5140), b2 = __byte_perm(E[0], E[2], 0x7362);
+        const uint32_t c = __byte_perm(E[4], E[6], 0x5140), d = __byte_perm(E[4], E[6], 0x7362);
+        lo[3] = __byte_perm(a, c, 0x5410); lo[2] = __byte_perm(a, c, 0x7632);
+        lo[1] = __byte_perm(b2, d, 0x5410); lo[0] = __byte_perm(b2, d, 0x7632);
+    }
+    {
+        const uint32_t a = __byte_perm(E[1], E[3], 0x5140), b2 = __byte_perm(E[1], E[3], 0x7362);
+        const uint32_t c = __byte_perm(E[5], E[7], 0x5140), d = __byte_perm(E[5], E[7], 0x7362);
+        hi[3] = __byte_perm(a, c, 0x5410); hi[2] = __byte_perm(a, c, 0x7632);
+        hi[1] = __byte_perm(b2, d, 0x5410); hi[0] = __byte_perm(b2, d, 0x7632);
+    }
+    int sum[4];
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        if (valid) *reinterpret_cast<uint2*>(digits + (size_t)p * stride + (size_t)blk * 8) = make_uint2(lo[p], hi[p]);
+        sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
+    }
+    // a group is 4*W consecutive blocks = 4*W consecutive lanes: sum them with shuffles
+    int s01 = 128 * sum[0] + sum[1], s23 = 128 * sum[2] + sum[3];
+#pragma unroll
+    for (int o = 1; o < 4 * W; o <<= 1) {
+        s01 += __shfl_xor_sync(0xffffffffu, s01, o);
+        s23 += __shfl_xor_sync(0xffffffffu, s23, o);
+    }
+    if (valid && (threadIdx.x & (4 * W - 1)) == 0) {
+        const int g = blk / (4 * W);
+        ss[2 * g] = s01;
+        ss[2 * g + 1] = s23;
+    }
+}
+
+// Turns the vector of one segment into digits and per-group digit sums in shared memory.
+// Returns (in every thread) the factor the integer result has to be multiplied with.
+template <int W>
+__device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digits, int* ss, float* red) {
+    const int nblk = in / 8;
+    float mx = 0.f, sq = 0.f;
+    float4 keep[SK_KEEP][2];
+#pragma unroll
+    for (int k = 0; k < SK_KEEP; k++) keep[k][0] = keep[k][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < SK_KEEP; k++) {
+        const int blk = threadIdx.x + k * SK_THREADS;
+        if (blk < nblk) stage_fetch(sg, blk, keep[k][0], keep[k][1], true, mx, sq);
+    }
+    for (int blk = threadIdx.x + SK_KEEP * SK_THREADS; blk < nblk; blk += SK_THREADS) {
+        float4 a, b;
+        stage_fetch(sg, blk, a, b, true, mx, sq);
+    }
+    const float total = block_reduce_2(mx, sq, red);
+    const float rs = sg.nw ? 1.0f / sqrtf(total / (float)in + eps) : 1.0f;  // src/models.rs:58-60
+    const float P = stage_scale(mx);
+    const int stride = in + 16;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int rounds = (nblk + SK_THREADS - 1) / SK_THREADS;
+#pragma unroll
+    for (int k = 0; k < SK_KEEP; k++) {
+        const int blk = threadIdx.x + k * SK_THREADS;
+        if (k < rounds && (blk & ~31) < nblk) {  // warp-uniform
+            const bool valid = blk < nblk;
+            stage_emit<W>(digits, ss, stride, blk, valid ? keep[k][0] : zero4, valid ? keep[k][1] : zero4, valid, P);
+        }
+    }
+    for (int k = SK_KEEP; k < rounds; k++) {
+        const int blk = threadIdx.x + k * SK_THREADS;
+        if ((blk & ~31) < nblk) {
+            const bool valid = blk < nblk;
+            float4 a = zero4, b = zero4;
+            float m2 = 0.f, s2 = 0.f;
+            if (valid) stage_fetch(sg, blk, a, b, false, m2, s2);
+            stage_emit<W>(digits, ss, stride, blk, a, b, valid, P);
+        }
+    }
+    return rs / P;
+}
+
+// Two segments whose vectors are two orderings of the same values (w1 and w3 read the same x, each
+// in its own K order, with the norm weight ordered alike): the maximum and the sum of squares are
+// taken once, from the first, and both are turned into digits with the same scale.  Needs
+// in <= 2 * 8 * SK_THREADS.  Returns the common output factor.
+template <int W>
+__device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, float eps, uint8_t* da, uint8_t* db, int* ssa, int* ssb, float* red) {
+    const int nblk = in / 8;
+    float mx = 0.f, sq = 0.f, m2 = 0.f, s2 = 0.f;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 ka[2][2], kb[2][2];
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        ka[k][0] = ka[k][1] = kb[k][0] = kb[k][1] = zero4;
+        const int blk = threadIdx.x + k * SK_THREADS;
+        if (blk < nblk) {
+            stage_fetch(sa, blk, ka[k][0], ka[k][1], true, mx, sq);
+            stage_fetch(sb, blk, kb[k][0], kb[k][1], false, m2, s2);
+        }
+    }
+    const float total = block_reduce_2(mx, sq, red);
+    const float rs = sa.nw ? 1.0f / sqrtf(total / (float)in + eps) : 1.0f;
+    const float P = stage_scale(mx);
+    const int stride = in + 16;
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const int blk = threadIdx.x + k * SK_THREADS;
+        if ((blk & ~31) < nblk) {
+            const bool valid = blk < nblk;
+            stage_emit<W>(da, ssa, stride, blk, ka[k][0], ka[k][1], valid, P);
+            stage_emit<W>(db, ssb, stride, blk, kb[k][0], kb[k][1], valid, P);
+        }
+    }
+    return rs / P;
+}
+
+// Asks the L2 to fetch [p, p + bytes) from HBM; nothing waits on it.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+    const char* c = static_cast<const char*>(p);
+    for (uint32_t off = 0; off < bytes; off += 32768u) {
+        const uint32_t n = min(32768u, bytes - off) & ~15u;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(c + off), "r"(n) : "memory");
+    }
+}
+}  // namespace l2

@@ -13,14 +13,14 @@
 //   * mma.sync.m16n8k32 (u8 x s8 -> s32) multiplies 16 rows x 32 weights by the four digit columns;
 //     the sums over one quantisation group are exact integers, the zero point is removed with the
 //     group's digit sums, and one f32 FMA per row and group applies the scale;
-//   * work split: every CTA owns a contiguous run of whole 16-row tiles; the (tile, group) units of
-//     that run are dealt out evenly to the warps as contiguous ranges (contiguous in memory as
-//     well), and tiles that straddle warps are summed through shared memory in warp order, so
-//     results are bit-reproducible and no CTA ever waits for another;
-//   * weights never pass through registers on their way in: every warp owns a small ring of shared
-//     memory slots that it fills with bulk asynchronous copies (cp.async.bulk, completion counted
-//     on an mbarrier per slot) of the next few units of its range; the copies are issued before the
-//     kernel waits for its predecessor and keep HBM streaming while the activations are staged;
+//   * work split: every CTA owns a contiguous run of whole 16-row tiles, i.e. one contiguous byte
+//     range of (tile, group) unit records; tiles are summed over the warps through shared memory in
+//     warp order, so results are bit-reproducible and no CTA ever waits for another;
+//   * weights never pass through registers on their way in: a producer warp streams the CTA's range
+//     into a ring of shared-memory slots with large bulk asynchronous copies (cp.async.bulk,
+//     completion counted on an mbarrier per slot, every wait bounded); the first copies are issued
+//     before the kernel waits for its predecessor and keep HBM streaming while the activations are
+//     staged; the 16 consumer warps take the units of a slot two at a time;
 //   * every CTA also asks the L2 to fetch its share of the next kernel's weights
 //     (cp.async.bulk.prefetch.L2).
 //
@@ -30,6 +30,7 @@
 #include <cfloat>
 #include <cmath>
 
+#include "gemv_device.cuh"
 #include "kernels.cuh"
 
 namespace l2 {
@@ -39,194 +40,6 @@ unsigned long long* g_sk_trace = nullptr;
 #define SK_STAMP(i) do { if (P.trace && threadIdx.x == 0) P.trace[blockIdx.x * 8 + (i)] = clock64(); } while (0)
 #define SK_STAMP0() do { if (threadIdx.x == 0) t_entry = clock64(); } while (0)
 
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Waits for a phase of the barrier, but never forever: after SK_WAIT_LIMIT polls it gives up and
-// reports failure (the caller records it in the status word and stops using the data).
-constexpr uint32_t SK_WAIT_LIMIT = 1u << 24;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = SK_WAIT_LIMIT) {
-    for (uint32_t i = 0; i < limit; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-// Bulk asynchronous copy global -> shared of this CTA; bytes and both addresses are multiples of 16.
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-
-// barrier of the SK_THREADS consumer threads only (the producer warp runs on its own)
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SK_THREADS) : "memory"); }
-
-__device__ __forceinline__ float block_reduce_2(float& mx, float sq, float* red /* 2*SK_WARPS+2 floats */) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    }
-    if (lane == 0) { red[warp] = mx; red[SK_WARPS + warp] = sq; }
-    consumer_sync();
-    if (warp == 0) {
-        float m = lane < SK_WARPS ? red[lane] : 0.f;
-        float s = lane < SK_WARPS ? red[SK_WARPS + lane] : 0.f;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            s += __shfl_xor_sync(0xffffffffu, s, o);
-        }
-        if (lane == 0) { red[2 * SK_WARPS] = m; red[2 * SK_WARPS + 1] = s; }
-    }
-    consumer_sync();
-    mx = red[2 * SK_WARPS];
-    const float total = red[2 * SK_WARPS + 1];
-    consumer_sync();
-    return total;
-}
-
-__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-    return (uint32_t)(a & 255) | ((uint32_t)(b & 255) << 8) | ((uint32_t)(c & 255) << 16) | ((uint32_t)(d & 255) << 24);
-}
-
-// Turns the vector of one segment into digits and per-group digit sums in shared memory.
-// Returns (in every thread) the factor the integer result has to be multiplied with.
-// Thread i owns the 8-input blocks i, i + 512, ...; the first SK_KEEP of them stay in registers
-// between the two passes (max / sum of squares, then digits).
-constexpr int SK_KEEP = 3;
-
-template <int W>
-__device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digits, int* ss, float* red) {
-    const float4* x4 = reinterpret_cast<const float4*>(sg.x);
-    const float4* n4 = reinterpret_cast<const float4*>(sg.nw);
-    const int nblk = in / 8;
-    float mx = 0.f, sq = 0.f;
-    float4 keep[SK_KEEP][2];
-#pragma unroll
-    for (int k = 0; k < SK_KEEP; k++) keep[k][0] = keep[k][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    auto fetch = [&](int blk, float4& v0, float4& v1, bool stats) {
-        v0 = x4[2 * blk];
-        v1 = x4[2 * blk + 1];
-        if (stats) sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
-        if (sg.nw) {
-            const float4 w0 = n4[2 * blk], w1 = n4[2 * blk + 1];
-            v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
-            v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
-        }
-        if (stats) {
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))));
-            mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
-        }
-    };
-#pragma unroll
-    for (int k = 0; k < SK_KEEP; k++) {
-        const int blk = threadIdx.x + k * SK_THREADS;
-        if (blk < nblk) fetch(blk, keep[k][0], keep[k][1], true);
-    }
-    for (int blk = threadIdx.x + SK_KEEP * SK_THREADS; blk < nblk; blk += SK_THREADS) {
-        float4 a, b;
-        fetch(blk, a, b, true);
-    }
-    const float total = block_reduce_2(mx, sq, red);
-    const float rs = sg.nw ? 1.0f / sqrtf(total / (float)in + eps) : 1.0f;  // src/models.rs:58-60
-    // P = 2^(26 - E) with 2^E <= max|v| < 2^(E+1): |v * P| < 2^27
-    int e = 0;
-    if (mx > 0.f && mx < INFINITY) e = 26 - (int)((__float_as_uint(mx) >> 23) & 255u) + 127;
-    e = max(-100, min(100, e));
-    const float P = __uint_as_float((uint32_t)(127 + e) << 23);
-    const int stride = in + 16;
-    // called by whole warps; lanes whose block lies beyond the vector pass zeros and valid = false
-    auto emit = [&](int blk, const float4& v0, const float4& v1, bool valid) {
-        const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        uint32_t E[8];  // per element: bytes d3, d2, d1, d0 (d0 signed, the others 0..127)
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const uint32_t X = (uint32_t)__float2int_rn(v[j] * P);
-            E[j] = (X & 0x7Fu) | ((X << 1) & 0x7F00u) | ((X << 2) & 0x7F0000u) | ((X << 3) & 0xFF000000u);
-        }
-        // 4x4 byte transposes: words of one digit for inputs (0,2,4,6) and (1,3,5,7), the order in
-        // which the nibbles of a weight word separate into its low and high halves
-        uint32_t lo[4], hi[4];
-        {
-            const uint32_t a = __byte_perm(E[0], E[2], 0x5140), b2 = __byte_perm(E[0], E[2], 0x7362);
-            const uint32_t c = __byte_perm(E[4], E[6], 0x5140), d = __byte_perm(E[4], E[6], 0x7362);
-            lo[3] = __byte_perm(a, c, 0x5410); lo[2] = __byte_perm(a, c, 0x7632);
-            lo[1] = __byte_perm(b2, d, 0x5410); lo[0] = __byte_perm(b2, d, 0x7632);
-        }
-        {
-            const uint32_t a = __byte_perm(E[1], E[3], 0x5140), b2 = __byte_perm(E[1], E[3], 0x7362);
-            const uint32_t c = __byte_perm(E[5], E[7], 0x5140), d = __byte_perm(E[5], E[7], 0x7362);
-            hi[3] = __byte_perm(a, c, 0x5410); hi[2] = __byte_perm(a, c, 0x7632);
-            hi[1] = __byte_perm(b2, d, 0x5410); hi[0] = __byte_perm(b2, d, 0x7632);
-        }
-        int sum[4];
-#pragma unroll
-        for (int p = 0; p < 4; p++) {
-            if (valid) *reinterpret_cast<uint2*>(digits + (size_t)p * stride + (size_t)blk * 8) = make_uint2(lo[p], hi[p]);
-            sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
-        }
-        // a group is 4*W consecutive blocks = 4*W consecutive lanes: sum them with shuffles
-        int s01 = 128 * sum[0] + sum[1], s23 = 128 * sum[2] + sum[3];
-#pragma unroll
-        for (int o = 1; o < 4 * W; o <<= 1) {
-            s01 += __shfl_xor_sync(0xffffffffu, s01, o);
-            s23 += __shfl_xor_sync(0xffffffffu, s23, o);
-        }
-        if (valid && (threadIdx.x & (4 * W - 1)) == 0) {
-            const int g = blk / (4 * W);
-            ss[2 * g] = s01;
-            ss[2 * g + 1] = s23;
-        }
-    };
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    const int rounds = (nblk + SK_THREADS - 1) / SK_THREADS;
-#pragma unroll
-    for (int k = 0; k < SK_KEEP; k++) {
-        const int blk = threadIdx.x + k * SK_THREADS;
-        if (k < rounds && (blk & ~31) < nblk) {  // warp-uniform
-            const bool valid = blk < nblk;
-            emit(blk, valid ? keep[k][0] : zero4, valid ? keep[k][1] : zero4, valid);
-        }
-    }
-    for (int k = SK_KEEP; k < rounds; k++) {
-        const int blk = threadIdx.x + k * SK_THREADS;
-        if ((blk & ~31) < nblk) {
-            const bool valid = blk < nblk;
-            float4 a = zero4, b = zero4;
-            if (valid) fetch(blk, a, b, false);
-            emit(blk, a, b, valid);
-        }
-    }
-    return rs / P;
-}
-
-// Asks the L2 to fetch [p, p + bytes) from HBM; nothing waits on it.
-__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
-    const char* c = static_cast<const char*>(p);
-    for (uint32_t off = 0; off < bytes; off += 32768u) {
-        const uint32_t n = min(32768u, bytes - off) & ~15u;
-        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(c + off), "r"(n) : "memory");
-    }
-}
 
 template <int W, int NSEG>
 __global__ void __launch_bounds__(SK_THREADS + 32, 1) gemv_sk_kernel(const SkParams* __restrict__ gp) {
@@ -447,7 +260,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) gemv_sk_kernel(const SkPar
     if (!ok) {
         // copies may still be in flight into this CTA's shared memory: give them a bounded time to land
         // before the CTA exits, without using their data
-        for (int i = 0; i < NS; i++) { mbar_wait(full + i, 0, 1u << 16); mbar_wait(full + i, 1, 1u << 16); }
+        for (int i = 0; i < NS; i++) { mbar_wait(full + i, 0, 1u << 8); mbar_wait(full + i, 1, 1u << 8); }
     }
     SK_STAMP(4);
     consumer_sync();

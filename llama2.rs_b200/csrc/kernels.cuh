@@ -26,7 +26,7 @@ enum : int { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
 
 constexpr int SK_THREADS = 512;            // one CTA per SM
 constexpr int SK_WARPS = SK_THREADS / 32;
-constexpr int SK_MAX_SLOTS = 8;            // ring slots per warp (upper bound)
+constexpr int SK_MAX_SLOTS = 16;           // ring slots of a CTA (upper bound)
 
 // One 4-bit matrix in device layout (see repack.cpp) with its input vector.
 struct SkSeg {
@@ -144,6 +144,37 @@ struct SelectParams {
     int* out_tokens;      // [SEQ] next token chosen at each position
     int vocab;
 };
+
+// ---- the whole token as one persistent kernel (token_kernel.cu) --------------------------------
+// A token is a list of phases; all CTAs run every phase and meet at a grid-wide barrier between
+// two phases.  A phase record is what the stand-alone kernel of the same name takes as parameters.
+enum : int { PH_EMBED = 0, PH_GEMV1, PH_GEMV2, PH_ATTN, PH_CLS, PH_SELECT, PH_ADVANCE };
+
+struct alignas(16) PhaseRec {
+    int type;
+    int pad[3];
+    union {
+        SkParams sk;     // PH_GEMV1 (one matrix per job) / PH_GEMV2 (w1 with w3 + SwiGLU)
+        AttnParams at;
+        EmbedParams em;
+        ClsParams cl;
+        SelectParams se; // PH_SELECT; PH_ADVANCE uses se.ctl only
+    } u;
+};
+
+struct TokenParams {
+    const PhaseRec* phases;     // device table
+    int nphases;
+    unsigned* bar;              // arrival counter of the grid barrier, zero at launch
+    int* status;                // set non-zero when a bounded wait gives up
+    unsigned long long* trace;  // debug: [grid][nphases][16] stamps, or null
+    int chunk, slots;           // ring geometry: unit records per slot, slots
+    unsigned fixed_bytes;       // shared memory in front of the ring (digits, sums, scratch of the other phases)
+};
+
+cudaError_t launch_token(const TokenParams& tk, int group_size, int grid, size_t smem, cudaStream_t st);
+cudaError_t token_init(int max_optin);     // max_optin: opt-in shared memory per block of the device
+size_t token_attn_scratch_bytes(int ag);   // shared memory the attention phase needs
 
 void launch_embed(const EmbedParams& p, cudaStream_t st, bool pdl);
 // `p` points to device memory: the kernel copies the record into shared memory with one cooperative load

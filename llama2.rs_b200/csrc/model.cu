@@ -163,6 +163,7 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
         return fail(L2_EINVAL, "tp_world %d does not divide the kv heads / leave whole 16-row tiles", m->tp_world);
     m->use_graph = !(m->opt.flags & L2_FLAG_NO_GRAPH);
     m->use_pdl = !(m->opt.flags & L2_FLAG_NO_PDL);
+    m->use_token_kernel = !(m->opt.flags & L2_FLAG_NO_TOKEN_KERNEL) && !getenv("L2_NO_TOKEN_KERNEL");
     L2_CUDA(cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking));
     m->stream = m->own_stream;
     const l2_config& c = shape.c;
@@ -331,7 +332,7 @@ static void launch_w13(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_l
 static void launch_w2(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_layer_gemv(s, l, 3, st, pdl); }
 
 // rope + cache append + attention (src/models.rs:228-256)
-static void launch_attention(l2_state* s, int l, cudaStream_t st, bool pdl) {
+static AttnParams attention_params(l2_state* s, int l) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
     const DevLayer& y = m->layers[l];
@@ -346,30 +347,118 @@ static void launch_attention(l2_state* s, int l, cudaStream_t st, bool pdl) {
     a.n_kv_local = c.n_kv_heads / m->tp_world; a.kvh0 = m->tp_rank * a.n_kv_local;
     a.max_split = s->max_split; a.split_min = 64;
     a.pos_fixed = -1;
-    launch_attn(a, st, pdl);
+    return a;
 }
 
-static void launch_classifier(l2_state* s, cudaStream_t st, bool pdl) {
+static void launch_attention(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_attn(attention_params(s, l), st, pdl); }
+
+static ClsParams classifier_params(l2_state* s) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
     ClsParams cp{};
     cp.w = m->wcls; cp.x = s->x; cp.nw = m->rms_final; cp.logits = s->logits;
     cp.rows = c.vocab_size; cp.in = c.dim; cp.eps = m->eps;
-    launch_cls(cp, m->sms * 2, st, pdl);
+    return cp;
+}
+
+static void launch_classifier(l2_state* s, cudaStream_t st, bool pdl) { launch_cls(classifier_params(s), s->m->sms * 2, st, pdl); }
+
+static EmbedParams embed_params(l2_state* s, int kind) {
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    EmbedParams e{};
+    e.table = m->tok_emb; e.ctl = s->ctl; e.prompt = s->prompt; e.x = s->x;
+    e.dim = c.dim; e.vocab = c.vocab_size; e.feed_prompt = kind == G_FEED;
+    set_scatter3(e.sdst, e.sidx, &e.nscatter, s, &m->layers[0]);
+    return e;
+}
+
+// ---- the forward pass as one persistent kernel ---------------------------------------------------
+
+// Ring geometry and shared-memory carve-up shared by every phase of the token kernel.
+static int plan_token(l2_state* s) {
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    size_t fixed = std::max<size_t>(token_attn_scratch_bytes(m->shape.attn_groups()), (size_t)c.dim * 4);
+    for (int which = 0; which < 4; which++) {
+        const SkLaunch& L = s->plans[which];  // every layer has the same shapes
+        int max_g = 0;
+        for (int i = 0; i < L.p.njobs; i++) max_g = std::max(max_g, L.p.job[i].G);
+        fixed = std::max(fixed, sk_smem_fixed(L.p.job[0].in, max_g, L.nseg, L.p.ptiles));
+    }
+    fixed = (fixed + 127) & ~(size_t)127;
+    const size_t budget = 222 * 1024;
+    int su = 32;
+    if (const char* e = getenv("L2_SK_CHUNK")) su = std::max(2, std::min(32, atoi(e) & ~1));  // a warp takes one pair per slot
+    int slots = 0;
+    for (; su >= 2; su /= 2) {
+        if (fixed < budget) slots = (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(c.group_size, su));
+        if (slots >= 2) break;
+    }
+    if (slots < 2) return fail(L2_EINVAL, "the token kernel needs %zu bytes of shared memory before its weight ring", fixed);
+    if (const char* e = getenv("L2_SK_SLOTS")) slots = std::max(2, std::min(slots, atoi(e)));
+    s->tk = TokenParams{};
+    s->tk.chunk = su;
+    s->tk.slots = slots;
+    s->tk.fixed_bytes = (unsigned)fixed;
+    s->tk.status = &s->ctl->status;
+    s->tk_smem = fixed + (size_t)slots * sk_slot_bytes(c.group_size, su);
+    if (int rc = dev_alloc(reinterpret_cast<void**>(&s->tk.bar), 256, s->allocs)) return rc;
+    return L2_OK;
+}
+
+static int build_phase_table(l2_state* s, int kind) {
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    std::vector<PhaseRec> t;
+    auto add = [&](int type) -> PhaseRec& {
+        t.emplace_back();
+        memset(&t.back(), 0, sizeof(PhaseRec));
+        t.back().type = type;
+        return t.back();
+    };
+    add(PH_EMBED).u.em = embed_params(s, kind);
+    for (int l = 0; l < c.n_layers; l++) {
+        for (int which = 0; which < 4; which++) {
+            const SkLaunch& L = s->plans[(size_t)l * 4 + which];
+            PhaseRec& r = add(L.nseg == 2 ? PH_GEMV2 : PH_GEMV1);
+            r.u.sk = L.p;
+            r.u.sk.trace = nullptr;
+            if (which == 0) add(PH_ATTN).u.at = attention_params(s, l);
+        }
+    }
+    if (kind == G_DECODE || kind == G_FWD_CLS) add(PH_CLS).u.cl = classifier_params(s);
+    if (kind == G_DECODE) {
+        SelectParams sp{};
+        sp.logits = s->logits; sp.ctl = s->ctl; sp.prompt = s->prompt; sp.out_tokens = s->out_tokens; sp.vocab = c.vocab_size;
+        add(PH_SELECT).u.se = sp;
+    } else if (kind == G_FEED) {
+        add(PH_ADVANCE).u.se.ctl = s->ctl;
+    }
+    if (int rc = dev_alloc(reinterpret_cast<void**>(&s->d_phases[kind]), sizeof(PhaseRec) * t.size(), s->allocs)) return rc;
+    L2_CUDA(cudaMemcpy(s->d_phases[kind], t.data(), sizeof(PhaseRec) * t.size(), cudaMemcpyHostToDevice));
+    s->n_phases[kind] = (int)t.size();
+    return L2_OK;
+}
+
+static int enqueue_token(l2_state* s, int kind, cudaStream_t st) {
+    l2_model* m = s->m;
+    TokenParams tk = s->tk;
+    tk.phases = s->d_phases[kind];
+    tk.nphases = s->n_phases[kind];
+    tk.trace = s->tk_trace && (size_t)m->sms * tk.nphases * 16 <= s->tk_trace_count ? s->tk_trace : nullptr;
+    L2_CUDA(cudaMemsetAsync(tk.bar, 0, sizeof(unsigned), st));
+    L2_CUDA(launch_token(tk, m->shape.c.group_size, m->sms, s->tk_smem, st));
+    return L2_OK;
 }
 
 static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
+    if (m->use_token_kernel && m->tp_world == 1) return enqueue_token(s, kind, st);
     const bool pdl = m->use_pdl;
     const int L = c.n_layers, D = c.dim;
-    {
-        EmbedParams e{};
-        e.table = m->tok_emb; e.ctl = s->ctl; e.prompt = s->prompt; e.x = s->x;
-        e.dim = D; e.vocab = c.vocab_size; e.feed_prompt = kind == G_FEED;
-        set_scatter3(e.sdst, e.sidx, &e.nscatter, s, &m->layers[0]);
-        launch_embed(e, st, false);  // first node of the token: plain stream order
-    }
+    launch_embed(embed_params(s, kind), st, false);  // first node of the token: plain stream order
     const int T = m->tp_world;
     for (int l = 0; l < L; l++) {
         const DevLayer& y = m->layers[l];
@@ -416,6 +505,7 @@ static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
 }
 
 static int nodes_per_forward(const l2_model* m, int kind) {
+    if (m->use_token_kernel && m->tp_world == 1) return 1;
     const int L = m->shape.c.n_layers;
     int n = 1 + 5 * L;
     if (m->tp_world > 1) n += 3 * L - 1;  // the copies into the consumers' K orders after each all-gather
@@ -427,6 +517,11 @@ static int nodes_per_forward(const l2_model* m, int kind) {
 // Runs one forward of the given kind on the model's stream (graph replay unless disabled).
 static int run_forward(l2_state* s, int kind) {
     l2_model* m = s->m;
+    if (m->use_token_kernel && m->tp_world == 1 && !s->d_phases[kind]) {
+        if (!s->tk.bar)
+            if (int rc = plan_token(s)) return rc;
+        if (int rc = build_phase_table(s, kind)) return rc;
+    }
     if (!m->use_graph) return enqueue_forward(s, kind, m->stream);
     if (!s->graphs[kind]) {
         cudaStream_t cap;
@@ -902,6 +997,27 @@ extern "C" int l2_debug_trace(int enable, unsigned long long* host_out, int n_ct
 
 // Algorithmic bytes one launch of l2_bench_projection's kernel streams: the checkpoint's
 // qweight + qzeros + scales of the projection(s), or the f32 classifier matrix.
+extern "C" int l2_debug_token_trace(l2_state* s, int enable, unsigned long long* host_out, size_t count) {
+    clear_error();
+    if (!s) return fail(L2_EINVAL, "l2_debug_token_trace: null state");
+    L2_CUDA(cudaSetDevice(s->m->device));
+    L2_CUDA(cudaStreamSynchronize(s->m->stream));
+    if (enable) {
+        if (!s->tk_trace) {
+            s->tk_trace_count = count;
+            if (int rc = dev_alloc(reinterpret_cast<void**>(&s->tk_trace), count * 8, s->allocs)) return rc;
+        }
+        if (count > s->tk_trace_count) return fail(L2_EINVAL, "l2_debug_token_trace: the buffer holds %zu stamps", s->tk_trace_count);
+        L2_CUDA(cudaMemset(s->tk_trace, 0, s->tk_trace_count * 8));
+        for (auto& g : s->graphs)  // captured launches carry the old setting
+            if (g) { cudaGraphExecDestroy(g); g = nullptr; }
+        return L2_OK;
+    }
+    if (!s->tk_trace || !host_out || count > s->tk_trace_count) return fail(L2_EINVAL, "l2_debug_token_trace: nothing recorded");
+    L2_CUDA(cudaMemcpy(host_out, s->tk_trace, count * 8, cudaMemcpyDeviceToHost));
+    return L2_OK;
+}
+
 extern "C" uint64_t l2_projection_bytes(const l2_model* m, int which) {
     if (!m) return 0;
     const Shape& sh = m->shape;

@@ -77,6 +77,7 @@ struct l2_model {
     size_t device_bytes = 0;
     l2_state* gen_state = nullptr;  // reused by l2_generate_ids
     bool use_graph = true, use_pdl = true;
+    bool use_token_kernel = true;    // B=1 forward as one persistent kernel (single GPU only)
     int tp_rank = 0, tp_world = 1;   // tensor parallelism: this process owns 1/tp_world of every matrix's rows
     void* nccl_comm = nullptr;
 };
@@ -99,6 +100,12 @@ struct l2_state {
     std::vector<l2::SkLaunch> plans;     // [layer][4] GEMV launches, planned once
     l2::SkParams* d_plans = nullptr;     // their parameter records on the device
     l2::BatchBuffers* batch = nullptr;   // activations of the batched forward, allocated on first use
+    l2::PhaseRec* d_phases[l2::G_COUNT] = {nullptr, nullptr, nullptr, nullptr};  // phase tables of the token kernel
+    int n_phases[l2::G_COUNT] = {0, 0, 0, 0};
+    l2::TokenParams tk{};                // ring geometry and barrier of the token kernel
+    size_t tk_smem = 0;
+    unsigned long long* tk_trace = nullptr;
+    size_t tk_trace_count = 0;
     cudaGraphExec_t graphs[l2::G_COUNT] = {nullptr, nullptr, nullptr, nullptr};
     int graph_nodes[l2::G_COUNT] = {0, 0, 0, 0};
     std::vector<void*> allocs;

@@ -81,6 +81,7 @@ SIGNATURES = {
     "l2_bench_projection": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int]),
     "l2_projection_bytes": (C.c_uint64, [_vp, C.c_int]),
     "l2_debug_trace": (C.c_int, [C.c_int, _p(C.c_uint64), C.c_int]),
+    "l2_debug_token_trace": (C.c_int, [C.c_void_p, C.c_int, _p(C.c_uint64), C.c_size_t]),
     "l2_random_u32": (C.c_uint32, [_u64p]),
     "l2_random_f32": (C.c_float, [_u64p]),
     "l2_tokenizer_open": (C.c_int, [C.c_char_p, C.c_int, _p(_vp)]),
@@ -112,3 +113,4 @@ def as_i32p(a):
 def as_f32p(a):
     return a.ctypes.data_as(_f32p)
 FLAG_NO_L2_PREFETCH = 4
+FLAG_NO_TOKEN_KERNEL = 8

@@ -151,14 +151,38 @@ def test_synthetic_on_device_equals_blob(l2):
 
 
 def test_graph_and_direct_launch_agree(l2):
+    # one persistent kernel per token (default) and one launch per operator, each with and without
+    # the CUDA graph / programmatic dependent launch: bit-identical inside a family, and the same
+    # token stream with logits equal up to the order of one rmsnorm sum between the two families
     cfg = tiny_config(l2, group_size=64, n_kv_heads=1)
     payload = l2.synth_fill(cfg, 4)
-    runs = []
-    for flags in (0, l2._lib.FLAG_NO_GRAPH, l2._lib.FLAG_NO_PDL, l2._lib.FLAG_NO_GRAPH | l2._lib.FLAG_NO_PDL):
-        m = l2.LlamaModel.from_blob(cfg, payload, flags=flags)
-        runs.append(l2.generate_ids(m, [9, 8, 7, 6, 5], 40, trace_logits=True))
-    for r in runs[1:]:
-        assert np.array_equal(r["logits"], runs[0]["logits"]) and np.array_equal(r["tokens"], runs[0]["tokens"])
+    F = l2._lib
+    families = [(0, F.FLAG_NO_GRAPH),
+                (F.FLAG_NO_TOKEN_KERNEL, F.FLAG_NO_TOKEN_KERNEL | F.FLAG_NO_GRAPH, F.FLAG_NO_TOKEN_KERNEL | F.FLAG_NO_PDL,
+                 F.FLAG_NO_TOKEN_KERNEL | F.FLAG_NO_GRAPH | F.FLAG_NO_PDL)]
+    firsts = []
+    for fam in families:
+        runs = []
+        for flags in fam:
+            m = l2.LlamaModel.from_blob(cfg, payload, flags=flags)
+            runs.append(l2.generate_ids(m, [9, 8, 7, 6, 5], 40, trace_logits=True))
+        for r in runs[1:]:
+            assert np.array_equal(r["logits"], runs[0]["logits"]) and np.array_equal(r["tokens"], runs[0]["tokens"])
+        firsts.append(runs[0])
+    assert np.array_equal(firsts[0]["tokens"], firsts[1]["tokens"])
+    assert_close(firsts[0]["logits"], firsts[1]["logits"], what="token kernel vs per-operator logits")
+
+
+def test_per_operator_path_7b_shapes(l2, orc):
+    # the launch-per-operator path (used under tensor parallelism) on the real 7B projection shapes
+    cfg = l2.preset_config("7B", 128)
+    cfg.n_layers, cfg.vocab_size, cfg.seq_len = 2, 2048, 128
+    gpu, cpu = make_pair(l2, orc, cfg, flags=l2._lib.FLAG_NO_TOKEN_KERNEL)
+    prompt = np.random.default_rng(8).integers(0, cfg.vocab_size, 5).astype(np.int32)
+    want = cpu.generate_ids(prompt, 5 + 32, trace_logits=True)
+    got = l2.generate_ids(gpu, prompt, 5 + 32, trace_logits=True)
+    assert_close(got["logits"], want["logits"], what="7B per-operator logits")
+    assert np.array_equal(got["tokens"], want["tokens"])
 
 
 @pytest.mark.parametrize("name,gs", [("7B", 128), ("13B", 128), ("70B", 64)])
