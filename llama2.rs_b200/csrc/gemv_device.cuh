@@ -63,6 +63,35 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// Shared-memory loads and barrier operations on 32-bit shared-space addresses.  The hot loops keep
+// their addresses in this form: generic 64-bit pointers cost two registers each and a chain of
+// wide integer operations per access.  The loads are volatile so that they stay in program order
+// with the barrier operations around them.
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive_u32(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // barrier of the SK_THREADS consumer threads only (the producer warp runs on its own)
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SK_THREADS) : "memory"); }
 
@@ -177,7 +206,7 @@ __device__ __forceinline__ void stage_emit(uint8_t* digits, int* ss, int stride,
 // Turns the vector of one segment into digits and per-group digit sums in shared memory.
 // Returns (in every thread) the factor the integer result has to be multiplied with.
 template <int W>
-__device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digits, int* ss, float* red) {
+__device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digits, int* ss, float* red, unsigned long long* dbg = nullptr) {
     const int nblk = in / 8;
     float mx = 0.f, sq = 0.f;
     float4 keep[SK_KEEP][2];
@@ -192,7 +221,9 @@ __device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digit
         float4 a, b;
         stage_fetch(sg, blk, a, b, true, mx, sq);
     }
+    if (dbg && threadIdx.x == 0) dbg[0] = clock64() + (mx > 1e30f ? 1 : 0);
     const float total = block_reduce_2(mx, sq, red);
+    if (dbg && threadIdx.x == 0) dbg[1] = clock64();
     const float rs = sg.nw ? 1.0f / sqrtf(total / (float)in + eps) : 1.0f;  // src/models.rs:58-60
     const float P = stage_scale(mx);
     const int stride = in + 16;
@@ -216,6 +247,7 @@ __device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digit
             stage_emit<W>(digits, ss, stride, blk, a, b, valid, P);
         }
     }
+    if (dbg && threadIdx.x == 0) dbg[2] = clock64();
     return rs / P;
 }
 
@@ -224,7 +256,7 @@ __device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digit
 // taken once, from the first, and both are turned into digits with the same scale.  Needs
 // in <= 2 * 8 * SK_THREADS.  Returns the common output factor.
 template <int W>
-__device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, float eps, uint8_t* da, uint8_t* db, int* ssa, int* ssb, float* red) {
+__device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, float eps, uint8_t* da, uint8_t* db, int* ssa, int* ssb, float* red, unsigned long long* dbg = nullptr) {
     const int nblk = in / 8;
     float mx = 0.f, sq = 0.f, m2 = 0.f, s2 = 0.f;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -238,7 +270,9 @@ __device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, flo
             stage_fetch(sb, blk, kb[k][0], kb[k][1], false, m2, s2);
         }
     }
+    if (dbg && threadIdx.x == 0) dbg[0] = clock64() + (mx > 1e30f ? 1 : 0);
     const float total = block_reduce_2(mx, sq, red);
+    if (dbg && threadIdx.x == 0) dbg[1] = clock64();
     const float rs = sa.nw ? 1.0f / sqrtf(total / (float)in + eps) : 1.0f;
     const float P = stage_scale(mx);
     const int stride = in + 16;
@@ -251,6 +285,7 @@ __device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, flo
             stage_emit<W>(db, ssb, stride, blk, kb[k][0], kb[k][1], valid, P);
         }
     }
+    if (dbg && threadIdx.x == 0) dbg[2] = clock64();
     return rs / P;
 }
 

@@ -167,12 +167,14 @@ struct TokenParams {
     int nphases;
     unsigned* bar;              // arrival counter of the grid barrier, zero at launch
     int* status;                // set non-zero when a bounded wait gives up
+    const Ctl* ctl;             // loop state: the position of this token
     unsigned long long* trace;  // debug: [grid][nphases][16] stamps, or null
     int chunk, slots;           // ring geometry: unit records per slot, slots
     unsigned fixed_bytes;       // shared memory in front of the ring (digits, sums, scratch of the other phases)
+    int skip;                   // debug: stream the weights but skip the GEMV arithmetic (results are wrong)
 };
 
-cudaError_t launch_token(const TokenParams& tk, int group_size, int grid, size_t smem, cudaStream_t st);
+cudaError_t launch_token(const TokenParams& tk, int group_size, int attn_groups, int grid, size_t smem, cudaStream_t st);
 cudaError_t token_init(int max_optin);     // max_optin: opt-in shared memory per block of the device
 size_t token_attn_scratch_bytes(int ag);   // shared memory the attention phase needs
 

@@ -102,6 +102,10 @@ int validate_config(const l2_config& c) {
     if (c.dim % 32 || c.hidden_dim % 32 || c.vocab_size % 8)
         return fail(L2_EINVAL, "config: dim/hidden_dim must be multiples of 32, vocab of 8");
     if (c.n_heads / c.n_kv_heads > 8) return fail(L2_EINVAL, "config: more than 8 query heads per kv head");
+    {
+        const int ag = c.n_heads / c.n_kv_heads;  // the attention kernels are instantiated for these
+        if (ag != 1 && ag != 2 && ag != 4 && ag != 8) return fail(L2_EINVAL, "config: %d query heads per kv head (1, 2, 4 or 8 supported)", ag);
+    }
     return L2_OK;
 }
 

@@ -402,6 +402,8 @@ static int plan_token(l2_state* s) {
     s->tk.slots = slots;
     s->tk.fixed_bytes = (unsigned)fixed;
     s->tk.status = &s->ctl->status;
+    s->tk.ctl = s->ctl;
+    s->tk.skip = (getenv("L2_SK_SKIP") ? 1 : 0) | (getenv("L2_TK_HOLD") ? 2 : 0);
     s->tk_smem = fixed + (size_t)slots * sk_slot_bytes(c.group_size, su);
     if (int rc = dev_alloc(reinterpret_cast<void**>(&s->tk.bar), 256, s->allocs)) return rc;
     return L2_OK;
@@ -448,7 +450,7 @@ static int enqueue_token(l2_state* s, int kind, cudaStream_t st) {
     tk.nphases = s->n_phases[kind];
     tk.trace = s->tk_trace && (size_t)m->sms * tk.nphases * 16 <= s->tk_trace_count ? s->tk_trace : nullptr;
     L2_CUDA(cudaMemsetAsync(tk.bar, 0, sizeof(unsigned), st));
-    L2_CUDA(launch_token(tk, m->shape.c.group_size, m->sms, s->tk_smem, st));
+    L2_CUDA(launch_token(tk, m->shape.c.group_size, m->shape.attn_groups(), m->sms, s->tk_smem, st));
     return L2_OK;
 }
 

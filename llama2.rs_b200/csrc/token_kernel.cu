@@ -21,6 +21,7 @@
 namespace l2 {
 
 constexpr int TK_NREC = 4;                    // phase records buffered in shared memory
+static_assert(sizeof(PhaseRec) % 16 == 0, "phase records travel as bulk copies");
 constexpr uint32_t TK_BAR_LIMIT = 1u << 22;   // polls of the grid barrier before giving up (about a second)
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -62,77 +63,70 @@ struct Ring {
     volatile int* abort_flag;
     int* status;
     const uint8_t* zeros;  // 32 bytes of zeros in shared memory
+    int skip;              // debug: consume the slot fills without doing the arithmetic
 };
 
-// Producer side of one GEMV phase (one thread): streams this CTA's unit records through the ring.
-// `kfill` counts slot fills since the start of the kernel.
+__device__ __forceinline__ void prefetch_line_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// Producer side of one GEMV phase (called by the whole producer warp, lane 0 issues): streams this
+// CTA's unit records through the ring.  `kfill` counts slot fills since the start of the kernel.
+// Nothing beyond the ring is requested ahead of time: prefetches into the L2 (bulk or per line) were
+// measured to cost more than they gain here, because every request of an SM shares one path to
+// the L2 and the latency-critical loads of a phase (its input vector, the K/V rows) queue behind
+// whatever has been requested ahead.
 template <int W>
-__device__ bool produce_units(const SkParams& P, int NSEG, const Ring& R, uint32_t& kfill) {
+__device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const Ring& R, uint32_t& kfill) {
     constexpr uint32_t UB = 256u * W + 80u;
+    const int lane = threadIdx.x & 31;
     const CtaRange c = sk_cta_range(P);
     const SkJob& J = P.job[c.ji];
     const int G = J.G, n = c.nt * NSEG * G;
     const int nslots = (n + R.SU - 1) / R.SU;
-    // A later phase's weights: every CTA asks the L2 for an equal slice of them, one piece with each
-    // of its own slot fills, so that the requests are paced with the demand instead of queueing in
-    // front of it.
-    const int pieces = max(nslots, 1);
-    const char* pf_ptr[6];
-    uint32_t pf_mine[6], pf_piece[6];
-    for (int i = 0; i < 6; i++) {
-        pf_ptr[i] = nullptr; pf_mine[i] = 0; pf_piece[i] = 0;
-        if (i < P.n_next) {
-            const size_t per = P.next_slice[i], off = per * blockIdx.x;
-            if (off < P.next_bytes[i]) {
-                pf_ptr[i] = static_cast<const char*>(P.next_ptr[i]) + off;
-                pf_mine[i] = (uint32_t)min(per, P.next_bytes[i] - off);
-                pf_piece[i] = ((pf_mine[i] + (uint32_t)pieces - 1u) / (uint32_t)pieces + 127u) & ~127u;
-            }
-        }
-    }
-    auto prefetch_piece = [&](int k) {
-#pragma unroll
-        for (int i = 0; i < 6; i++) {
-            const uint32_t b = pf_piece[i] * (uint32_t)k;
-            if (b < pf_mine[i]) prefetch_l2(pf_ptr[i] + b, min(pf_piece[i], pf_mine[i] - b));
+    struct Cur { int tl, seg, g; };
+    // visits the runs of records (contiguous in memory) that the next `count` units consist of
+    auto walk = [&](Cur& cu, int count, auto&& visit) {
+        while (count > 0) {
+            const int run = NSEG == 1 ? count : min(count, G - cu.g);  // one matrix: tiles follow one another in memory
+            const SkSeg& S = J.seg[NSEG == 1 ? 0 : cu.seg];
+            const size_t mu = (size_t)(c.tau_first + cu.tl) * G + cu.g;
+            visit(S.rec + mu * (UB / 4), (uint32_t)run * UB);
+            count -= run;
+            cu.g += run;
+            while (cu.g >= G) { cu.g -= G; if (++cu.seg == NSEG) { cu.seg = 0; cu.tl++; } }
         }
     };
-    if (nslots == 0) prefetch_piece(0);
-    int tl = 0, seg = 0, g = 0;
+    Cur cf{0, 0, 0};
     for (int k = 0; k < nslots; k++) {
-        prefetch_piece(k);
         const uint32_t f = kfill + (uint32_t)k;
         const int slot = (int)(f % (uint32_t)R.NS);
-        if (f >= (uint32_t)R.NS && !mbar_wait(R.empty + slot, (f / (uint32_t)R.NS - 1u) & 1u)) {
-            if (R.status) atomicExch(R.status, 1002);
-            *R.abort_flag = 1;
-            return false;
+        int good = 1;
+        if (lane == 0) {
+            if (f >= (uint32_t)R.NS && !mbar_wait(R.empty + slot, (f / (uint32_t)R.NS - 1u) & 1u)) {
+                if (R.status) atomicExch(R.status, 1002);
+                *R.abort_flag = 1;
+                good = 0;
+            }
+            if (*R.abort_flag) good = 0;
         }
-        if (*R.abort_flag) return false;
-        int left = min(R.SU, n - k * R.SU);
-        mbar_expect_tx(R.full + slot, (uint32_t)left * UB);
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) return false;
+        const int left = min(R.SU, n - k * R.SU);
+        if (lane == 0) mbar_expect_tx(R.full + slot, (uint32_t)left * UB);
         uint8_t* dst = R.base + (size_t)slot * R.slot_bytes;
-        while (left > 0) {
-            const int run = NSEG == 1 ? left : min(left, G - g);  // one matrix: tiles follow one another in memory
-            const SkSeg& S = J.seg[NSEG == 1 ? 0 : seg];
-            const size_t mu = (size_t)(c.tau_first + tl) * G + g;
-            bulk_g2s(dst, S.rec + mu * (UB / 4), (uint32_t)run * UB, R.full + slot);
-            dst += (size_t)run * UB;
-            left -= run;
-            g += run;
-            while (g >= G) { g -= G; if (++seg == NSEG) { seg = 0; tl++; } }
-        }
+        walk(cf, left, [&](const uint32_t* src, uint32_t bytes) {
+            if (lane == 0) bulk_g2s(dst, src, bytes, R.full + slot);
+            dst += bytes;
+        });
     }
     kfill += (uint32_t)nslots;
     return true;
 }
 
-__device__ __forceinline__ void prefetch_line_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 // Producer warp, ahead of the consumers: asks the L2 for the small operands of a GEMV phase that do
 // not depend on the previous phase (norm weights, spread over the CTAs; the scatter indices and the
 // residual rows of this CTA), so that the consumers' dependent loads do not go to HBM.
-__device__ void warm_operands(const SkParams& P, int NSEG) {
+__device__ __forceinline__ void warm_operands(const SkParams& P, int NSEG) {
     const int lane = threadIdx.x & 31;
     const CtaRange c = sk_cta_range(P);
     const SkJob& J = P.job[c.ji];
@@ -147,6 +141,49 @@ __device__ void warm_operands(const SkParams& P, int NSEG) {
             for (int sc = 0; sc < J.nscatter; sc++) prefetch_line_l2(J.sidx[sc] + row0 + i);
         }
     }
+}
+
+// Producer warp, ahead of the consumers: brings the K/V rows this CTA will read in an attention phase
+// (the same item split as attn_phase) and the output positions of its heads into the L2.  These are
+// real loads, not prefetch hints: hints were found to leave the rows in HBM, and the attention phase
+// has nothing to hide that latency behind.  The values are folded into a word that is stored only
+// if it has a value it cannot have.
+__device__ __forceinline__ void warm_attention(const AttnParams& p, int* sink) {
+    const int lane = threadIdx.x & 31;
+    const int pos = p.pos_fixed >= 0 ? p.pos_fixed : p.ctl->pos;
+    const int T = pos + 1;
+    const int nkv = p.n_kv_local > 0 ? p.n_kv_local : p.n_kv_heads;
+    int nsplit = (T + 255) / 256;
+    nsplit = min(nsplit, min(p.max_split, max(1, (int)gridDim.x / nkv)));
+    const int chunk = (T + nsplit - 1) / nsplit;
+    nsplit = (T + chunk - 1) / chunk;
+    const int KV = p.n_kv_heads * HS;
+    float fold = 0.f;
+    for (int item = blockIdx.x; item < nkv * nsplit; item += gridDim.x) {
+        const int kvh = item % nkv + p.kvh0, split = item / nkv;
+        const int t0 = split * chunk, t1 = min(pos, t0 + chunk);  // row `pos` is written by the phase itself
+        const float4* kc4 = reinterpret_cast<const float4*>(p.kc) + (size_t)kvh * (HS / 4) + lane;
+        const float4* vc4 = reinterpret_cast<const float4*>(p.vc) + (size_t)kvh * (HS / 4) + lane;
+        const size_t rs = (size_t)KV / 4;
+        for (int tb = t0; tb < t1; tb += 8) {
+            float4 a[8], b[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int tt = min(tb + u, t1 - 1);
+                a[u] = __ldcg(kc4 + (size_t)tt * rs);
+                b[u] = __ldcg(vc4 + (size_t)tt * rs);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) fold += a[u].x + b[u].x;
+        }
+        if (p.oidx && split == 0) {  // output positions of the group's heads: ag * 128 indices
+            for (int i = lane; i < p.ag * (HS / 4); i += 32) {
+                const int4 v = __ldg(reinterpret_cast<const int4*>(p.oidx + (size_t)kvh * p.ag * HS) + i);
+                fold += (float)v.x;
+            }
+        }
+    }
+    if (fold == 1.2345678e38f && sink) *sink = 1;  // never true in practice; keeps the loads alive
 }
 
 // Consumer side of one GEMV phase: stage the digits, multiply, reduce, epilogue.  Returns false
@@ -174,12 +211,12 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     if (n > 0) {  // the first barrier inside also orders the zeroing of `partial`
         if (NSEG == 2 && J.in <= 2 * 8 * SK_THREADS) {
             // w1 and w3 read the same x, each in its own K order: one pass over the statistics
-            const float f = stage_digits_pair<W>(J.seg[0], J.seg[NSEG - 1], J.in, P.eps, digits, digits + (size_t)4 * dstride, ss, ss + G * 2, red);
+            const float f = stage_digits_pair<W>(J.seg[0], J.seg[NSEG - 1], J.in, P.eps, digits, digits + (size_t)4 * dstride, ss, ss + G * 2, red, stamp ? stamp + 10 : nullptr);
             if (threadIdx.x == 0) oscale[0] = oscale[1] = f;
         } else {
 #pragma unroll
             for (int s = 0; s < NSEG; s++) {
-                const float f = stage_digits<W>(J.seg[s], J.in, P.eps, digits + (size_t)s * 4 * dstride, ss + s * G * 2, red);
+                const float f = stage_digits<W>(J.seg[s], J.in, P.eps, digits + (size_t)s * 4 * dstride, ss + s * G * 2, red, stamp ? stamp + 10 : nullptr);
                 if (threadIdx.x == 0) oscale[s] = f;
             }
         }
@@ -216,65 +253,73 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
         tot0 = tot1 = 0.f;
     };
     const int zshift = 4 * r;
-    const int* ss_lane = ss + (t & 1);
-    // scale, zero point and digit sums of one finished unit (exact integers up to the final FMA);
-    // gg = position of the unit inside its (super) tile: segment * G + group
-    auto unit_finish = [&](const uint8_t* rec, int tl, int gg, const int (&c)[4]) {
-        const int key = 2 * tl + (NSEG == 2 && gg >= G ? 1 : 0);
-        if (key != cur_key) { flush(); cur_key = key; }  // warp-uniform
-        const uint32_t* mt = reinterpret_cast<const uint32_t*>(rec + 256 * W);
-        const float s0 = __uint_as_float(mt[r]), s1 = __uint_as_float(mt[8 + r]);
-        const uint2 zz = *reinterpret_cast<const uint2*>(mt + 16);
-        const int z0 = (int)((zz.x >> zshift) & 15u) + 1, z1 = (int)((zz.y >> zshift) & 15u) + 1;  // src/gptq.rs:148
-        const int sv = ss_lane[gg * 2];
-        tot0 = fmaf(s0, (float)(c[0] * 128 + c[1] - z0 * sv), tot0);
-        tot1 = fmaf(s1, (float)(c[2] * 128 + c[3] - z1 * sv), tot1);
-    };
-    constexpr uint32_t M = 0x0F0F0F0Fu;
+    // 32-bit shared-space addresses of everything the loop touches
+    const uint32_t ring_a = smem_u32(R.base) + (uint32_t)(2 * warp) * UB;   // this warp's pair inside slot 0
+    const uint32_t full_a = smem_u32(R.full), empty_a = smem_u32(R.empty);
+    const uint32_t ss_a = smem_u32(ss) + 4u * (uint32_t)(t & 1);
     // this lane's digits of the group at position gg; lanes r >= 4 (MMA columns 4..7) read zeros
-    const uint8_t* dg_lane = r < 4 ? digits + (size_t)r * dstride + t * (8 * W) : R.zeros;
-    const int dmul = r < 4 ? 1 : 0;
+    const uint32_t dg_a = r < 4 ? smem_u32(digits) + (uint32_t)(r * dstride + t * (8 * W)) : smem_u32(R.zeros);
+    const uint32_t dmul = r < 4 ? 1u : 0u;
+    constexpr uint32_t META = 256u * W;  // scales, then the two zero-point words
     auto digits_of = [&](int gg) {
         const int seg = NSEG == 2 && gg >= G ? 1 : 0;
-        return dg_lane + (seg * 4 * dstride + (gg - seg * G) * GS) * dmul;
+        return dg_a + (uint32_t)(seg * 4 * dstride + (gg - seg * G) * GS) * dmul;
     };
-    // loads and MMAs of one unit whose record starts at rec
-    auto unit_mma = [&](const uint8_t* rec, const uint8_t* dg, int (&c)[4]) {
+    auto key_of = [&](int tl, int gg) { return 2 * tl + (NSEG == 2 && gg >= G ? 1 : 0); };
+    struct Unit { uint32_t a[W], b[W], d[2 * W]; };
+    auto unit_load = [&](uint32_t rec, uint32_t dg, Unit& u) {
         if constexpr (W == 4) {
-            const uint4 a = *reinterpret_cast<const uint4*>(rec + lane * 16), b = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
-            const uint4 d0 = reinterpret_cast<const uint4*>(dg)[0], d1 = reinterpret_cast<const uint4*>(dg)[1];
-            mma_u8s8_first(c, a.x & M, b.x & M, (a.x >> 4) & M, (b.x >> 4) & M, d0.x, d0.y);
-            mma_u8s8(c, a.y & M, b.y & M, (a.y >> 4) & M, (b.y >> 4) & M, d0.z, d0.w);
-            mma_u8s8(c, a.z & M, b.z & M, (a.z >> 4) & M, (b.z >> 4) & M, d1.x, d1.y);
-            mma_u8s8(c, a.w & M, b.w & M, (a.w >> 4) & M, (b.w >> 4) & M, d1.z, d1.w);
+            const uint4 a = lds128(rec + lane * 16), b = lds128(rec + 512 + lane * 16), d0 = lds128(dg), d1 = lds128(dg + 16);
+            u.a[0] = a.x; u.a[1] = a.y; u.a[2] = a.z; u.a[3] = a.w;
+            u.b[0] = b.x; u.b[1] = b.y; u.b[2] = b.z; u.b[3] = b.w;
+            u.d[0] = d0.x; u.d[1] = d0.y; u.d[2] = d0.z; u.d[3] = d0.w; u.d[4] = d1.x; u.d[5] = d1.y; u.d[6] = d1.z; u.d[7] = d1.w;
         } else if constexpr (W == 2) {
-            const uint2 a = *reinterpret_cast<const uint2*>(rec + lane * 8), b = *reinterpret_cast<const uint2*>(rec + 256 + lane * 8);
-            const uint4 d0 = reinterpret_cast<const uint4*>(dg)[0];
-            mma_u8s8_first(c, a.x & M, b.x & M, (a.x >> 4) & M, (b.x >> 4) & M, d0.x, d0.y);
-            mma_u8s8(c, a.y & M, b.y & M, (a.y >> 4) & M, (b.y >> 4) & M, d0.z, d0.w);
+            const uint2 a = lds64(rec + lane * 8), b = lds64(rec + 256 + lane * 8);
+            const uint4 d0 = lds128(dg);
+            u.a[0] = a.x; u.a[1] = a.y; u.b[0] = b.x; u.b[1] = b.y;
+            u.d[0] = d0.x; u.d[1] = d0.y; u.d[2] = d0.z; u.d[3] = d0.w;
         } else {
-            const uint32_t a = *reinterpret_cast<const uint32_t*>(rec + lane * 4);
-            const uint32_t b = *reinterpret_cast<const uint32_t*>(rec + 128 + lane * 4);
-            const uint2 bb = *reinterpret_cast<const uint2*>(dg);
-            mma_u8s8_first(c, a & M, b & M, (a >> 4) & M, (b >> 4) & M, bb.x, bb.y);
+            u.a[0] = lds32(rec + lane * 4); u.b[0] = lds32(rec + 128 + lane * 4);
+            const uint2 d0 = lds64(dg);
+            u.d[0] = d0.x; u.d[1] = d0.y;
         }
     };
-    auto release = [&](int slot) {
+    constexpr uint32_t M = 0x0F0F0F0Fu;
+    auto unit_mma = [&](const Unit& u, int (&c)[4]) {
+        mma_u8s8_first(c, u.a[0] & M, u.b[0] & M, (u.a[0] >> 4) & M, (u.b[0] >> 4) & M, u.d[0], u.d[1]);
+#pragma unroll
+        for (int i = 1; i < W; i++) mma_u8s8(c, u.a[i] & M, u.b[i] & M, (u.a[i] >> 4) & M, (u.b[i] >> 4) & M, u.d[2 * i], u.d[2 * i + 1]);
+    };
+    struct Meta { uint32_t s0, s1, sv; uint2 zz; };
+    auto meta_load = [&](uint32_t rec, int gg, Meta& mt) {
+        mt.s0 = lds32(rec + META + 4 * r);
+        mt.s1 = lds32(rec + META + 32 + 4 * r);
+        mt.zz = lds64(rec + META + 64);
+        mt.sv = lds32(ss_a + 8u * (uint32_t)gg);
+    };
+    // scale, zero point and digit sums of one finished unit (exact integers up to the final FMA)
+    auto unit_finish = [&](const Meta& mt, int key, const int (&c)[4]) {
+        if (key != cur_key) { flush(); cur_key = key; }  // warp-uniform
+        const int z0 = (int)((mt.zz.x >> zshift) & 15u) + 1, z1 = (int)((mt.zz.y >> zshift) & 15u) + 1;  // src/gptq.rs:148
+        const int sv = (int)mt.sv;
+        tot0 = fmaf(__uint_as_float(mt.s0), (float)(c[0] * 128 + c[1] - z0 * sv), tot0);
+        tot1 = fmaf(__uint_as_float(mt.s1), (float)(c[2] * 128 + c[3] - z1 * sv), tot1);
+    };
+    auto release = [&](uint32_t slot) {
         __syncwarp();  // every lane has read the slot
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(R.empty + slot)) : "memory");
+        if (lane == 0) mbar_arrive_u32(empty_a + 8u * slot);
     };
     // position of this warp's first unit of the current fill; advanced by SU units per fill
     int tl0 = (2 * warp) / Gs, gg0 = (2 * warp) % Gs;
     // the pair of the previous fill, finished one iteration later
     int pc0[4] = {0, 0, 0, 0}, pc1[4] = {0, 0, 0, 0};
-    const uint8_t* p_rec = nullptr;
-    int p_tl0 = 0, p_gg0 = 0, p_tl1 = 0, p_gg1 = 0, p_n = 0, p_slot = -1;
+    uint32_t p_rec = 0, p_slot = 0;
+    int p_gg0 = 0, p_gg1 = 0, p_key0 = 0, p_key1 = 0, p_n = -1;
     uint32_t fslot = kbase % (uint32_t)NS, fpar = (kbase / (uint32_t)NS) & 1u;  // slot and parity of the next fill
-    const uint8_t* rec_lane = R.base + (uint32_t)(2 * warp) * UB;
     for (int k = 0; k < nslots; k++) {
-        const int slot = (int)fslot;
+        const uint32_t slot = fslot;
         const int m = min(SU, n - k * SU);
-        bool got = mbar_try_wait(R.full + slot, fpar);
+        bool got = mbar_try_wait_u32(full_a + 8u * slot, fpar);
         if (!__all_sync(0xffffffffu, got)) {  // not there yet: the bounded wait
             got = !*R.abort_flag && mbar_wait(R.full + slot, fpar);
             if (!__all_sync(0xffffffffu, got)) {
@@ -283,43 +328,60 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
                 break;
             }
         }
-        const uint8_t* rec0 = rec_lane + (uint32_t)slot * R.slot_bytes;
+        if (R.skip) {
+            release(slot);
+            if (++fslot == (uint32_t)NS) { fslot = 0; fpar ^= 1u; }
+            continue;
+        }
+        const uint32_t rec0 = ring_a + slot * R.slot_bytes;
         int tl1 = tl0, gg1 = gg0 + 1;
         if (gg1 == Gs) { gg1 = 0; tl1++; }
         int c0[4], c1[4];
         if (m == 2 * SK_WARPS) {  // a full slot: straight-line
-            unit_mma(rec0, digits_of(gg0), c0);
-            unit_mma(rec0 + UB, digits_of(gg1), c1);
-            if (k > 0) {  // the previous fill was a full one as well; runs while the MMAs above are in flight
-                unit_finish(p_rec, p_tl0, p_gg0, pc0);
-                unit_finish(p_rec + UB, p_tl1, p_gg1, pc1);
+            Unit u0, u1;
+            unit_load(rec0, digits_of(gg0), u0);
+            unit_load(rec0 + UB, digits_of(gg1), u1);
+            if (k > 0) {  // the previous fill was a full one as well; its last step runs while the MMAs are in flight
+                Meta m0, m1;
+                meta_load(p_rec, p_gg0, m0);
+                meta_load(p_rec + UB, p_gg1, m1);
+                unit_mma(u0, c0);
+                unit_mma(u1, c1);
+                unit_finish(m0, p_key0, pc0);
+                unit_finish(m1, p_key1, pc1);
                 release(p_slot);
+            } else {
+                unit_mma(u0, c0);
+                unit_mma(u1, c1);
             }
             p_n = 2;
         } else {  // the last, partial fill
             const int j = 2 * warp;
             const int nu = j + 1 < m ? 2 : (j < m ? 1 : 0);
             c0[0] = c0[1] = c0[2] = c0[3] = c1[0] = c1[1] = c1[2] = c1[3] = 0;
-            if (nu > 0) unit_mma(rec0, digits_of(gg0), c0);
-            if (nu > 1) unit_mma(rec0 + UB, digits_of(gg1), c1);
+            if (nu > 0) { Unit u; unit_load(rec0, digits_of(gg0), u); unit_mma(u, c0); }
+            if (nu > 1) { Unit u; unit_load(rec0 + UB, digits_of(gg1), u); unit_mma(u, c1); }
             if (k > 0) {
-                unit_finish(p_rec, p_tl0, p_gg0, pc0);
-                unit_finish(p_rec + UB, p_tl1, p_gg1, pc1);
+                Meta m0, m1;
+                meta_load(p_rec, p_gg0, m0);
+                meta_load(p_rec + UB, p_gg1, m1);
+                unit_finish(m0, p_key0, pc0);
+                unit_finish(m1, p_key1, pc1);
                 release(p_slot);
             }
             p_n = nu;
         }
         p_rec = rec0; p_slot = slot;
-        p_tl0 = tl0; p_gg0 = gg0; p_tl1 = tl1; p_gg1 = gg1;
+        p_gg0 = gg0; p_gg1 = gg1; p_key0 = key_of(tl0, gg0); p_key1 = key_of(tl1, gg1);
 #pragma unroll
         for (int i = 0; i < 4; i++) { pc0[i] = c0[i]; pc1[i] = c1[i]; }
         gg0 += SU;
         while (gg0 >= Gs) { gg0 -= Gs; tl0++; }
         if (++fslot == (uint32_t)NS) { fslot = 0; fpar ^= 1u; }
     }
-    if (ok && p_slot >= 0) {
-        if (p_n > 0) unit_finish(p_rec, p_tl0, p_gg0, pc0);
-        if (p_n > 1) unit_finish(p_rec + UB, p_tl1, p_gg1, pc1);
+    if (ok && p_n >= 0) {
+        if (p_n > 0) { Meta m0; meta_load(p_rec, p_gg0, m0); unit_finish(m0, p_key0, pc0); }
+        if (p_n > 1) { Meta m1; meta_load(p_rec + UB, p_gg1, m1); unit_finish(m1, p_key1, pc1); }
         release(p_slot);
     }
     kbase += (uint32_t)nslots;
@@ -382,7 +444,7 @@ __device__ __forceinline__ float tk_warp_sum(float v) {
     return v;
 }
 
-__device__ __noinline__ void embed_phase(const EmbedParams& p) {
+__device__ __forceinline__ void embed_phase(const EmbedParams& p) {
     const int pos = p.ctl->pos;
     int token = p.ctl->token;
     if (p.feed_prompt) token = pos == 0 ? 1 : p.prompt[pos - 1];  // src/inference.rs:29-35
@@ -401,11 +463,11 @@ __device__ __noinline__ void embed_phase(const EmbedParams& p) {
 constexpr int TK_ATT_WARPS = SK_WARPS;
 
 __host__ __device__ constexpr size_t tk_att_bytes(int ag) {
-    return ((size_t)ag * HS + (size_t)TK_ATT_WARPS * ag * HS + 2 * (size_t)TK_ATT_WARPS * ag + 4) * 4;
+    return ((size_t)ag * HS + (size_t)TK_ATT_WARPS * ag * HS + 2 * (size_t)TK_ATT_WARPS * ag + 4 + 2 * HS) * 4;
 }
 
 template <int AG>
-__device__ __noinline__ void attn_phase(const AttnParams& p, uint8_t* scratch) {
+__device__ __forceinline__ void attn_phase(const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* base = reinterpret_cast<float*>(scratch);
     float(*qs)[HS] = reinterpret_cast<float(*)[HS]>(base);
@@ -413,8 +475,10 @@ __device__ __noinline__ void attn_phase(const AttnParams& p, uint8_t* scratch) {
     float(*sm_m)[AG] = reinterpret_cast<float(*)[AG]>(base + AG * HS + TK_ATT_WARPS * AG * HS);
     float(*sm_l)[AG] = reinterpret_cast<float(*)[AG]>(base + AG * HS + TK_ATT_WARPS * AG * HS + TK_ATT_WARPS * AG);
     volatile int* sm_last = reinterpret_cast<volatile int*>(base + AG * HS + TK_ATT_WARPS * AG * HS + 2 * TK_ATT_WARPS * AG);
+    float* new_k = base + AG * HS + TK_ATT_WARPS * AG * HS + 2 * TK_ATT_WARPS * AG + 4;  // the row of `pos`: k (rotated), then v
+    float* new_v = new_k + HS;
 
-    const int pos = p.pos_fixed >= 0 ? p.pos_fixed : p.ctl->pos;
+    if (p.pos_fixed >= 0) pos = p.pos_fixed;
     const int T = pos + 1;
     const int nkv = p.n_kv_local > 0 ? p.n_kv_local : p.n_kv_heads;
     // splits: about 256 positions each, no more than the CTAs can take in one round
@@ -425,37 +489,72 @@ __device__ __noinline__ void attn_phase(const AttnParams& p, uint8_t* scratch) {
     const int nitems = nkv * nsplit;
     const int KV = p.n_kv_heads * HS;
     const float inv_div = sqrtf((float)HS);
+    constexpr int U = AG >= 4 ? 2 : 4;
+    // combine: thread (j0, i) owns element i of heads j0, j0 + 4, ...
+    const int i = tid & (HS - 1), j0 = tid >> 7;
 
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
         const int kvh = item % nkv + p.kvh0, split = item / nkv;
         const int t0 = split * chunk, t1 = min(T, t0 + chunk);
+        const int nwarps = min(TK_ATT_WARPS, (t1 - t0 + U - 1) / U);  // warps that have rows in the first round
+        // Loads that do not depend on this token's projections are issued first, so that their latency
+        // overlaps the loads of q/k/v and the RoPE below: the first round of K/V rows (except the row
+        // of `pos` itself) and the output positions.
+        const float4* kc4 = reinterpret_cast<const float4*>(p.kc) + (size_t)kvh * (HS / 4) + lane;
+        const float4* vc4 = reinterpret_cast<const float4*>(p.vc) + (size_t)kvh * (HS / 4) + lane;
+        const size_t rs = (size_t)KV / 4;
+        float4 kk[U], vv[U];
+        const int tb0 = t0 + warp * U;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int tt = min(tb0 + u, t1 - 1);
+            if (tt != pos && tb0 < t1) {
+                kk[u] = kc4[(size_t)tt * rs];
+                vv[u] = vc4[(size_t)tt * rs];
+            } else {
+                kk[u] = vv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        int oi[(AG + 3) / 4];
+#pragma unroll
+        for (int gi = 0; gi < (AG + 3) / 4; gi++) {
+            const int g = j0 + 4 * gi;
+            const int o = (kvh * AG + min(g, AG - 1)) * HS + i;
+            oi[gi] = p.oidx ? __ldg(p.oidx + o) : o;
+        }
+        if (stamp && tid == 0) stamp[10] = clock64();
         // rotate-half RoPE updated in place: the second half uses the already rotated first half (src/models.rs:106-116)
         for (int idx = tid; idx < AG * (HS / 2); idx += SK_THREADS) {
-            const int g = idx / (HS / 2), i = idx % (HS / 2);
+            const int g = idx / (HS / 2), e = idx % (HS / 2);
             const int h = kvh * AG + g;
-            const float c = __ldg(p.rope_cos + (size_t)pos * (HS / 2) + i), s = __ldg(p.rope_sin + (size_t)pos * (HS / 2) + i);
-            const float a = __ldcg(p.q + (size_t)h * HS + i), b = __ldcg(p.q + (size_t)h * HS + HS / 2 + i);
+            const float c = __ldg(p.rope_cos + (size_t)pos * (HS / 2) + e), s = __ldg(p.rope_sin + (size_t)pos * (HS / 2) + e);
+            const float a = __ldcg(p.q + (size_t)h * HS + e), b = __ldcg(p.q + (size_t)h * HS + HS / 2 + e);
             const float na = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
             const float nb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(na, s));
-            qs[g][i] = na;
-            qs[g][HS / 2 + i] = nb;
+            qs[g][e] = na;
+            qs[g][HS / 2 + e] = nb;
         }
         if (split == nsplit - 1 && warp >= SK_WARPS - 6) {  // this CTA owns position `pos`: append k (rotated) and v
             const int u = tid - (SK_WARPS - 6) * 32;          // 0..191, taken from the warps the RoPE of q uses last
             if (u < HS / 2) {
-                const int i = u;
-                const float c = __ldg(p.rope_cos + (size_t)pos * (HS / 2) + i), s = __ldg(p.rope_sin + (size_t)pos * (HS / 2) + i);
-                const float a = __ldcg(p.k + (size_t)kvh * HS + i), b = __ldcg(p.k + (size_t)kvh * HS + HS / 2 + i);
+                const int e = u;
+                const float c = __ldg(p.rope_cos + (size_t)pos * (HS / 2) + e), s = __ldg(p.rope_sin + (size_t)pos * (HS / 2) + e);
+                const float a = __ldcg(p.k + (size_t)kvh * HS + e), b = __ldcg(p.k + (size_t)kvh * HS + HS / 2 + e);
                 const float na = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
                 const float nb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(na, s));
-                p.kc[(size_t)pos * KV + kvh * HS + i] = na;
-                p.kc[(size_t)pos * KV + kvh * HS + HS / 2 + i] = nb;
+                p.kc[(size_t)pos * KV + kvh * HS + e] = na;
+                p.kc[(size_t)pos * KV + kvh * HS + HS / 2 + e] = nb;
+                new_k[e] = na;
+                new_k[HS / 2 + e] = nb;
             } else {
-                const int i = u - HS / 2;  // 0..127
-                p.vc[(size_t)pos * KV + kvh * HS + i] = __ldcg(p.v + (size_t)kvh * HS + i);
+                const int e = u - HS / 2;  // 0..127
+                const float vv0 = __ldcg(p.v + (size_t)kvh * HS + e);
+                p.vc[(size_t)pos * KV + kvh * HS + e] = vv0;
+                new_v[e] = vv0;
             }
         }
         consumer_sync();
+        if (stamp && tid == 0) stamp[11] = clock64();
 
         float4 qr[AG], acc[AG];
         float m[AG], l[AG];
@@ -466,28 +565,42 @@ __device__ __noinline__ void attn_phase(const AttnParams& p, uint8_t* scratch) {
             l[g] = 0.f;
             acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        const float4* kc4 = reinterpret_cast<const float4*>(p.kc) + (size_t)kvh * (HS / 4) + lane;
-        const float4* vc4 = reinterpret_cast<const float4*>(p.vc) + (size_t)kvh * (HS / 4) + lane;
-        const size_t rs = (size_t)KV / 4;
-        constexpr int U = AG >= 8 ? 2 : 4;
-        for (int tb = t0 + warp * U; tb < t1; tb += TK_ATT_WARPS * U) {
-            float4 kk[U], vv[U];
+        // the row this phase has just written comes from shared memory, not through the L2
+        auto load_k = [&](int tt, float4& k) { k = tt == pos ? reinterpret_cast<const float4*>(new_k)[lane] : kc4[(size_t)tt * rs]; };
+        auto load_v = [&](int tt, float4& v) { v = tt == pos ? reinterpret_cast<const float4*>(new_v)[lane] : vc4[(size_t)tt * rs]; };
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int tt = min(tb + u, t1 - 1);
-                kk[u] = kc4[(size_t)tt * rs];
-                vv[u] = vc4[(size_t)tt * rs];
+        for (int u = 0; u < U; u++) {
+            const int tt = min(tb0 + u, t1 - 1);
+            if (tt == pos && tb0 < t1) { load_k(tt, kk[u]); load_v(tt, vv[u]); }
+        }
+        for (int tb = tb0; tb < t1; tb += TK_ATT_WARPS * U) {
+            const int tbn = tb + TK_ATT_WARPS * U;  // the next round's rows are requested as soon as a register is free
+            // all scores of the round first (independent warp reductions), then the running softmax in row order
+            float sc[U][AG];
+#pragma unroll
+            for (int u = 0; u < U; u++)
+#pragma unroll
+                for (int g = 0; g < AG; g++)
+                    sc[u][g] = qr[g].x * kk[u].x + qr[g].y * kk[u].y + qr[g].z * kk[u].z + qr[g].w * kk[u].w;
+            if (tbn < t1) {
+#pragma unroll
+                for (int u = 0; u < U; u++) load_k(min(tbn + u, t1 - 1), kk[u]);
             }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int u = 0; u < U; u++)
+#pragma unroll
+                    for (int g = 0; g < AG; g++) sc[u][g] += __shfl_xor_sync(0xffffffffu, sc[u][g], o);
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 if (tb + u < t1) {
 #pragma unroll
                     for (int g = 0; g < AG; g++) {
-                        float d = qr[g].x * kk[u].x + qr[g].y * kk[u].y + qr[g].z * kk[u].z + qr[g].w * kk[u].w;
-                        d = tk_warp_sum(d);
-                        const float sc = __fdiv_rn(d, inv_div);  // src/models.rs:158
-                        const float mn = fmaxf(m[g], sc);
-                        const float corr = expf(m[g] - mn), pr = expf(sc - mn);
+                        const float s1 = __fdiv_rn(sc[u][g], inv_div);  // src/models.rs:158
+                        const float mn = fmaxf(m[g], s1);
+                        const float ex = expf(-fabsf(s1 - m[g]));  // the larger of the two has the factor exp(0) = 1
+                        const float corr = s1 > m[g] ? ex : 1.0f, pr = s1 > m[g] ? 1.0f : ex;
                         l[g] = l[g] * corr + pr;
                         acc[g].x = acc[g].x * corr + pr * vv[u].x;
                         acc[g].y = acc[g].y * corr + pr * vv[u].y;
@@ -496,31 +609,51 @@ __device__ __noinline__ void attn_phase(const AttnParams& p, uint8_t* scratch) {
                         m[g] = mn;
                     }
                 }
+                if (tbn < t1) load_v(min(tbn + u, t1 - 1), vv[u]);
             }
         }
+        if (stamp && tid == 0) stamp[12] = clock64() + (acc[0].x == 1.2345f ? 1 : 0);
+        if (warp < nwarps) {
 #pragma unroll
-        for (int g = 0; g < AG; g++) {
-            reinterpret_cast<float4*>(sm_acc[warp][g])[lane] = acc[g];
-            if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+            for (int g = 0; g < AG; g++) {
+                reinterpret_cast<float4*>(sm_acc[warp][g])[lane] = acc[g];
+                if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+            }
         }
         consumer_sync();
 
-        // combine the warps in warp order: thread (j, i) owns element i of heads j, j + 4, ...
-        const int i = tid & (HS - 1), j0 = tid >> 7;
-        if (nsplit > 1) {
-            for (int g = j0; g < AG; g += SK_THREADS / HS) {
-                float mm = -INFINITY;
-                for (int w = 0; w < TK_ATT_WARPS; w++) mm = fmaxf(mm, sm_m[w][g]);
-                float ll = 0.f, aa = 0.f;
+        // combine the warps that had rows, in warp order
+#pragma unroll
+        for (int gi = 0; gi < (AG + 3) / 4; gi++) {
+            const int g = j0 + 4 * gi;
+            if (g < AG) {
+                // unrolled over all warps (those without rows count as empty): the exponentials are
+                // independent and overlap, the sums are taken in warp order
+                float mw[TK_ATT_WARPS], mm = -INFINITY;
+#pragma unroll
                 for (int w = 0; w < TK_ATT_WARPS; w++) {
-                    const float e = sm_m[w][g] == -INFINITY ? 0.f : expf(sm_m[w][g] - mm);
-                    ll += sm_l[w][g] * e;
-                    aa += sm_acc[w][g][i] * e;
+                    mw[w] = w < nwarps ? sm_m[w][g] : -INFINITY;
+                    mm = fmaxf(mm, mw[w]);
                 }
-                float* dst = p.part + ((size_t)(kvh * AG + g) * p.max_split + split) * (HS + 2);
-                dst[i] = aa;
-                if (i == 0) { dst[HS] = mm; dst[HS + 1] = ll; }
+                float ll = 0.f, aa = 0.f;
+#pragma unroll
+                for (int w = 0; w < TK_ATT_WARPS; w++) {
+                    const float e = mw[w] == -INFINITY ? 0.f : expf(mw[w] - mm);
+                    if (w < nwarps) {
+                        ll += sm_l[w][g] * e;
+                        aa += sm_acc[w][g][i] * e;
+                    }
+                }
+                if (nsplit == 1) {
+                    p.out[oi[gi]] = aa / ll;
+                } else {
+                    float* dst = p.part + ((size_t)(kvh * AG + g) * p.max_split + split) * (HS + 2);
+                    dst[i] = aa;
+                    if (i == 0) { dst[HS] = mm; dst[HS + 1] = ll; }
+                }
             }
+        }
+        if (nsplit > 1) {
             __threadfence();
             consumer_sync();
             if (tid == 0) {
@@ -530,42 +663,33 @@ __device__ __noinline__ void attn_phase(const AttnParams& p, uint8_t* scratch) {
                 *sm_last = last;
             }
             consumer_sync();
-            if (*sm_last) {
+            if (*sm_last) {  // the CTA that finishes the last split merges the splits in split order
                 __threadfence();
-                for (int g = j0; g < AG; g += SK_THREADS / HS) {
-                    const float* src = p.part + (size_t)(kvh * AG + g) * p.max_split * (HS + 2);
-                    float mm = -INFINITY;
-                    for (int s = 0; s < nsplit; s++) mm = fmaxf(mm, __ldcg(src + (size_t)s * (HS + 2) + HS));
-                    float ll = 0.f, aa = 0.f;
-                    for (int s = 0; s < nsplit; s++) {
-                        const float e = expf(__ldcg(src + (size_t)s * (HS + 2) + HS) - mm);
-                        ll += __ldcg(src + (size_t)s * (HS + 2) + HS + 1) * e;
-                        aa += __ldcg(src + (size_t)s * (HS + 2) + i) * e;
+#pragma unroll
+                for (int gi = 0; gi < (AG + 3) / 4; gi++) {
+                    const int g = j0 + 4 * gi;
+                    if (g < AG) {
+                        const float* src = p.part + (size_t)(kvh * AG + g) * p.max_split * (HS + 2);
+                        float mm = -INFINITY;
+                        for (int s = 0; s < nsplit; s++) mm = fmaxf(mm, __ldcg(src + (size_t)s * (HS + 2) + HS));
+                        float ll = 0.f, aa = 0.f;
+                        for (int s = 0; s < nsplit; s++) {
+                            const float e = expf(__ldcg(src + (size_t)s * (HS + 2) + HS) - mm);
+                            ll += __ldcg(src + (size_t)s * (HS + 2) + HS + 1) * e;
+                            aa += __ldcg(src + (size_t)s * (HS + 2) + i) * e;
+                        }
+                        p.out[oi[gi]] = aa / ll;
                     }
-                    const int o = (kvh * AG + g) * HS + i;
-                    p.out[p.oidx ? __ldg(p.oidx + o) : o] = aa / ll;
                 }
-            }
-        } else {
-            for (int g = j0; g < AG; g += SK_THREADS / HS) {
-                float mm = -INFINITY;
-                for (int w = 0; w < TK_ATT_WARPS; w++) mm = fmaxf(mm, sm_m[w][g]);
-                float ll = 0.f, aa = 0.f;
-                for (int w = 0; w < TK_ATT_WARPS; w++) {
-                    const float e = sm_m[w][g] == -INFINITY ? 0.f : expf(sm_m[w][g] - mm);
-                    ll += sm_l[w][g] * e;
-                    aa += sm_acc[w][g][i] * e;
-                }
-                const int o = (kvh * AG + g) * HS + i;
-                p.out[p.oidx ? __ldg(p.oidx + o) : o] = aa / ll;
             }
         }
         consumer_sync();  // the scratch is reused by the next item
+        if (stamp && tid == 0) stamp[13] = clock64();
     }
 }
 
 // final rmsnorm + dense f32 classifier (src/models.rs:288-297, src/model.rs:22-31)
-__device__ __noinline__ void cls_phase(const ClsParams& p, float* xs, float* red) {
+__device__ __forceinline__ void cls_phase(const ClsParams& p, float* xs, float* red) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r0 = (int)(((long long)blockIdx.x * p.rows) / gridDim.x);
     const int r1 = (int)(((long long)(blockIdx.x + 1) * p.rows) / gridDim.x);
@@ -622,7 +746,7 @@ __device__ __forceinline__ unsigned tk_random_u32(unsigned long long& s) {  // s
 
 // Next-token selection by the consumer threads of one CTA: forced / prompt / argmax (last maximum
 // wins, src/util.rs:39-46) / temperature sample (src/inference.rs:164-173, src/util.rs:102-113).
-__device__ __noinline__ void select_phase(const SelectParams& p, float* scratch) {
+__device__ __forceinline__ void select_phase(const SelectParams& p, float* scratch) {
     float* s_val = scratch;                                   // [SK_WARPS]
     int* s_idx = reinterpret_cast<int*>(scratch + SK_WARPS);   // [SK_WARPS]
     float* s_f = scratch + 2 * SK_WARPS;                       // [SK_WARPS + 2]
@@ -721,7 +845,7 @@ __device__ __noinline__ void select_phase(const SelectParams& p, float* scratch)
 
 // ---- the kernel ------------------------------------------------------------------------------------
 
-template <int W>
+template <int W, int AG>
 __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_constant__ TokenParams tk) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(16) PhaseRec recs[TK_NREC];
@@ -751,15 +875,19 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
     R.abort_flag = &abort_flag;
     R.status = tk.status;
     R.zeros = reinterpret_cast<const uint8_t*>(zeros);
+    R.skip = tk.skip & 1;
 
     // ================= producer warp ================================================================
     if (warp == SK_WARPS) {
         uint32_t kfill = 0;
-        for (int p = 0; p < tk.nphases; p++) {
-            bool okp = true;
-            if (p >= TK_NREC) {  // its record buffer is free once the consumers have finished phase p - TK_NREC
+        // Phase records travel into their shared-memory buffers as bulk copies that complete on
+        // rec_full[]; they are requested two phases ahead so that the switch from one phase to the
+        // next costs no trip to global memory.
+        bool okp = true;
+        auto request_record = [&](int q) {
+            if (q >= TK_NREC) {  // the buffer is free once the consumers have finished phase q - TK_NREC
                 uint32_t it = 0;
-                while (consumer_phase < p - TK_NREC + 1) {
+                while (consumer_phase < q - TK_NREC + 1) {
                     if (abort_flag || ++it > (1u << 24)) { okp = false; break; }
                     __nanosleep(64);
                 }
@@ -767,27 +895,41 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
             okp = __all_sync(0xffffffffu, okp);
             if (!okp) {
                 if (lane == 0 && !abort_flag) { if (tk.status) atomicExch(tk.status, 1003); abort_flag = 1; }
+                return;
+            }
+            if (lane == 0) {
+                mbar_expect_tx(rec_full + q % TK_NREC, (uint32_t)sizeof(PhaseRec));
+                bulk_g2s(&recs[q % TK_NREC], tk.phases + q, (uint32_t)sizeof(PhaseRec), rec_full + q % TK_NREC);
+            }
+        };
+        for (int q = 0; q < 2 && q < tk.nphases && okp; q++) request_record(q);
+        for (int p = 0; p < tk.nphases && okp; p++) {
+            if (p + 2 < tk.nphases) request_record(p + 2);
+            if (!okp) break;
+            bool got = mbar_wait(rec_full + p % TK_NREC, (uint32_t)(p / TK_NREC) & 1u);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+                if (lane == 0 && !abort_flag) { if (tk.status) atomicExch(tk.status, 1006); abort_flag = 1; }
                 break;
             }
-            const uint4* src = reinterpret_cast<const uint4*>(tk.phases + p);
-            uint4* dst = reinterpret_cast<uint4*>(&recs[p % TK_NREC]);
-            for (int i = lane; i < (int)(sizeof(PhaseRec) / 16); i += 32) dst[i] = __ldg(src + i);
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(rec_full + p % TK_NREC)) : "memory");
-            __syncwarp();
             const PhaseRec& rec = recs[p % TK_NREC];
             if (rec.type == PH_GEMV1 || rec.type == PH_GEMV2) {
+                // An attention phase that follows is warmed up first, a whole phase early: once this
+                // phase's weights are on their way its loads would queue behind them.
+                if (p + 1 < tk.nphases) {
+                    bool got1 = mbar_wait(rec_full + (p + 1) % TK_NREC, (uint32_t)((p + 1) / TK_NREC) & 1u);
+                    got1 = __all_sync(0xffffffffu, got1);
+                    if (got1 && recs[(p + 1) % TK_NREC].type == PH_ATTN) warm_attention(recs[(p + 1) % TK_NREC].u.at, nullptr);
+                }
                 warm_operands(rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1);
-                int good = 1;
-                if (lane == 0) good = produce_units<W>(rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1, R, kfill) ? 1 : 0;
-                good = __shfl_sync(0xffffffffu, good, 0);
-                if (!good) break;
+                if (!produce_units<W>(rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1, R, kfill)) break;
             }
         }
         return;
     }
 
     // ================= consumer warps ===============================================================
+    const int tok_pos = tk.ctl->pos;  // read once: the attention phases would pay a trip to the L2 each
     uint32_t kbase = 0;
     unsigned bar_target = 0;
     bool ok = true;
@@ -807,12 +949,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
             case PH_GEMV1: ok = gemv_phase<W, 1>(rec.u.sk, smem, R, red, oscale, kbase, stamp); break;
             case PH_GEMV2: ok = gemv_phase<W, 2>(rec.u.sk, smem, R, red, oscale, kbase, stamp); break;
             case PH_ATTN:
-                switch (rec.u.at.ag) {
-                    case 1: attn_phase<1>(rec.u.at, smem); break;
-                    case 2: attn_phase<2>(rec.u.at, smem); break;
-                    case 4: attn_phase<4>(rec.u.at, smem); break;
-                    default: attn_phase<8>(rec.u.at, smem); break;
-                }
+                attn_phase<AG>(rec.u.at, smem, tok_pos, stamp);
                 break;
             case PH_CLS: cls_phase(rec.u.cl, reinterpret_cast<float*>(smem), red); break;
             case PH_SELECT: if (blockIdx.x == 0) select_phase(rec.u.se, red); break;
@@ -854,7 +991,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
 
 size_t token_attn_scratch_bytes(int ag) { return tk_att_bytes(ag); }
 
-template <int W>
+template <int W, int AG>
 static cudaError_t launch_token_t(const TokenParams& tk, int grid, size_t smem, cudaStream_t st) {
     cudaLaunchConfig_t cfg{};
     cudaLaunchAttribute attr[1];
@@ -867,14 +1004,28 @@ static cudaError_t launch_token_t(const TokenParams& tk, int grid, size_t smem, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     g_launches++;
-    return cudaLaunchKernelEx(&cfg, token_kernel<W>, tk);
+    return cudaLaunchKernelEx(&cfg, token_kernel<W, AG>, tk);
 }
 
-cudaError_t launch_token(const TokenParams& tk, int group_size, int grid, size_t smem, cudaStream_t st) {
+template <int W>
+static cudaError_t launch_token_w(const TokenParams& tk, int ag, int grid, size_t smem, cudaStream_t st) {
+    switch (ag) {
+        case 1: return launch_token_t<W, 1>(tk, grid, smem, st);
+        case 2: return launch_token_t<W, 2>(tk, grid, smem, st);
+        case 4: return launch_token_t<W, 4>(tk, grid, smem, st);
+        case 8: return launch_token_t<W, 8>(tk, grid, smem, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+// One instantiation per (group size, query heads per kv head): everything is inlined into the kernel,
+// which keeps its working set in registers (local memory is close to uncached here, almost all of the
+// L1 being configured as shared memory).
+cudaError_t launch_token(const TokenParams& tk, int group_size, int ag, int grid, size_t smem, cudaStream_t st) {
     switch (group_size) {
-        case 128: return launch_token_t<4>(tk, grid, smem, st);
-        case 64: return launch_token_t<2>(tk, grid, smem, st);
-        default: return launch_token_t<1>(tk, grid, smem, st);
+        case 128: return launch_token_w<4>(tk, ag, grid, smem, st);
+        case 64: return launch_token_w<2>(tk, ag, grid, smem, st);
+        default: return launch_token_w<1>(tk, ag, grid, smem, st);
     }
 }
 
@@ -882,11 +1033,13 @@ cudaError_t launch_token(const TokenParams& tk, int group_size, int grid, size_t
 cudaError_t token_init(int max_optin) {
     cudaError_t e;
     cudaFuncAttributes fa;
-#define L2_TK_ATTR(W)                                                                                     \
-    if ((e = cudaFuncGetAttributes(&fa, token_kernel<W>)) != cudaSuccess) return e;                       \
-    if ((e = cudaFuncSetAttribute(token_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+#define L2_TK_ATTR(W, AG)                                                                                 \
+    if ((e = cudaFuncGetAttributes(&fa, token_kernel<W, AG>)) != cudaSuccess) return e;                   \
+    if ((e = cudaFuncSetAttribute(token_kernel<W, AG>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
                                   max_optin - (int)fa.sharedSizeBytes)) != cudaSuccess) return e;
-    L2_TK_ATTR(4) L2_TK_ATTR(2) L2_TK_ATTR(1)
+#define L2_TK_ATTR_W(W) L2_TK_ATTR(W, 1) L2_TK_ATTR(W, 2) L2_TK_ATTR(W, 4) L2_TK_ATTR(W, 8)
+    L2_TK_ATTR_W(4) L2_TK_ATTR_W(2) L2_TK_ATTR_W(1)
+#undef L2_TK_ATTR_W
 #undef L2_TK_ATTR
     return cudaSuccess;
 }
