@@ -403,7 +403,7 @@ static int plan_token(l2_state* s) {
     s->tk.fixed_bytes = (unsigned)fixed;
     s->tk.status = &s->ctl->status;
     s->tk.ctl = s->ctl;
-    s->tk.skip = (getenv("L2_SK_SKIP") ? 1 : 0) | (getenv("L2_TK_HOLD") ? 2 : 0);
+    s->tk.skip = getenv("L2_SK_SKIP") ? 1 : 0;
     s->tk_smem = fixed + (size_t)slots * sk_slot_bytes(c.group_size, su);
     if (int rc = dev_alloc(reinterpret_cast<void**>(&s->tk.bar), 256, s->allocs)) return rc;
     return L2_OK;

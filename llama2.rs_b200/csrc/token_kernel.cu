@@ -467,7 +467,7 @@ __host__ __device__ constexpr size_t tk_att_bytes(int ag) {
 }
 
 template <int AG>
-__device__ __forceinline__ void attn_phase(const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp) {
+__device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* base = reinterpret_cast<float*>(scratch);
     float(*qs)[HS] = reinterpret_cast<float(*)[HS]>(base);
@@ -686,6 +686,7 @@ __device__ __forceinline__ void attn_phase(const AttnParams& p, uint8_t* scratch
         consumer_sync();  // the scratch is reused by the next item
         if (stamp && tid == 0) stamp[13] = clock64();
     }
+    return nitems;
 }
 
 // final rmsnorm + dense f32 classifier (src/models.rs:288-297, src/model.rs:22-31)
@@ -875,7 +876,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
     R.abort_flag = &abort_flag;
     R.status = tk.status;
     R.zeros = reinterpret_cast<const uint8_t*>(zeros);
-    R.skip = tk.skip & 1;
+    R.skip = tk.skip;
 
     // ================= producer warp ================================================================
     if (warp == SK_WARPS) {
@@ -948,9 +949,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
             case PH_EMBED: embed_phase(rec.u.em); break;
             case PH_GEMV1: ok = gemv_phase<W, 1>(rec.u.sk, smem, R, red, oscale, kbase, stamp); break;
             case PH_GEMV2: ok = gemv_phase<W, 2>(rec.u.sk, smem, R, red, oscale, kbase, stamp); break;
-            case PH_ATTN:
-                attn_phase<AG>(rec.u.at, smem, tok_pos, stamp);
-                break;
+            case PH_ATTN: attn_phase<AG>(rec.u.at, smem, tok_pos, stamp); break;
             case PH_CLS: cls_phase(rec.u.cl, reinterpret_cast<float*>(smem), red); break;
             case PH_SELECT: if (blockIdx.x == 0) select_phase(rec.u.se, red); break;
             case PH_ADVANCE: if (blockIdx.x == 0 && threadIdx.x == 0) rec.u.se.ctl->pos = rec.u.se.ctl->pos + 1; break;
