@@ -32,6 +32,7 @@ WORKLOADS = {  # name: (model size, group size, prompt tokens, decode tokens)  -
     "70b": ("70B", 64, 64, 256),
 }
 WEIGHT_SEED, PROMPT_SEED = 20240, 7
+TOKEN_KERNEL_TRAFFIC_RATIO = 1.038  # DRAM bytes / algorithmic bytes of the token kernel, from its ncu capture
 
 
 def measured_peaks():
@@ -129,6 +130,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-warmup", type=int, default=3, help="profiling runs may lower the warm-up floor")
+    ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model to this many layers (not a benchmark number)")
+    ap.add_argument("--flags", type=int, default=0, help="L2_FLAG_* bits for the model (8 = one launch per operator instead of one kernel per token)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -167,12 +170,15 @@ def main():
     dev = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(dev)
     cfg = l2.preset_config(size, gs)
+    if args.layers:
+        cfg.n_layers = args.layers
+        config["truncated_layers"] = args.layers
     need_payload = rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "70b"
     payload = l2.synth_fill(cfg, WEIGHT_SEED) if need_payload else None
     if payload is not None:
-        model = l2.LlamaModel.from_blob(cfg, payload, device=dev)
+        model = l2.LlamaModel.from_blob(cfg, payload, device=dev, flags=args.flags)
     else:
-        model = l2.LlamaModel.synthetic(cfg, WEIGHT_SEED, device=dev, tp=(rank, world) if tp else (0, 1))
+        model = l2.LlamaModel.synthetic(cfg, WEIGHT_SEED, device=dev, flags=args.flags, tp=(rank, world) if tp else (0, 1))
     if tp:
         ids = [l2.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
@@ -250,18 +256,31 @@ def main():
     if rank != 0:
         return
     peak, peak_kind = measured_peaks()
-    dom_bytes = int(l2.lib.l2_projection_bytes(model._h, 2))
-    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     tok_s = value / streams
+    launches_per_token = launches / max(1, n_loop * args.steps)
+    if launches_per_token < 3:
+        # One persistent kernel per token: it is the dominant (only) kernel.  Algorithmic bytes per launch
+        # = the checkpoint bytes one token reads; launch duration = the CUDA-event time per token above.
+        roofline = {"bound": "hbm", "kernel": "token_kernel (whole B=1 forward, one launch per token)",
+                    "achieved": model.decode_bytes * tok_s / 1e9, "peak": peak, "unit": "GB/s",
+                    "frac": model.decode_bytes * tok_s / 1e9 / peak, "peak_kind": peak_kind,
+                    # DRAM bytes per launch: ncu capture of the 4-layer case (profiles/token_kernel_7B_4layers.md,
+                    # dram read+write = 1.038 x its algorithmic bytes), scaled to a full launch by the bytes processed
+                    "traffic": int(TOKEN_KERNEL_TRAFFIC_RATIO * model.decode_bytes),
+                    "bytes_per_launch": int(model.decode_bytes), "us_per_launch": 1e6 / tok_s}
+    else:
+        dom_bytes = int(l2.lib.l2_projection_bytes(model._h, 2))
+        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "gemv_sk_kernel (w1/w3 + SwiGLU)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                    "bytes_per_launch": dom_bytes, "us_per_launch": dom_ms * 1e3}
     out = {
         "metric": "batch-1 decode tok/s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": max(args.min_warmup, args.warmup), "ms_per_step": (decode_ms + prefill_ms) / args.steps, "higher_is_better": True,
         "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32 activations / int4 weights", "data": "synthetic", "config": config,
         "prefill_tok_s": streams * pos0 * args.steps / max(prefill_ms, 1e-9) * 1e3,
         "decode_ms_per_token": decode_ms / (n_loop * args.steps),
-        "roofline": {"bound": "hbm", "kernel": "gemv_q4 (w1/w3 + SwiGLU)", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
-                     "bytes_per_launch": dom_bytes, "us_per_launch": dom_ms * 1e3},
+        "roofline": roofline,
         "token_roofline": {"bytes_per_token": model.decode_bytes, "achieved_gbs": model.decode_bytes * tok_s / 1e9,
                            "frac_of_8tbs": model.decode_bytes * tok_s / 8e12, "frac_of_measured": model.decode_bytes * tok_s / (peak * 1e9)},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),

@@ -112,7 +112,6 @@ void launch_embed(const EmbedParams& p, cudaStream_t st, bool pdl) {
 
 constexpr int ATT_THREADS = 128;
 constexpr int ATT_WARPS = ATT_THREADS / 32;
-constexpr int ATT_MAX_AG = 8;
 
 template <int AG>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_kernel(const __grid_constant__ AttnParams p) {

@@ -132,11 +132,58 @@ constexpr int SK_KEEP = 3;
 
 // Loads block `blk` of the segment's vector times its norm weight; with `stats` also folds the block
 // into the running max |v| and sum of x^2.
-__device__ __forceinline__ void stage_fetch(const SkSeg& sg, int blk, float4& v0, float4& v1, bool stats, float& mx, float& sq) {
+// Values that travel from CTA to CTA inside one kernel without a barrier in between are stored as
+// (value, tag) pairs, one 64-bit word each: the reader polls until the tag is the one it expects (the
+// tag names the launch and the phase that writes the value), so no fence, flag or barrier has to
+// order the two sides.  Polls are bounded: after TAG_POLL_LIMIT tries the reader gives up.
+constexpr uint32_t TAG_POLL_LIMIT = 1u << 20;
+
+__device__ __forceinline__ void store_tagged(void* base, size_t index, float v, uint32_t tag) {
+    const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(static_cast<unsigned long long*>(base) + index), "l"(w) : "memory");
+}
+// One tagged value; returns false when the poll limit is reached.
+__device__ __forceinline__ bool load_tagged(const void* base, size_t index, uint32_t tag, float& v) {
+    const unsigned long long* p = static_cast<const unsigned long long*>(base) + index;
+    for (uint32_t it = 0; it < TAG_POLL_LIMIT; it++) {
+        unsigned long long w;
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+        if ((uint32_t)(w >> 32) == tag) { v = __uint_as_float((uint32_t)w); return true; }
+    }
+    v = 0.f;
+    return false;
+}
+// Eight consecutive tagged values (64 bytes, 64-byte aligned).
+__device__ __forceinline__ bool load_tagged8(const void* base, size_t index, uint32_t tag, float4& v0, float4& v1) {
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const unsigned long long*>(base) + index);
+    for (uint32_t it = 0; it < TAG_POLL_LIMIT; it++) {
+        uint4 a, b, c, d;
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p) : "memory");
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p + 1) : "memory");
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(c.x), "=r"(c.y), "=r"(c.z), "=r"(c.w) : "l"(p + 2) : "memory");
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "l"(p + 3) : "memory");
+        if (a.y == tag && a.w == tag && b.y == tag && b.w == tag && c.y == tag && c.w == tag && d.y == tag && d.w == tag) {
+            v0 = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+            v1 = make_float4(__uint_as_float(c.x), __uint_as_float(c.z), __uint_as_float(d.x), __uint_as_float(d.z));
+            return true;
+        }
+    }
+    v0 = v1 = make_float4(0.f, 0.f, 0.f, 0.f);
+    return false;
+}
+
+// Loads block `blk` of the segment's vector times its norm weight; with `stats` also folds the block
+// into the running max |v| and sum of x^2.  tag != 0: the vector is stored as tagged pairs.
+__device__ __forceinline__ void stage_fetch(const SkSeg& sg, int blk, float4& v0, float4& v1, bool stats, float& mx, float& sq,
+                                            uint32_t tag = 0, volatile int* fail = nullptr) {
     const float4* x4 = reinterpret_cast<const float4*>(sg.x);
     const float4* n4 = reinterpret_cast<const float4*>(sg.nw);
-    v0 = __ldcg(x4 + 2 * blk);  // written by other CTAs shortly before: read at the L2, never from a stale L1 line
-    v1 = __ldcg(x4 + 2 * blk + 1);
+    if (tag) {
+        if (!load_tagged8(sg.x, (size_t)blk * 8, tag, v0, v1) && fail) *fail = 1;
+    } else {
+        v0 = __ldcg(x4 + 2 * blk);  // written by other CTAs shortly before: read at the L2, never from a stale L1 line
+        v1 = __ldcg(x4 + 2 * blk + 1);
+    }
     if (stats) sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
     if (sg.nw) {
         const float4 w0 = __ldg(n4 + 2 * blk), w1 = __ldg(n4 + 2 * blk + 1);
@@ -206,7 +253,8 @@ __device__ __forceinline__ void stage_emit(uint8_t* digits, int* ss, int stride,
 // Turns the vector of one segment into digits and per-group digit sums in shared memory.
 // Returns (in every thread) the factor the integer result has to be multiplied with.
 template <int W>
-__device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digits, int* ss, float* red, unsigned long long* dbg = nullptr) {
+__device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digits, int* ss, float* red, unsigned long long* dbg = nullptr,
+                              uint32_t tag = 0, volatile int* fail = nullptr) {
     const int nblk = in / 8;
     float mx = 0.f, sq = 0.f;
     float4 keep[SK_KEEP][2];
@@ -215,11 +263,11 @@ __device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digit
 #pragma unroll
     for (int k = 0; k < SK_KEEP; k++) {
         const int blk = threadIdx.x + k * SK_THREADS;
-        if (blk < nblk) stage_fetch(sg, blk, keep[k][0], keep[k][1], true, mx, sq);
+        if (blk < nblk) stage_fetch(sg, blk, keep[k][0], keep[k][1], true, mx, sq, tag, fail);
     }
     for (int blk = threadIdx.x + SK_KEEP * SK_THREADS; blk < nblk; blk += SK_THREADS) {
         float4 a, b;
-        stage_fetch(sg, blk, a, b, true, mx, sq);
+        stage_fetch(sg, blk, a, b, true, mx, sq, tag, fail);
     }
     if (dbg && threadIdx.x == 0) dbg[0] = clock64() + (mx > 1e30f ? 1 : 0);
     const float total = block_reduce_2(mx, sq, red);
@@ -243,7 +291,7 @@ __device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digit
             const bool valid = blk < nblk;
             float4 a = zero4, b = zero4;
             float m2 = 0.f, s2 = 0.f;
-            if (valid) stage_fetch(sg, blk, a, b, false, m2, s2);
+            if (valid) stage_fetch(sg, blk, a, b, false, m2, s2, tag, fail);
             stage_emit<W>(digits, ss, stride, blk, a, b, valid, P);
         }
     }
@@ -256,7 +304,8 @@ __device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digit
 // taken once, from the first, and both are turned into digits with the same scale.  Needs
 // in <= 2 * 8 * SK_THREADS.  Returns the common output factor.
 template <int W>
-__device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, float eps, uint8_t* da, uint8_t* db, int* ssa, int* ssb, float* red, unsigned long long* dbg = nullptr) {
+__device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, float eps, uint8_t* da, uint8_t* db, int* ssa, int* ssb, float* red,
+                                   unsigned long long* dbg = nullptr, uint32_t tag = 0, volatile int* fail = nullptr) {
     const int nblk = in / 8;
     float mx = 0.f, sq = 0.f, m2 = 0.f, s2 = 0.f;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -266,8 +315,8 @@ __device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, flo
         ka[k][0] = ka[k][1] = kb[k][0] = kb[k][1] = zero4;
         const int blk = threadIdx.x + k * SK_THREADS;
         if (blk < nblk) {
-            stage_fetch(sa, blk, ka[k][0], ka[k][1], true, mx, sq);
-            stage_fetch(sb, blk, kb[k][0], kb[k][1], false, m2, s2);
+            stage_fetch(sa, blk, ka[k][0], ka[k][1], true, mx, sq, tag, fail);
+            stage_fetch(sb, blk, kb[k][0], kb[k][1], false, m2, s2, tag, fail);
         }
     }
     if (dbg && threadIdx.x == 0) dbg[0] = clock64() + (mx > 1e30f ? 1 : 0);

@@ -46,6 +46,9 @@ struct SkJob {
     int tq, trem;          // tiles / ncta and tiles % ncta
     float rGs;             // 1 / (nseg * G)
     int epi, nscatter;
+    // token kernel only: x / out / sdst point to (value, tag) pairs; the phases (indices into the phase
+    // table) that write this job's inputs and the residual it adds to
+    int in_phase[2], resid_phase;
 };
 
 struct alignas(16) SkParams {
@@ -126,6 +129,7 @@ struct AttnParams {
     int n_kv_heads, ag, max_split, split_min;
     int pos_fixed;                                   // >= 0: use this position instead of ctl->pos
     int kvh0, n_kv_local;                            // tensor parallelism: this launch covers kv heads [kvh0, kvh0 + n_kv_local); 0 local = all
+    int in_phase;                                    // token kernel only: q/k/v/out are (value, tag) pairs, written by this phase
 };
 
 struct ClsParams {
@@ -135,6 +139,7 @@ struct ClsParams {
     float* logits;
     int rows, in;
     float eps;
+    int in_phase;         // token kernel only: x is (value, tag) pairs written by this phase
 };
 
 struct SelectParams {
@@ -152,7 +157,8 @@ enum : int { PH_EMBED = 0, PH_GEMV1, PH_GEMV2, PH_ATTN, PH_CLS, PH_SELECT, PH_AD
 
 struct alignas(16) PhaseRec {
     int type;
-    int pad[3];
+    int barrier_after;   // all CTAs meet at a grid barrier after this phase (else the next phase polls its tagged inputs)
+    int pad[2];
     union {
         SkParams sk;     // PH_GEMV1 (one matrix per job) / PH_GEMV2 (w1 with w3 + SwiGLU)
         AttnParams at;
@@ -165,7 +171,7 @@ struct alignas(16) PhaseRec {
 struct TokenParams {
     const PhaseRec* phases;     // device table
     int nphases;
-    unsigned* bar;              // arrival counter of the grid barrier, zero at launch
+    unsigned* bar;              // arrival counter of the grid barrier, zero at launch; bar[32]: launches so far (tag epoch)
     int* status;                // set non-zero when a bounded wait gives up
     const Ctl* ctl;             // loop state: the position of this token
     unsigned long long* trace;  // debug: [grid][nphases][16] stamps, or null

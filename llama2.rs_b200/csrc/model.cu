@@ -406,6 +406,16 @@ static int plan_token(l2_state* s) {
     s->tk.skip = getenv("L2_SK_SKIP") ? 1 : 0;
     s->tk_smem = fixed + (size_t)slots * sk_slot_bytes(c.group_size, su);
     if (int rc = dev_alloc(reinterpret_cast<void**>(&s->tk.bar), 256, s->allocs)) return rc;
+    L2_CUDA(cudaMemset(s->tk.bar, 0, 256));
+    {   // tagged activations, zeroed once: tag 0 is never expected
+        const size_t D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
+        struct { unsigned long long** p; size_t n; } bufs[] = {{&s->t_x, D}, {&s->t_xq, D}, {&s->t_xk, D}, {&s->t_xv, D}, {&s->t_q, D}, {&s->t_k, KV},
+                                                               {&s->t_v, KV}, {&s->t_att, D}, {&s->t_x1, D}, {&s->t_x3, D}, {&s->t_hb, H}};
+        for (auto& b : bufs) {
+            if (int rc = dev_alloc(reinterpret_cast<void**>(b.p), b.n * 8, s->allocs)) return rc;
+            L2_CUDA(cudaMemset(*b.p, 0, b.n * 8));
+        }
+    }
     return L2_OK;
 }
 
@@ -419,17 +429,69 @@ static int build_phase_table(l2_state* s, int kind) {
         t.back().type = type;
         return t.back();
     };
-    add(PH_EMBED).u.em = embed_params(s, kind);
+    // the token kernel's copies of the activation vectors: (value, tag) pairs instead of floats
+    auto tg = [&](const float* plain) -> float* {
+        const struct { const float* f; unsigned long long* t; } map[] = {{s->x, s->t_x}, {s->xq, s->t_xq}, {s->xk, s->t_xk}, {s->xv, s->t_xv},
+                                                                          {s->q, s->t_q}, {s->k, s->t_k}, {s->v, s->t_v}, {s->att, s->t_att},
+                                                                          {s->x1, s->t_x1}, {s->x3, s->t_x3}, {s->hb, s->t_hb}};
+        for (auto& e : map)
+            if (e.f == plain) return reinterpret_cast<float*>(e.t);
+        return nullptr;
+    };
+    bool bad = false;
+    auto must = [&](float* p) { if (!p) bad = true; return p; };
+    {
+        EmbedParams e = embed_params(s, kind);
+        e.x = must(tg(e.x));
+        for (int i = 0; i < e.nscatter; i++) e.sdst[i] = must(tg(e.sdst[i]));
+        add(PH_EMBED).u.em = e;
+    }
+    int x_phase = 0;  // the phase that last wrote the residual stream (and its copies for the next consumer)
     for (int l = 0; l < c.n_layers; l++) {
+        int qkv_phase = 0, attn_phase = 0, w13_phase = 0;
         for (int which = 0; which < 4; which++) {
             const SkLaunch& L = s->plans[(size_t)l * 4 + which];
+            const int me = (int)t.size();
             PhaseRec& r = add(L.nseg == 2 ? PH_GEMV2 : PH_GEMV1);
             r.u.sk = L.p;
             r.u.sk.trace = nullptr;
-            if (which == 0) add(PH_ATTN).u.at = attention_params(s, l);
+            r.u.sk.n_next = 0;
+            const int in_phase = which == 0 ? x_phase : which == 1 ? attn_phase : which == 2 ? x_phase : w13_phase;
+            for (int j = 0; j < r.u.sk.njobs; j++) {
+                SkJob& J = r.u.sk.job[j];
+                for (int sg = 0; sg < L.nseg; sg++) {
+                    J.seg[sg].x = must(tg(J.seg[sg].x));
+                    J.in_phase[sg] = in_phase;
+                }
+                J.out = must(tg(J.out));
+                for (int i = 0; i < J.nscatter; i++) J.sdst[i] = must(tg(J.sdst[i]));
+                J.resid_phase = x_phase;
+            }
+            if (which == 0) {
+                qkv_phase = me;
+                attn_phase = (int)t.size();
+                AttnParams a = attention_params(s, l);
+                a.q = must(tg(a.q)); a.k = must(tg(a.k)); a.v = must(tg(a.v));
+                a.out = must(tg(a.out));
+                a.in_phase = qkv_phase;
+                add(PH_ATTN).u.at = a;
+            } else if (which == 1) {
+                x_phase = me;  // wo wrote x (+ copies for w1/w3)
+            } else if (which == 2) {
+                w13_phase = me;
+            } else {
+                x_phase = me;  // w2 wrote x (+ copies for the next layer's q/k/v)
+            }
         }
     }
-    if (kind == G_DECODE || kind == G_FWD_CLS) add(PH_CLS).u.cl = classifier_params(s);
+    if (kind == G_DECODE || kind == G_FWD_CLS) {
+        ClsParams cp = classifier_params(s);
+        cp.x = must(tg(cp.x));
+        cp.in_phase = x_phase;
+        PhaseRec& r = add(PH_CLS);
+        r.u.cl = cp;
+        r.barrier_after = 1;  // the selection reads every logit
+    }
     if (kind == G_DECODE) {
         SelectParams sp{};
         sp.logits = s->logits; sp.ctl = s->ctl; sp.prompt = s->prompt; sp.out_tokens = s->out_tokens; sp.vocab = c.vocab_size;
@@ -437,6 +499,8 @@ static int build_phase_table(l2_state* s, int kind) {
     } else if (kind == G_FEED) {
         add(PH_ADVANCE).u.se.ctl = s->ctl;
     }
+    if (bad) return fail(L2_EINVAL, "token kernel: an activation buffer of the launch plan has no tagged counterpart");
+    if (t.size() >= 1024) return fail(L2_EINVAL, "token kernel: %zu phases do not fit the 10-bit phase field of a tag", t.size());
     if (int rc = dev_alloc(reinterpret_cast<void**>(&s->d_phases[kind]), sizeof(PhaseRec) * t.size(), s->allocs)) return rc;
     L2_CUDA(cudaMemcpy(s->d_phases[kind], t.data(), sizeof(PhaseRec) * t.size(), cudaMemcpyHostToDevice));
     s->n_phases[kind] = (int)t.size();

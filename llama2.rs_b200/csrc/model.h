@@ -104,6 +104,9 @@ struct l2_state {
     int n_phases[l2::G_COUNT] = {0, 0, 0, 0};
     l2::TokenParams tk{};                // ring geometry and barrier of the token kernel
     size_t tk_smem = 0;
+    // activations of the token kernel as (value, tag) pairs, 8 bytes per element (see token_kernel.cu)
+    unsigned long long *t_x = nullptr, *t_xq = nullptr, *t_xk = nullptr, *t_xv = nullptr, *t_q = nullptr, *t_k = nullptr, *t_v = nullptr;
+    unsigned long long *t_att = nullptr, *t_x1 = nullptr, *t_x3 = nullptr, *t_hb = nullptr;
     unsigned long long* tk_trace = nullptr;
     size_t tk_trace_count = 0;
     cudaGraphExec_t graphs[l2::G_COUNT] = {nullptr, nullptr, nullptr, nullptr};

@@ -148,9 +148,9 @@ __device__ __forceinline__ void warm_operands(const SkParams& P, int NSEG) {
 // real loads, not prefetch hints: hints were found to leave the rows in HBM, and the attention phase
 // has nothing to hide that latency behind.  The values are folded into a word that is stored only
 // if it has a value it cannot have.
-__device__ __forceinline__ void warm_attention(const AttnParams& p, int* sink) {
+__device__ __forceinline__ void warm_attention(const AttnParams& p, int pos_now, int* sink) {
     const int lane = threadIdx.x & 31;
-    const int pos = p.pos_fixed >= 0 ? p.pos_fixed : p.ctl->pos;
+    const int pos = p.pos_fixed >= 0 ? p.pos_fixed : pos_now;
     const int T = pos + 1;
     const int nkv = p.n_kv_local > 0 ? p.n_kv_local : p.n_kv_heads;
     int nsplit = (T + 255) / 256;
@@ -190,7 +190,7 @@ __device__ __forceinline__ void warm_attention(const AttnParams& p, int* sink) {
 // when a wait gave up.  `kbase` is the number of slot fills consumed before this phase.
 template <int W, int NSEG>
 __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, const Ring& R, float* red, float* oscale, uint32_t& kbase,
-                           unsigned long long* stamp) {
+                           unsigned long long* stamp, uint32_t tagbase, int phase) {
     constexpr int GS = 32 * W;
     constexpr int ROWS = 16 * NSEG;
     constexpr uint32_t UB = 256u * W + 80u;
@@ -211,12 +211,14 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     if (n > 0) {  // the first barrier inside also orders the zeroing of `partial`
         if (NSEG == 2 && J.in <= 2 * 8 * SK_THREADS) {
             // w1 and w3 read the same x, each in its own K order: one pass over the statistics
-            const float f = stage_digits_pair<W>(J.seg[0], J.seg[NSEG - 1], J.in, P.eps, digits, digits + (size_t)4 * dstride, ss, ss + G * 2, red, stamp ? stamp + 10 : nullptr);
+            const float f = stage_digits_pair<W>(J.seg[0], J.seg[NSEG - 1], J.in, P.eps, digits, digits + (size_t)4 * dstride, ss, ss + G * 2, red,
+                                                 stamp ? stamp + 10 : nullptr, tagbase | (uint32_t)J.in_phase[0], R.abort_flag);
             if (threadIdx.x == 0) oscale[0] = oscale[1] = f;
         } else {
 #pragma unroll
             for (int s = 0; s < NSEG; s++) {
-                const float f = stage_digits<W>(J.seg[s], J.in, P.eps, digits + (size_t)s * 4 * dstride, ss + s * G * 2, red, stamp ? stamp + 10 : nullptr);
+                const float f = stage_digits<W>(J.seg[s], J.in, P.eps, digits + (size_t)s * 4 * dstride, ss + s * G * 2, red,
+                                                stamp ? stamp + 10 : nullptr, tagbase | (uint32_t)J.in_phase[s], R.abort_flag);
                 if (threadIdx.x == 0) oscale[s] = f;
             }
         }
@@ -386,21 +388,22 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     }
     kbase += (uint32_t)nslots;
     flush();
-    // epilogue operands of this warp's first tile, fetched while the other warps finish
+    // scatter positions of this warp's first tile, fetched while the other warps finish
     const int e_row = (tau_first + warp) * 16 + (lane & 15);
     const bool e_pre = NSEG == 1 && warp < nt && lane < 16 && e_row < J.rows && J.epi == EPI_RESID;
     int e_idx[3] = {0, 0, 0};
-    float e_out = 0.f;
     if (e_pre) {
 #pragma unroll
         for (int s = 0; s < 3; s++)
             if (s < J.nscatter) e_idx[s] = __ldg(J.sidx[s] + e_row);
-        e_out = __ldcg(J.out + e_row);
     }
     if (stamp && threadIdx.x == 0) { stamp[2] = clock64(); stamp[9] = (unsigned long long)nslots; }
     consumer_sync();
     if (*R.abort_flag) return false;
 
+    // Results leave as (value, tag) pairs: whoever needs them polls for the tag of this phase.
+    const uint32_t out_tag = tagbase | (uint32_t)phase;
+    bool fine = true;
     for (int tl = warp; tl < nt; tl += SK_WARPS) {
         const int tau = tau_first + tl;
         float v = 0.f;
@@ -412,11 +415,11 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
             const float y3 = __shfl_down_sync(0xffffffffu, y, 16);
             if (lane < 16 && row < J.rows) {
                 const float sg = y * (1.0f / (1.0f + expf(-y)));
-                J.out[row] = sg * y3;
+                store_tagged(J.out, row, sg * y3, out_tag);
             }
         } else if (lane < 16 && row < J.rows) {
             if (J.epi == EPI_STORE) {
-                J.out[row] = y;
+                store_tagged(J.out, row, y, out_tag);
             } else {  // residual add (src/models.rs:47-51) + copies in the next consumers' K orders
                 const bool pre = e_pre && tl == warp;
                 int idx[3] = {e_idx[0], e_idx[1], e_idx[2]};
@@ -425,13 +428,19 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
                     for (int s = 0; s < 3; s++)
                         if (s < J.nscatter) idx[s] = __ldg(J.sidx[s] + row);
                 }
-                const float xv = (pre ? e_out : __ldcg(J.out + row)) + y;
-                J.out[row] = xv;
+                float res;
+                fine = load_tagged(J.out, row, tagbase | (uint32_t)J.resid_phase, res) && fine;
+                const float xv = res + y;
+                store_tagged(J.out, row, xv, out_tag);
 #pragma unroll
                 for (int s = 0; s < 3; s++)
-                    if (s < J.nscatter) J.sdst[s][idx[s]] = xv;
+                    if (s < J.nscatter) store_tagged(J.sdst[s], idx[s], xv, out_tag);
             }
         }
+    }
+    if (!fine) {
+        if (R.status) atomicExch(R.status, 1008);
+        *R.abort_flag = 1;
     }
     return true;
 }
@@ -444,15 +453,15 @@ __device__ __forceinline__ float tk_warp_sum(float v) {
     return v;
 }
 
-__device__ __forceinline__ void embed_phase(const EmbedParams& p) {
+__device__ __forceinline__ void embed_phase(const EmbedParams& p, uint32_t out_tag) {
     const int pos = p.ctl->pos;
     int token = p.ctl->token;
     if (p.feed_prompt) token = pos == 0 ? 1 : p.prompt[pos - 1];  // src/inference.rs:29-35
     if (token < 0 || token >= p.vocab) token = 0;
     for (int i = blockIdx.x * SK_THREADS + threadIdx.x; i < p.dim; i += gridDim.x * SK_THREADS) {
         const float v = __ldg(p.table + (size_t)token * p.dim + i);
-        p.x[i] = v;
-        for (int s = 0; s < p.nscatter; s++) p.sdst[s][__ldg(p.sidx[s] + i)] = v;
+        store_tagged(p.x, i, v, out_tag);
+        for (int s = 0; s < p.nscatter; s++) store_tagged(p.sdst[s], __ldg(p.sidx[s] + i), v, out_tag);
     }
 }
 
@@ -463,11 +472,11 @@ __device__ __forceinline__ void embed_phase(const EmbedParams& p) {
 constexpr int TK_ATT_WARPS = SK_WARPS;
 
 __host__ __device__ constexpr size_t tk_att_bytes(int ag) {
-    return ((size_t)ag * HS + (size_t)TK_ATT_WARPS * ag * HS + 2 * (size_t)TK_ATT_WARPS * ag + 4 + 2 * HS) * 4;
+    return ((size_t)ag * HS + (size_t)TK_ATT_WARPS * ag * HS + 2 * (size_t)TK_ATT_WARPS * ag + 4 + 2 * HS + ag) * 4;
 }
 
 template <int AG>
-__device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp) {
+__device__ __forceinline__ bool attn_phase(const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp, uint32_t in_tag, uint32_t out_tag) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* base = reinterpret_cast<float*>(scratch);
     float(*qs)[HS] = reinterpret_cast<float(*)[HS]>(base);
@@ -477,6 +486,7 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
     volatile int* sm_last = reinterpret_cast<volatile int*>(base + AG * HS + TK_ATT_WARPS * AG * HS + 2 * TK_ATT_WARPS * AG);
     float* new_k = base + AG * HS + TK_ATT_WARPS * AG * HS + 2 * TK_ATT_WARPS * AG + 4;  // the row of `pos`: k (rotated), then v
     float* new_v = new_k + HS;
+    float* sm_mx = new_v + HS;  // [AG] maximum over the warps
 
     if (p.pos_fixed >= 0) pos = p.pos_fixed;
     const int T = pos + 1;
@@ -489,6 +499,7 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
     const int nitems = nkv * nsplit;
     const int KV = p.n_kv_heads * HS;
     const float inv_div = sqrtf((float)HS);
+    bool fine = true;  // false when a poll for a tagged input gave up
     constexpr int U = AG >= 4 ? 2 : 4;
     // combine: thread (j0, i) owns element i of heads j0, j0 + 4, ...
     const int i = tid & (HS - 1), j0 = tid >> 7;
@@ -528,7 +539,9 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
             const int g = idx / (HS / 2), e = idx % (HS / 2);
             const int h = kvh * AG + g;
             const float c = __ldg(p.rope_cos + (size_t)pos * (HS / 2) + e), s = __ldg(p.rope_sin + (size_t)pos * (HS / 2) + e);
-            const float a = __ldcg(p.q + (size_t)h * HS + e), b = __ldcg(p.q + (size_t)h * HS + HS / 2 + e);
+            float a, b;
+            fine = load_tagged(p.q, (size_t)h * HS + e, in_tag, a) && fine;
+            fine = load_tagged(p.q, (size_t)h * HS + HS / 2 + e, in_tag, b) && fine;
             const float na = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
             const float nb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(na, s));
             qs[g][e] = na;
@@ -539,7 +552,9 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
             if (u < HS / 2) {
                 const int e = u;
                 const float c = __ldg(p.rope_cos + (size_t)pos * (HS / 2) + e), s = __ldg(p.rope_sin + (size_t)pos * (HS / 2) + e);
-                const float a = __ldcg(p.k + (size_t)kvh * HS + e), b = __ldcg(p.k + (size_t)kvh * HS + HS / 2 + e);
+                float a, b;
+                fine = load_tagged(p.k, (size_t)kvh * HS + e, in_tag, a) && fine;
+                fine = load_tagged(p.k, (size_t)kvh * HS + HS / 2 + e, in_tag, b) && fine;
                 const float na = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
                 const float nb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(na, s));
                 p.kc[(size_t)pos * KV + kvh * HS + e] = na;
@@ -548,7 +563,8 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
                 new_k[HS / 2 + e] = nb;
             } else {
                 const int e = u - HS / 2;  // 0..127
-                const float vv0 = __ldcg(p.v + (size_t)kvh * HS + e);
+                float vv0;
+                fine = load_tagged(p.v, (size_t)kvh * HS + e, in_tag, vv0) && fine;
                 p.vc[(size_t)pos * KV + kvh * HS + e] = vv0;
                 new_v[e] = vv0;
             }
@@ -592,24 +608,35 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
                 for (int u = 0; u < U; u++)
 #pragma unroll
                     for (int g = 0; g < AG; g++) sc[u][g] += __shfl_xor_sync(0xffffffffu, sc[u][g], o);
+            // one rescale per round: the exponentials of the round's rows are independent of one another
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                if (tb + u < t1) {
+            for (int g = 0; g < AG; g++) {
+                float mr = -INFINITY;
 #pragma unroll
-                    for (int g = 0; g < AG; g++) {
-                        const float s1 = __fdiv_rn(sc[u][g], inv_div);  // src/models.rs:158
-                        const float mn = fmaxf(m[g], s1);
-                        const float ex = expf(-fabsf(s1 - m[g]));  // the larger of the two has the factor exp(0) = 1
-                        const float corr = s1 > m[g] ? ex : 1.0f, pr = s1 > m[g] ? 1.0f : ex;
-                        l[g] = l[g] * corr + pr;
-                        acc[g].x = acc[g].x * corr + pr * vv[u].x;
-                        acc[g].y = acc[g].y * corr + pr * vv[u].y;
-                        acc[g].z = acc[g].z * corr + pr * vv[u].z;
-                        acc[g].w = acc[g].w * corr + pr * vv[u].w;
-                        m[g] = mn;
-                    }
+                for (int u = 0; u < U; u++) {
+                    sc[u][g] = __fdiv_rn(sc[u][g], inv_div);  // src/models.rs:158
+                    if (tb + u < t1) mr = fmaxf(mr, sc[u][g]);
                 }
-                if (tbn < t1) load_v(min(tbn + u, t1 - 1), vv[u]);
+                const float mn = fmaxf(m[g], mr);
+                const float corr = expf(m[g] - mn);  // exp(-inf) = 0 on the first round
+                float pr[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) pr[u] = tb + u < t1 ? expf(sc[u][g] - mn) : 0.f;
+                float ls = 0.f;
+                float4 as = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    ls += pr[u];
+                    as.x += pr[u] * vv[u].x; as.y += pr[u] * vv[u].y; as.z += pr[u] * vv[u].z; as.w += pr[u] * vv[u].w;
+                }
+                l[g] = l[g] * corr + ls;
+                acc[g].x = acc[g].x * corr + as.x; acc[g].y = acc[g].y * corr + as.y;
+                acc[g].z = acc[g].z * corr + as.z; acc[g].w = acc[g].w * corr + as.w;
+                m[g] = mn;
+            }
+            if (tbn < t1) {
+#pragma unroll
+                for (int u = 0; u < U; u++) load_v(min(tbn + u, t1 - 1), vv[u]);
             }
         }
         if (stamp && tid == 0) stamp[12] = clock64() + (acc[0].x == 1.2345f ? 1 : 0);
@@ -622,34 +649,41 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
         }
         consumer_sync();
 
-        // combine the warps that had rows, in warp order
+        // combine the warps that had rows, in warp order.  The factor exp(m_w - max) of a warp is the same
+        // for all 128 elements: thread (w, g) computes it once and leaves it where the warp's maximum was.
+        float fmax_g = -INFINITY;
+        if (tid < TK_ATT_WARPS * AG) {
+            const int g = tid % AG;
+            float mm = -INFINITY;
+            for (int w2 = 0; w2 < nwarps; w2++) mm = fmaxf(mm, sm_m[w2][g]);
+            fmax_g = mm;
+        }
+        consumer_sync();
+        if (tid < TK_ATT_WARPS * AG) {
+            const int w = tid / AG, g = tid % AG;
+            if (w < nwarps) {
+                const float mw = sm_m[w][g];
+                sm_m[w][g] = mw == -INFINITY ? 0.f : expf(mw - fmax_g);
+            }
+            if (w == 0) sm_mx[g] = fmax_g;
+        }
+        consumer_sync();
 #pragma unroll
         for (int gi = 0; gi < (AG + 3) / 4; gi++) {
             const int g = j0 + 4 * gi;
             if (g < AG) {
-                // unrolled over all warps (those without rows count as empty): the exponentials are
-                // independent and overlap, the sums are taken in warp order
-                float mw[TK_ATT_WARPS], mm = -INFINITY;
-#pragma unroll
-                for (int w = 0; w < TK_ATT_WARPS; w++) {
-                    mw[w] = w < nwarps ? sm_m[w][g] : -INFINITY;
-                    mm = fmaxf(mm, mw[w]);
-                }
                 float ll = 0.f, aa = 0.f;
-#pragma unroll
-                for (int w = 0; w < TK_ATT_WARPS; w++) {
-                    const float e = mw[w] == -INFINITY ? 0.f : expf(mw[w] - mm);
-                    if (w < nwarps) {
-                        ll += sm_l[w][g] * e;
-                        aa += sm_acc[w][g][i] * e;
-                    }
+                for (int w = 0; w < nwarps; w++) {
+                    const float e = sm_m[w][g];
+                    ll += sm_l[w][g] * e;
+                    aa += sm_acc[w][g][i] * e;
                 }
                 if (nsplit == 1) {
-                    p.out[oi[gi]] = aa / ll;
+                    store_tagged(p.out, oi[gi], aa / ll, out_tag);
                 } else {
                     float* dst = p.part + ((size_t)(kvh * AG + g) * p.max_split + split) * (HS + 2);
                     dst[i] = aa;
-                    if (i == 0) { dst[HS] = mm; dst[HS + 1] = ll; }
+                    if (i == 0) { dst[HS] = sm_mx[g]; dst[HS + 1] = ll; }
                 }
             }
         }
@@ -678,7 +712,7 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
                             ll += __ldcg(src + (size_t)s * (HS + 2) + HS + 1) * e;
                             aa += __ldcg(src + (size_t)s * (HS + 2) + i) * e;
                         }
-                        p.out[oi[gi]] = aa / ll;
+                        store_tagged(p.out, oi[gi], aa / ll, out_tag);
                     }
                 }
             }
@@ -686,20 +720,25 @@ __device__ __forceinline__ int attn_phase(const AttnParams& p, uint8_t* scratch,
         consumer_sync();  // the scratch is reused by the next item
         if (stamp && tid == 0) stamp[13] = clock64();
     }
-    return nitems;
+    return fine;
 }
 
 // final rmsnorm + dense f32 classifier (src/models.rs:288-297, src/model.rs:22-31)
-__device__ __forceinline__ void cls_phase(const ClsParams& p, float* xs, float* red) {
+__device__ __forceinline__ bool cls_phase(const ClsParams& p, float* xs, float* red, uint32_t in_tag) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r0 = (int)(((long long)blockIdx.x * p.rows) / gridDim.x);
     const int r1 = (int)(((long long)(blockIdx.x + 1) * p.rows) / gridDim.x);
     const int n4 = p.in / 4;
-    const float4* x4 = reinterpret_cast<const float4*>(p.x);
+    // the residual stream arrives as tagged pairs; the raw values are parked in xs for the second pass
+    float4* xs4 = reinterpret_cast<float4*>(xs);
+    bool fine = true;
     float s = 0.f;
-    for (int i = threadIdx.x; i < n4; i += SK_THREADS) {
-        const float4 v = __ldcg(x4 + i);
-        s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    for (int i = threadIdx.x; i < n4 / 2; i += SK_THREADS) {
+        float4 v0, v1;
+        fine = load_tagged8(p.x, (size_t)i * 8, in_tag, v0, v1) && fine;
+        s += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+        xs4[2 * i] = v0;
+        xs4[2 * i + 1] = v1;
     }
     s = tk_warp_sum(s);
     if (lane == 0) red[warp] = s;
@@ -708,12 +747,14 @@ __device__ __forceinline__ void cls_phase(const ClsParams& p, float* xs, float* 
     for (int w = 0; w < SK_WARPS; w++) sum += red[w];
     const float ss = 1.0f / sqrtf(sum / (float)p.in + p.eps);
     const float4* w4 = reinterpret_cast<const float4*>(p.nw);
-    float4* xs4 = reinterpret_cast<float4*>(xs);
-    for (int i = threadIdx.x; i < n4; i += SK_THREADS) {
-        float4 v = __ldcg(x4 + i);
-        const float4 w = __ldg(w4 + i);
-        v.x = (w.x * ss) * v.x; v.y = (w.y * ss) * v.y; v.z = (w.z * ss) * v.z; v.w = (w.w * ss) * v.w;
-        xs4[i] = v;
+    for (int i = threadIdx.x; i < n4 / 2; i += SK_THREADS) {  // the elements this thread parked above
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            float4 v = xs4[2 * i + h];
+            const float4 w = __ldg(w4 + 2 * i + h);
+            v.x = (w.x * ss) * v.x; v.y = (w.y * ss) * v.y; v.z = (w.z * ss) * v.z; v.w = (w.w * ss) * v.w;
+            xs4[2 * i + h] = v;
+        }
     }
     consumer_sync();
     for (int row = r0 + warp * 2; row < r1; row += SK_WARPS * 2) {
@@ -736,6 +777,7 @@ __device__ __forceinline__ void cls_phase(const ClsParams& p, float* xs, float* 
             if (two) p.logits[row + 1] = yb;
         }
     }
+    return fine;
 }
 
 __device__ __forceinline__ unsigned tk_random_u32(unsigned long long& s) {  // src/util.rs:71-77
@@ -881,6 +923,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
     // ================= producer warp ================================================================
     if (warp == SK_WARPS) {
         uint32_t kfill = 0;
+        const int prod_pos = tk.ctl->pos;  // read before any CTA can have advanced it
         // Phase records travel into their shared-memory buffers as bulk copies that complete on
         // rec_full[]; they are requested two phases ahead so that the switch from one phase to the
         // next costs no trip to global memory.
@@ -920,7 +963,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
                 if (p + 1 < tk.nphases) {
                     bool got1 = mbar_wait(rec_full + (p + 1) % TK_NREC, (uint32_t)((p + 1) / TK_NREC) & 1u);
                     got1 = __all_sync(0xffffffffu, got1);
-                    if (got1 && recs[(p + 1) % TK_NREC].type == PH_ATTN) warm_attention(recs[(p + 1) % TK_NREC].u.at, nullptr);
+                    if (got1 && recs[(p + 1) % TK_NREC].type == PH_ATTN) warm_attention(recs[(p + 1) % TK_NREC].u.at, prod_pos, nullptr);
                 }
                 warm_operands(rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1);
                 if (!produce_units<W>(rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1, R, kfill)) break;
@@ -931,6 +974,9 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
 
     // ================= consumer warps ===============================================================
     const int tok_pos = tk.ctl->pos;  // read once: the attention phases would pay a trip to the L2 each
+    // Tags of this launch: (launches so far + 1) in the upper bits, the writing phase in the lower ten.
+    const uint32_t epoch = tk.bar[32];
+    const uint32_t tagbase = (epoch + 1u) << 10;
     uint32_t kbase = 0;
     unsigned bar_target = 0;
     bool ok = true;
@@ -945,22 +991,29 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
         unsigned long long* stamp = tk.trace ? tk.trace + ((size_t)blockIdx.x * tk.nphases + p) * 16 : nullptr;
         TK_STAMP(p, 0);
         TK_STAMP_NS(p, 4);
+        const uint32_t out_tag = tagbase | (uint32_t)p;
+        bool fine = true;
         switch (rec.type) {
-            case PH_EMBED: embed_phase(rec.u.em); break;
-            case PH_GEMV1: ok = gemv_phase<W, 1>(rec.u.sk, smem, R, red, oscale, kbase, stamp); break;
-            case PH_GEMV2: ok = gemv_phase<W, 2>(rec.u.sk, smem, R, red, oscale, kbase, stamp); break;
-            case PH_ATTN: attn_phase<AG>(rec.u.at, smem, tok_pos, stamp); break;
-            case PH_CLS: cls_phase(rec.u.cl, reinterpret_cast<float*>(smem), red); break;
+            case PH_EMBED: embed_phase(rec.u.em, out_tag); break;
+            case PH_GEMV1: ok = gemv_phase<W, 1>(rec.u.sk, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
+            case PH_GEMV2: ok = gemv_phase<W, 2>(rec.u.sk, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
+            case PH_ATTN: fine = attn_phase<AG>(rec.u.at, smem, tok_pos, stamp, tagbase | (uint32_t)rec.u.at.in_phase, out_tag); break;
+            case PH_CLS: fine = cls_phase(rec.u.cl, reinterpret_cast<float*>(smem), red, tagbase | (uint32_t)rec.u.cl.in_phase); break;
             case PH_SELECT: if (blockIdx.x == 0) select_phase(rec.u.se, red); break;
             case PH_ADVANCE: if (blockIdx.x == 0 && threadIdx.x == 0) rec.u.se.ctl->pos = rec.u.se.ctl->pos + 1; break;
             default: break;
         }
+        if (!fine) {  // a poll for a tagged input gave up
+            if (tk.status) atomicCAS(tk.status, 0, 1009);
+            abort_flag = 1;
+        }
         if (!ok) break;
-        if (p + 1 < tk.nphases) {
-            // grid barrier: this CTA's writes are published by thread 0's fence after the CTA barrier
+        TK_STAMP(p, 7);
+        TK_STAMP_NS(p, 5);
+        if (rec.barrier_after && p + 1 < tk.nphases) {
+            // Grid barrier (only where the next phase cannot poll its inputs: the selection reads every
+            // logit).  This CTA's writes are published by thread 0's fence after the CTA barrier.
             consumer_sync();
-            TK_STAMP(p, 7);
-            TK_STAMP_NS(p, 5);
             if (threadIdx.x == 0) {
                 bar_target += gridDim.x;
                 __threadfence();
@@ -975,13 +1028,15 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
                 }
                 __threadfence();
             }
-            consumer_sync();
-            if (abort_flag) { ok = false; break; }
         }
+        consumer_sync();  // the next phase reuses this phase's shared memory
+        if (abort_flag) { ok = false; break; }
         TK_STAMP(p, 3);
         TK_STAMP_NS(p, 6);
         if (threadIdx.x == 0) consumer_phase = p + 1;
     }
+    // the next launch uses new tags; every CTA has read the count long before CTA 0 gets here
+    if (ok && blockIdx.x == 0 && threadIdx.x == 0) tk.bar[32] = epoch + 1u;
     if (!ok) {
         // copies may still be in flight into this CTA's shared memory: give them a bounded time to land
         for (int i = 0; i < tk.slots; i++) { mbar_wait(full + i, 0, 1u << 8); mbar_wait(full + i, 1, 1u << 8); }
