@@ -171,7 +171,7 @@ struct alignas(16) PhaseRec {
 struct TokenParams {
     const PhaseRec* phases;     // device table
     int nphases;
-    unsigned* bar;              // arrival counter of the grid barrier, zero at launch; bar[32]: launches so far (tag epoch)
+    unsigned* bar;              // bar[0]: arrivals at grid barriers (never reset), bar[32]: launches so far (tag epoch), bar[33]: barriers so far
     int* status;                // set non-zero when a bounded wait gives up
     const Ctl* ctl;             // loop state: the position of this token
     unsigned long long* trace;  // debug: [grid][nphases][16] stamps, or null

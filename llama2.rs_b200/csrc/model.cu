@@ -513,7 +513,6 @@ static int enqueue_token(l2_state* s, int kind, cudaStream_t st) {
     tk.phases = s->d_phases[kind];
     tk.nphases = s->n_phases[kind];
     tk.trace = s->tk_trace && (size_t)m->sms * tk.nphases * 16 <= s->tk_trace_count ? s->tk_trace : nullptr;
-    L2_CUDA(cudaMemsetAsync(tk.bar, 0, sizeof(unsigned), st));
     L2_CUDA(launch_token(tk, m->shape.c.group_size, m->shape.attn_groups(), m->sms, s->tk_smem, st));
     return L2_OK;
 }
@@ -804,6 +803,12 @@ extern "C" int l2_state_reset(l2_state* s) {
     L2_CUDA(cudaMemsetAsync(s->ctl, 0, sizeof(Ctl), m->stream));
     L2_CUDA(cudaMemsetAsync(s->prompt, 0, sizeof(int) * c.seq_len, m->stream));
     L2_CUDA(cudaMemsetAsync(s->out_tokens, 0, sizeof(int) * c.seq_len, m->stream));
+    if (s->tk.bar) {
+        // grid-barrier bookkeeping of the token kernel (a launch that gave up may have left it uneven);
+        // the launch count behind the tags keeps running, so stale activations can never match
+        L2_CUDA(cudaMemsetAsync(s->tk.bar, 0, sizeof(unsigned), m->stream));
+        L2_CUDA(cudaMemsetAsync(s->tk.bar + 33, 0, sizeof(unsigned), m->stream));
+    }
     L2_CUDA(cudaStreamSynchronize(m->stream));
     return L2_OK;
 }

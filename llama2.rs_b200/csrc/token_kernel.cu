@@ -226,6 +226,20 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     consumer_sync();
     if (stamp && threadIdx.x == 0) stamp[1] = clock64();
 
+    // Epilogue operands of this warp's first tile that are known long before the epilogue (the scatter
+    // positions, and the residual value, written phases ago): requested now, so that their trip to the
+    // L2 overlaps the main loop.
+    const int e_row = (tau_first + warp) * 16 + (lane & 15);
+    const bool e_pre = NSEG == 1 && warp < nt && lane < 16 && e_row < J.rows && J.epi == EPI_RESID;
+    int e_idx[3] = {0, 0, 0};
+    unsigned long long e_res = 0;
+    if (e_pre) {
+#pragma unroll
+        for (int s = 0; s < 3; s++)
+            if (s < J.nscatter) e_idx[s] = __ldg(J.sidx[s] + e_row);
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(e_res) : "l"(reinterpret_cast<const unsigned long long*>(J.out) + e_row) : "memory");
+    }
+
     // ---- main loop.  In every slot fill this warp owns units 2*warp and 2*warp + 1.  With four warps
     // per scheduler the loop lives on instruction count and on the length of its dependent chain, so
     //  * the common case (a full slot: every warp has its pair) is straight-line code without
@@ -388,15 +402,6 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     }
     kbase += (uint32_t)nslots;
     flush();
-    // scatter positions of this warp's first tile, fetched while the other warps finish
-    const int e_row = (tau_first + warp) * 16 + (lane & 15);
-    const bool e_pre = NSEG == 1 && warp < nt && lane < 16 && e_row < J.rows && J.epi == EPI_RESID;
-    int e_idx[3] = {0, 0, 0};
-    if (e_pre) {
-#pragma unroll
-        for (int s = 0; s < 3; s++)
-            if (s < J.nscatter) e_idx[s] = __ldg(J.sidx[s] + e_row);
-    }
     if (stamp && threadIdx.x == 0) { stamp[2] = clock64(); stamp[9] = (unsigned long long)nslots; }
     consumer_sync();
     if (*R.abort_flag) return false;
@@ -428,8 +433,9 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
                     for (int s = 0; s < 3; s++)
                         if (s < J.nscatter) idx[s] = __ldg(J.sidx[s] + row);
                 }
-                float res;
-                fine = load_tagged(J.out, row, tagbase | (uint32_t)J.resid_phase, res) && fine;
+                float res = __uint_as_float((uint32_t)e_res);
+                if (!pre || (uint32_t)(e_res >> 32) != (tagbase | (uint32_t)J.resid_phase))  // not the early copy: poll
+                    fine = load_tagged(J.out, row, tagbase | (uint32_t)J.resid_phase, res) && fine;
                 const float xv = res + y;
                 store_tagged(J.out, row, xv, out_tag);
 #pragma unroll
@@ -978,7 +984,8 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
     const uint32_t epoch = tk.bar[32];
     const uint32_t tagbase = (epoch + 1u) << 10;
     uint32_t kbase = 0;
-    unsigned bar_target = 0;
+    unsigned bar_target = tk.bar[33] * gridDim.x;  // arrivals of the grid barriers of earlier launches (the counter is never reset)
+    unsigned bars_done = 0;
     bool ok = true;
     for (int p = 0; p < tk.nphases && ok; p++) {
         if (!mbar_wait(rec_full + p % TK_NREC, (uint32_t)(p / TK_NREC) & 1u)) {
@@ -1014,12 +1021,13 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
             // Grid barrier (only where the next phase cannot poll its inputs: the selection reads every
             // logit).  This CTA's writes are published by thread 0's fence after the CTA barrier.
             consumer_sync();
+            bars_done++;
             if (threadIdx.x == 0) {
                 bar_target += gridDim.x;
                 __threadfence();
                 atomicAdd(tk.bar, 1u);
                 uint32_t it = 0;
-                while (ld_acquire_u32(tk.bar) < bar_target) {
+                while ((int)(ld_acquire_u32(tk.bar) - bar_target) < 0) {
                     if (++it > TK_BAR_LIMIT || ((it & 255u) == 0 && tk.status && *reinterpret_cast<volatile int*>(tk.status) != 0)) {
                         if (tk.status) atomicCAS(tk.status, 0, 1004);
                         abort_flag = 1;
@@ -1036,7 +1044,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
         if (threadIdx.x == 0) consumer_phase = p + 1;
     }
     // the next launch uses new tags; every CTA has read the count long before CTA 0 gets here
-    if (ok && blockIdx.x == 0 && threadIdx.x == 0) tk.bar[32] = epoch + 1u;
+    if (ok && blockIdx.x == 0 && threadIdx.x == 0) { tk.bar[32] = epoch + 1u; tk.bar[33] += bars_done; }
     if (!ok) {
         // copies may still be in flight into this CTA's shared memory: give them a bounded time to land
         for (int i = 0; i < tk.slots; i++) { mbar_wait(full + i, 0, 1u << 8); mbar_wait(full + i, 1, 1u << 8); }
