@@ -206,11 +206,12 @@ uint64_t l2_projection_bytes(const l2_model* m, int which);
  * launches planned afterwards, host_out (may be NULL) receives the stamps of the last launch. */
 int l2_debug_trace(int enable, unsigned long long* host_out, int n_ctas);
 
-/* Debug: clock stamps of the one-kernel-per-token path.  enable = 1 arms recording into a device
- * buffer of `count` stamps (needs SMs x phases x 16); enable = 0 copies the first `count` stamps
- * to host_out, laid out [CTA][phase][16]: SM clock at phase start, digits staged, main loop done,
- * barrier passed; global nanosecond timer at phase start, barrier arrival, barrier passed; SM
- * clock at barrier arrival; cycles warp 0 waited for weights; slot fills; rest unused.
+/* Debug: clock stamps of the one-kernel-per-token path; they are written only by a library built
+ * with -DL2_TK_TRACE (L2_TK_TRACE=1 for build.py), a default build leaves the buffer zero.
+ * enable = 1 arms recording into a device buffer of `count` stamps (needs SMs x phases x 16);
+ * enable = 0 copies the first `count` stamps to host_out, laid out [CTA][phase][16]: SM clock at
+ * phase start, inputs staged, main loop done, phase left; global nanosecond timer at phase start,
+ * phase end, phase left; SM clock at phase end; the rest are per-phase details.
  * No counterpart in the reference. */
 int l2_debug_token_trace(l2_state* s, int enable, unsigned long long* host_out, size_t count);
 

@@ -38,7 +38,9 @@ def build(verbose=False, force=False):
         obj = os.path.join(HERE, "build", src + ".o")
         objs.append(obj)
         if force or _stale(obj, [path] + headers):
-            cmd = [NVCC] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
+            # L2_TK_TRACE=1: compile the clock stamps of the token kernel in (a debugging build: they cost registers)
+            trace = ["-DL2_TK_TRACE"] if os.environ.get("L2_TK_TRACE") else []
+            cmd = [NVCC] + NVCC_FLAGS + trace + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
             if not src.endswith(".cu"):
                 cmd = [NVCC] + NVCC_FLAGS + ["-x", "cu", "-c", path, "-o", obj]
             r = subprocess.run(cmd, capture_output=True, text=True)

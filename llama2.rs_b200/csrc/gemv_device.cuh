@@ -88,6 +88,29 @@ __device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_wait_u32(uint32_t bar, uint32_t parity, uint32_t limit = SK_WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; i++) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(20000u) : "memory");
+        if (ok) return true;
+        __nanosleep(200);
+    }
+    return false;
+}
+__device__ __forceinline__ void mbar_expect_tx_u32(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s_u32(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ int lds_volatile_i32(uint32_t a) {
+    int v;
+    asm volatile("ld.volatile.shared.s32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts_volatile_i32(uint32_t a, int v) { asm volatile("st.volatile.shared.s32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
 __device__ __forceinline__ void mbar_arrive_u32(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -175,11 +198,11 @@ __device__ __forceinline__ bool load_tagged8(const void* base, size_t index, uin
 // Loads block `blk` of the segment's vector times its norm weight; with `stats` also folds the block
 // into the running max |v| and sum of x^2.  tag != 0: the vector is stored as tagged pairs.
 __device__ __forceinline__ void stage_fetch(const SkSeg& sg, int blk, float4& v0, float4& v1, bool stats, float& mx, float& sq,
-                                            uint32_t tag = 0, volatile int* fail = nullptr) {
+                                            uint32_t tag = 0, bool* fail = nullptr) {
     const float4* x4 = reinterpret_cast<const float4*>(sg.x);
     const float4* n4 = reinterpret_cast<const float4*>(sg.nw);
     if (tag) {
-        if (!load_tagged8(sg.x, (size_t)blk * 8, tag, v0, v1) && fail) *fail = 1;
+        if (!load_tagged8(sg.x, (size_t)blk * 8, tag, v0, v1) && fail) *fail = true;
     } else {
         v0 = __ldcg(x4 + 2 * blk);  // written by other CTAs shortly before: read at the L2, never from a stale L1 line
         v1 = __ldcg(x4 + 2 * blk + 1);
@@ -254,7 +277,7 @@ __device__ __forceinline__ void stage_emit(uint8_t* digits, int* ss, int stride,
 // Returns (in every thread) the factor the integer result has to be multiplied with.
 template <int W>
 __device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digits, int* ss, float* red, unsigned long long* dbg = nullptr,
-                              uint32_t tag = 0, volatile int* fail = nullptr) {
+                              uint32_t tag = 0, bool* fail = nullptr) {
     const int nblk = in / 8;
     float mx = 0.f, sq = 0.f;
     float4 keep[SK_KEEP][2];
@@ -305,7 +328,7 @@ __device__ float stage_digits(const SkSeg& sg, int in, float eps, uint8_t* digit
 // in <= 2 * 8 * SK_THREADS.  Returns the common output factor.
 template <int W>
 __device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, float eps, uint8_t* da, uint8_t* db, int* ssa, int* ssb, float* red,
-                                   unsigned long long* dbg = nullptr, uint32_t tag = 0, volatile int* fail = nullptr) {
+                                   unsigned long long* dbg = nullptr, uint32_t tag = 0, bool* fail = nullptr) {
     const int nblk = in / 8;
     float mx = 0.f, sq = 0.f, m2 = 0.f, s2 = 0.f;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);

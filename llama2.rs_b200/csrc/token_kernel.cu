@@ -29,8 +29,13 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+#ifdef L2_TK_TRACE
 #define TK_STAMP_NS(p, i) do { if (tk.trace && threadIdx.x == 0) tk.trace[((size_t)blockIdx.x * tk.nphases + (p)) * 16 + (i)] = global_ns(); } while (0)
 #define TK_STAMP(p, i) do { if (tk.trace && threadIdx.x == 0) tk.trace[((size_t)blockIdx.x * tk.nphases + (p)) * 16 + (i)] = clock64(); } while (0)
+#else
+#define TK_STAMP_NS(p, i) do { } while (0)
+#define TK_STAMP(p, i) do { } while (0)
+#endif
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     unsigned v;
@@ -55,16 +60,21 @@ __device__ __forceinline__ CtaRange sk_cta_range(const SkParams& P) {
     return c;
 }
 
+// Everything about the weight ring that the phases need, as 32-bit shared-space addresses: the record
+// is alive across the whole phase loop, and generic pointers would cost two registers each.
 struct Ring {
-    uint8_t* base;
-    uint64_t *full, *empty;
+    uint32_t base, full, empty, zeros;  // slot 0; full[] / empty[] barriers; 32 bytes of zeros
+    uint32_t abort_flag;                // int: raised when a bounded wait gave up
     uint32_t slot_bytes;
     int SU, NS;
-    volatile int* abort_flag;
     int* status;
-    const uint8_t* zeros;  // 32 bytes of zeros in shared memory
-    int skip;              // debug: consume the slot fills without doing the arithmetic
+    int skip;  // debug: consume the slot fills without doing the arithmetic
 };
+__device__ __forceinline__ bool ring_aborted(const Ring& R) { return lds_volatile_i32(R.abort_flag) != 0; }
+__device__ __forceinline__ void ring_abort(const Ring& R, int code) {
+    if (R.status) atomicCAS(R.status, 0, code);
+    sts_volatile_i32(R.abort_flag, 1);
+}
 
 __device__ __forceinline__ void prefetch_line_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
@@ -101,20 +111,19 @@ __device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const
         const int slot = (int)(f % (uint32_t)R.NS);
         int good = 1;
         if (lane == 0) {
-            if (f >= (uint32_t)R.NS && !mbar_wait(R.empty + slot, (f / (uint32_t)R.NS - 1u) & 1u)) {
-                if (R.status) atomicExch(R.status, 1002);
-                *R.abort_flag = 1;
+            if (f >= (uint32_t)R.NS && !mbar_wait_u32(R.empty + 8u * slot, (f / (uint32_t)R.NS - 1u) & 1u)) {
+                ring_abort(R, 1002);
                 good = 0;
             }
-            if (*R.abort_flag) good = 0;
+            if (ring_aborted(R)) good = 0;
         }
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) return false;
         const int left = min(R.SU, n - k * R.SU);
-        if (lane == 0) mbar_expect_tx(R.full + slot, (uint32_t)left * UB);
-        uint8_t* dst = R.base + (size_t)slot * R.slot_bytes;
+        if (lane == 0) mbar_expect_tx_u32(R.full + 8u * slot, (uint32_t)left * UB);
+        uint32_t dst = R.base + (uint32_t)slot * R.slot_bytes;
         walk(cf, left, [&](const uint32_t* src, uint32_t bytes) {
-            if (lane == 0) bulk_g2s(dst, src, bytes, R.full + slot);
+            if (lane == 0) bulk_g2s_u32(dst, src, bytes, R.full + 8u * slot);
             dst += bytes;
         });
     }
@@ -208,21 +217,23 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     float* partial = reinterpret_cast<float*>(ss + NSEG * G * 2);         // [nt][SK_WARPS][ROWS]
 
     for (int i = threadIdx.x; i < nt * SK_WARPS * ROWS; i += SK_THREADS) partial[i] = 0.f;
+    bool stage_failed = false;  // a poll for a tagged input gave up
     if (n > 0) {  // the first barrier inside also orders the zeroing of `partial`
         if (NSEG == 2 && J.in <= 2 * 8 * SK_THREADS) {
             // w1 and w3 read the same x, each in its own K order: one pass over the statistics
             const float f = stage_digits_pair<W>(J.seg[0], J.seg[NSEG - 1], J.in, P.eps, digits, digits + (size_t)4 * dstride, ss, ss + G * 2, red,
-                                                 stamp ? stamp + 10 : nullptr, tagbase | (uint32_t)J.in_phase[0], R.abort_flag);
+                                                 stamp ? stamp + 10 : nullptr, tagbase | (uint32_t)J.in_phase[0], &stage_failed);
             if (threadIdx.x == 0) oscale[0] = oscale[1] = f;
         } else {
 #pragma unroll
             for (int s = 0; s < NSEG; s++) {
                 const float f = stage_digits<W>(J.seg[s], J.in, P.eps, digits + (size_t)s * 4 * dstride, ss + s * G * 2, red,
-                                                stamp ? stamp + 10 : nullptr, tagbase | (uint32_t)J.in_phase[s], R.abort_flag);
+                                                stamp ? stamp + 10 : nullptr, tagbase | (uint32_t)J.in_phase[s], &stage_failed);
                 if (threadIdx.x == 0) oscale[s] = f;
             }
         }
     }
+    if (stage_failed) ring_abort(R, 1010);
     consumer_sync();
     if (stamp && threadIdx.x == 0) stamp[1] = clock64();
 
@@ -270,11 +281,11 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     };
     const int zshift = 4 * r;
     // 32-bit shared-space addresses of everything the loop touches
-    const uint32_t ring_a = smem_u32(R.base) + (uint32_t)(2 * warp) * UB;   // this warp's pair inside slot 0
-    const uint32_t full_a = smem_u32(R.full), empty_a = smem_u32(R.empty);
+    const uint32_t ring_a = R.base + (uint32_t)(2 * warp) * UB;   // this warp's pair inside slot 0
+    const uint32_t full_a = R.full, empty_a = R.empty;
     const uint32_t ss_a = smem_u32(ss) + 4u * (uint32_t)(t & 1);
     // this lane's digits of the group at position gg; lanes r >= 4 (MMA columns 4..7) read zeros
-    const uint32_t dg_a = r < 4 ? smem_u32(digits) + (uint32_t)(r * dstride + t * (8 * W)) : smem_u32(R.zeros);
+    const uint32_t dg_a = r < 4 ? smem_u32(digits) + (uint32_t)(r * dstride + t * (8 * W)) : R.zeros;
     const uint32_t dmul = r < 4 ? 1u : 0u;
     constexpr uint32_t META = 256u * W;  // scales, then the two zero-point words
     auto digits_of = [&](int gg) {
@@ -337,9 +348,9 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
         const int m = min(SU, n - k * SU);
         bool got = mbar_try_wait_u32(full_a + 8u * slot, fpar);
         if (!__all_sync(0xffffffffu, got)) {  // not there yet: the bounded wait
-            got = !*R.abort_flag && mbar_wait(R.full + slot, fpar);
+            got = !ring_aborted(R) && mbar_wait_u32(full_a + 8u * slot, fpar);
             if (!__all_sync(0xffffffffu, got)) {
-                if (!*R.abort_flag) { if (R.status) atomicExch(R.status, 1001); *R.abort_flag = 1; }
+                if (!ring_aborted(R)) ring_abort(R, 1001);
                 ok = false;
                 break;
             }
@@ -404,7 +415,7 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     flush();
     if (stamp && threadIdx.x == 0) { stamp[2] = clock64(); stamp[9] = (unsigned long long)nslots; }
     consumer_sync();
-    if (*R.abort_flag) return false;
+    if (ring_aborted(R)) return false;
 
     // Results leave as (value, tag) pairs: whoever needs them polls for the tag of this phase.
     const uint32_t out_tag = tagbase | (uint32_t)phase;
@@ -444,10 +455,7 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
             }
         }
     }
-    if (!fine) {
-        if (R.status) atomicExch(R.status, 1008);
-        *R.abort_flag = 1;
-    }
+    if (!fine) ring_abort(R, 1008);
     return true;
 }
 
@@ -917,13 +925,13 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
     __syncthreads();
 
     Ring R;
-    R.base = smem + tk.fixed_bytes;
-    R.full = full; R.empty = empty;
+    R.base = smem_u32(smem) + tk.fixed_bytes;
+    R.full = smem_u32(full); R.empty = smem_u32(empty);
     R.SU = tk.chunk; R.NS = tk.slots;
     R.slot_bytes = (uint32_t)tk.chunk * (256u * W + 80u);
-    R.abort_flag = &abort_flag;
+    R.abort_flag = smem_u32(const_cast<int*>(&abort_flag));
     R.status = tk.status;
-    R.zeros = reinterpret_cast<const uint8_t*>(zeros);
+    R.zeros = smem_u32(zeros);
     R.skip = tk.skip;
 
     // ================= producer warp ================================================================
@@ -995,7 +1003,11 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
         consumer_sync();
         if (abort_flag) { ok = false; break; }
         const PhaseRec& rec = recs[p % TK_NREC];
+#ifdef L2_TK_TRACE
         unsigned long long* stamp = tk.trace ? tk.trace + ((size_t)blockIdx.x * tk.nphases + p) * 16 : nullptr;
+#else
+        unsigned long long* const stamp = nullptr;  // clock stamps are compiled in with -DL2_TK_TRACE only: they cost registers
+#endif
         TK_STAMP(p, 0);
         TK_STAMP_NS(p, 4);
         const uint32_t out_tag = tagbase | (uint32_t)p;
