@@ -183,6 +183,8 @@ def main():
         ids = [l2.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         model.tp_connect(ids[0])
+    # one persistent kernel per token on a single GPU; one launch per operator under tensor parallelism or on request
+    token_kernel = not tp and not (args.flags & 8) and not os.environ.get("L2_NO_TOKEN_KERNEL")
     stream = torch.cuda.Stream(device=dev)
     model.set_stream(stream.cuda_stream)
     state = l2.RunState(model)
@@ -217,16 +219,18 @@ def main():
             prefill_ms += pf
             decode_ms += dc
             assert np.array_equal(toks, toks_ref), "decode is not reproducible from step to step"
-        # the dominant kernel alone: w1/w3 + SwiGLU GEMV, cycling through the layers (each launch reads other weights)
-        n_dom = 4 * cfg.n_layers
-        l2.check(l2.lib.l2_bench_projection(model._h, state._h, 2, 0, cfg.n_layers))
-        torch.cuda.synchronize()
-        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        d0.record(stream)
-        l2.check(l2.lib.l2_bench_projection(model._h, state._h, 2, 0, n_dom))
-        d1.record(stream)
-        torch.cuda.synchronize()
-        dom_ms = d0.elapsed_time(d1) / n_dom
+        dom_ms = None
+        if not token_kernel:
+            # the dominant kernel alone: w1/w3 + SwiGLU GEMV, cycling through the layers (each launch reads other weights)
+            n_dom = 4 * cfg.n_layers
+            l2.check(l2.lib.l2_bench_projection(model._h, state._h, 2, 0, cfg.n_layers))
+            torch.cuda.synchronize()
+            d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            d0.record(stream)
+            l2.check(l2.lib.l2_bench_projection(model._h, state._h, 2, 0, n_dom))
+            d1.record(stream)
+            torch.cuda.synchronize()
+            dom_ms = d0.elapsed_time(d1) / n_dom
     barrier()
     launches = l2.lib.l2_launch_count() - launches0
     n_loop = total - pos0           # positions run by the B=1 loop per step (a few teacher-forced ones first)
@@ -257,8 +261,7 @@ def main():
         return
     peak, peak_kind = measured_peaks()
     tok_s = value / streams
-    launches_per_token = launches / max(1, n_loop * args.steps)
-    if launches_per_token < 3:
+    if token_kernel:
         # One persistent kernel per token: it is the dominant (only) kernel.  Algorithmic bytes per launch
         # = the checkpoint bytes one token reads; launch duration = the CUDA-event time per token above.
         roofline = {"bound": "hbm", "kernel": "token_kernel (whole B=1 forward, one launch per token)",
