@@ -3,6 +3,10 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 7b|13b|70b] [--impl ours|reference]
 
+With N > 1 (launched by torch.distributed.run, one rank per GPU) the default workload stays the 7B one: every rank
+decodes its own token stream (batch-1 decode has nothing to exchange; `scaling` is "weak", `value` the sum over the
+ranks).  `--workload 70b` on N > 1 GPUs shards the 70B model over the ranks (tensor parallel, NCCL all-gathers).
+
 A step is one pass of the workload: a seeded random prompt through prefill, then the decode
 loop (BASELINE config 0 for 7B: 32 prompt tokens, 256 greedy tokens).  `value` is decode tok/s with
 weights, KV cache and the loop state resident in HBM (CUDA events on the launching stream);
@@ -126,7 +130,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(WORKLOADS),
-                    help="auto: 7b on one GPU, 70b tensor-parallel over all ranks on several")
+                    help="auto: 7b (N > 1: independent replicas, weak scaling); 70b on N > 1 GPUs is tensor-parallel over all ranks")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-warmup", type=int, default=3, help="profiling runs may lower the warm-up floor")
@@ -136,8 +140,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.workload == "auto":
-        args.workload = "7b" if world == 1 else "70b"
-    tp = world > 1 and args.workload == "70b"  # 70B is sharded over the ranks; smaller models run as replicas
+        args.workload = "7b"  # the configuration the metric is quoted on, at every N (N > 1: one token stream per GPU)
+    tp = world > 1 and args.workload == "70b"  # 70B is sharded over the ranks (tensor parallel); smaller models run as replicas
     size, gs, n_prompt, n_decode = WORKLOADS[args.workload]
     config = {"workload": "Llama2-%s GPTQ 4-bit g%d act-order, %d-token random prompt, %d greedy decode tokens, batch 1"
                           % (size, gs, n_prompt, n_decode),
