@@ -338,10 +338,6 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
     };
     // position of this warp's first unit of the current fill; advanced by SU units per fill
     int tl0 = (2 * warp) / Gs, gg0 = (2 * warp) % Gs;
-    // the pair of the previous fill, finished one iteration later
-    int pc0[4] = {0, 0, 0, 0}, pc1[4] = {0, 0, 0, 0};
-    uint32_t p_rec = 0, p_slot = 0;
-    int p_gg0 = 0, p_gg1 = 0, p_key0 = 0, p_key1 = 0, p_n = -1;
     uint32_t fslot = kbase % (uint32_t)NS, fpar = (kbase / (uint32_t)NS) & 1u;  // slot and parity of the next fill
     for (int k = 0; k < nslots; k++) {
         const uint32_t slot = fslot;
@@ -355,61 +351,44 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
                 break;
             }
         }
-        if (R.skip) {
-            release(slot);
-            if (++fslot == (uint32_t)NS) { fslot = 0; fpar ^= 1u; }
-            continue;
-        }
-        const uint32_t rec0 = ring_a + slot * R.slot_bytes;
-        int tl1 = tl0, gg1 = gg0 + 1;
-        if (gg1 == Gs) { gg1 = 0; tl1++; }
-        int c0[4], c1[4];
-        if (m == 2 * SK_WARPS) {  // a full slot: straight-line
-            Unit u0, u1;
-            unit_load(rec0, digits_of(gg0), u0);
-            unit_load(rec0 + UB, digits_of(gg1), u1);
-            if (k > 0) {  // the previous fill was a full one as well; its last step runs while the MMAs are in flight
+        if (!R.skip) {
+            const uint32_t rec0 = ring_a + slot * R.slot_bytes;
+            int tl1 = tl0, gg1 = gg0 + 1;
+            if (gg1 == Gs) { gg1 = 0; tl1++; }
+            int c0[4], c1[4];
+            if (m == 2 * SK_WARPS) {  // a full slot: straight-line, all loads first
+                Unit u0, u1;
                 Meta m0, m1;
-                meta_load(p_rec, p_gg0, m0);
-                meta_load(p_rec + UB, p_gg1, m1);
+                unit_load(rec0, digits_of(gg0), u0);
+                unit_load(rec0 + UB, digits_of(gg1), u1);
+                meta_load(rec0, gg0, m0);
+                meta_load(rec0 + UB, gg1, m1);
                 unit_mma(u0, c0);
                 unit_mma(u1, c1);
-                unit_finish(m0, p_key0, pc0);
-                unit_finish(m1, p_key1, pc1);
-                release(p_slot);
-            } else {
-                unit_mma(u0, c0);
-                unit_mma(u1, c1);
+                unit_finish(m0, key_of(tl0, gg0), c0);
+                unit_finish(m1, key_of(tl1, gg1), c1);
+            } else {  // the last, partial fill
+                const int j = 2 * warp;
+                if (j < m) {
+                    Unit u; Meta mt;
+                    unit_load(rec0, digits_of(gg0), u);
+                    meta_load(rec0, gg0, mt);
+                    unit_mma(u, c0);
+                    unit_finish(mt, key_of(tl0, gg0), c0);
+                }
+                if (j + 1 < m) {
+                    Unit u; Meta mt;
+                    unit_load(rec0 + UB, digits_of(gg1), u);
+                    meta_load(rec0 + UB, gg1, mt);
+                    unit_mma(u, c1);
+                    unit_finish(mt, key_of(tl1, gg1), c1);
+                }
             }
-            p_n = 2;
-        } else {  // the last, partial fill
-            const int j = 2 * warp;
-            const int nu = j + 1 < m ? 2 : (j < m ? 1 : 0);
-            c0[0] = c0[1] = c0[2] = c0[3] = c1[0] = c1[1] = c1[2] = c1[3] = 0;
-            if (nu > 0) { Unit u; unit_load(rec0, digits_of(gg0), u); unit_mma(u, c0); }
-            if (nu > 1) { Unit u; unit_load(rec0 + UB, digits_of(gg1), u); unit_mma(u, c1); }
-            if (k > 0) {
-                Meta m0, m1;
-                meta_load(p_rec, p_gg0, m0);
-                meta_load(p_rec + UB, p_gg1, m1);
-                unit_finish(m0, p_key0, pc0);
-                unit_finish(m1, p_key1, pc1);
-                release(p_slot);
-            }
-            p_n = nu;
         }
-        p_rec = rec0; p_slot = slot;
-        p_gg0 = gg0; p_gg1 = gg1; p_key0 = key_of(tl0, gg0); p_key1 = key_of(tl1, gg1);
-#pragma unroll
-        for (int i = 0; i < 4; i++) { pc0[i] = c0[i]; pc1[i] = c1[i]; }
+        release(slot);
         gg0 += SU;
         while (gg0 >= Gs) { gg0 -= Gs; tl0++; }
         if (++fslot == (uint32_t)NS) { fslot = 0; fpar ^= 1u; }
-    }
-    if (ok && p_n >= 0) {
-        if (p_n > 0) { Meta m0; meta_load(p_rec, p_gg0, m0); unit_finish(m0, p_key0, pc0); }
-        if (p_n > 1) { Meta m1; meta_load(p_rec + UB, p_gg1, m1); unit_finish(m1, p_key1, pc1); }
-        release(p_slot);
     }
     kbase += (uint32_t)nslots;
     flush();
@@ -490,7 +469,7 @@ __host__ __device__ constexpr size_t tk_att_bytes(int ag) {
 }
 
 template <int AG>
-__device__ __forceinline__ bool attn_phase(const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp, uint32_t in_tag, uint32_t out_tag) {
+__device__ __noinline__ bool attn_phase(const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp, uint32_t in_tag, uint32_t out_tag) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* base = reinterpret_cast<float*>(scratch);
     float(*qs)[HS] = reinterpret_cast<float(*)[HS]>(base);
