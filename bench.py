@@ -170,6 +170,8 @@ def main():
     import llama2_rs as l2
 
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # the version banner goes to stdout, which carries the one JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
     dev = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(dev)
@@ -292,7 +294,7 @@ def main():
                            "frac_of_8tbs": model.decode_bytes * tok_s / 8e12, "frac_of_measured": model.decode_bytes * tok_s / (peak * 1e9)},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
     }
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:  # the CPU leg belongs to the single-GPU line
         try:
             out["cpu_baseline"] = CpuArm(args.workload, payload=payload, cfg=cfg).run()
         except Exception as e:  # the GPU numbers stand even if the CPU leg cannot run
