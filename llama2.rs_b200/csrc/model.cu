@@ -819,7 +819,15 @@ extern "C" void l2_state_free(l2_state* s) {
     for (auto& g : s->graphs) if (g) cudaGraphExecDestroy(g);
     free_allocs(s->allocs);
     if (s->h_ctl) cudaFreeHost(s->h_ctl);
-    if (s->batch) { if (s->batch->h_stage) cudaFreeHost(s->batch->h_stage); delete s->batch; }
+    if (s->batch) {
+        if (s->batch->h_stage) cudaFreeHost(s->batch->h_stage);
+        for (int i = 0; i < 2; i++) {
+            if (s->batch->aux[i]) cudaStreamDestroy(s->batch->aux[i]);
+            if (s->batch->join[i]) cudaEventDestroy(s->batch->join[i]);
+        }
+        if (s->batch->fork) cudaEventDestroy(s->batch->fork);
+        delete s->batch;
+    }
     if (s->m->gen_state == s) s->m->gen_state = nullptr;
     delete s;
 }

@@ -53,6 +53,9 @@ struct BatchBuffers {
     int *tok = nullptr, *pos = nullptr;             // device token ids / positions of the batch
     int* h_stage = nullptr;                         // pinned ring for their upload
     int stage_slot = 0;
+    // independent projections of a layer (wq/wk/wv, w1/w3) run side by side on two more streams
+    cudaStream_t aux[2] = {nullptr, nullptr};
+    cudaEvent_t fork = nullptr, join[2] = {nullptr, nullptr};
 };
 
 enum GraphKind : int { G_DECODE = 0, G_FEED, G_FWD_CLS, G_FWD, G_COUNT };

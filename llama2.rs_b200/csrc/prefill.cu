@@ -52,6 +52,11 @@ static int ensure_batch(l2_state* s) {
     if ((rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->tok), B * sizeof(int), s->allocs)) ||
         (rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->pos), B * sizeof(int), s->allocs))) { delete b; return rc; }
     if (cudaMallocHost(reinterpret_cast<void**>(&b->h_stage), sizeof(int) * 2 * B * CTL_RING) != cudaSuccess) { delete b; return fail(L2_ECUDA, "cudaMallocHost failed"); }
+    for (int i = 0; i < 2; i++) {
+        L2_CUDA(cudaStreamCreateWithFlags(&b->aux[i], cudaStreamNonBlocking));
+        L2_CUDA(cudaEventCreateWithFlags(&b->join[i], cudaEventDisableTiming));
+    }
+    L2_CUDA(cudaEventCreateWithFlags(&b->fork, cudaEventDisableTiming));
     s->batch = b;
     return L2_OK;
 }
@@ -76,10 +81,17 @@ int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos)
     for (int l = 0; l < c.n_layers; l++) {
         const DevLayer& y = m->layers[l];
         int rc;
-        // rmsnorm + wq/wk/wv (:217-226)
+        // rmsnorm + wq/wk/wv (:217-226): three independent GEMMs of 32 CTAs each (7B), side by side on three streams
+        L2_CUDA(cudaEventRecord(b->fork, st));
+        L2_CUDA(cudaStreamWaitEvent(b->aux[0], b->fork, 0));
+        L2_CUDA(cudaStreamWaitEvent(b->aux[1], b->fork, 0));
         if ((rc = gemm_batched(y.wq, b->x, D, true, y.nw_q, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->q, D, EPI_STORE, status, st))) return rc;
-        if ((rc = gemm_batched(y.wk, b->x, D, true, y.nw_k, m->eps, M, b->img[1], b->sv[1], b->osc[1], b->k, KV, EPI_STORE, status, st))) return rc;
-        if ((rc = gemm_batched(y.wv, b->x, D, true, y.nw_v, m->eps, M, b->img[2], b->sv[2], b->osc[2], b->v, KV, EPI_STORE, status, st))) return rc;
+        if ((rc = gemm_batched(y.wk, b->x, D, true, y.nw_k, m->eps, M, b->img[1], b->sv[1], b->osc[1], b->k, KV, EPI_STORE, status, b->aux[0]))) return rc;
+        if ((rc = gemm_batched(y.wv, b->x, D, true, y.nw_v, m->eps, M, b->img[2], b->sv[2], b->osc[2], b->v, KV, EPI_STORE, status, b->aux[1]))) return rc;
+        for (int i = 0; i < 2; i++) {
+            L2_CUDA(cudaEventRecord(b->join[i], b->aux[i]));
+            L2_CUDA(cudaStreamWaitEvent(st, b->join[i], 0));
+        }
         // rope, all rows into the cache, then attention (:228-256)
         RopeParams r{};
         r.q = b->q; r.k = b->k; r.v = b->v; r.kc = s->kc + (size_t)l * ls; r.vc = s->vc + (size_t)l * ls;
@@ -93,8 +105,12 @@ int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos)
         // wo + residual (:260-264)
         if ((rc = gemm_batched(y.wo, b->att, D, true, nullptr, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->x, D, EPI_RESID, status, st))) return rc;
         // rmsnorm + w1/w3 + SwiGLU (:266-276); their rows are stored in w2's K order
+        L2_CUDA(cudaEventRecord(b->fork, st));
+        L2_CUDA(cudaStreamWaitEvent(b->aux[0], b->fork, 0));
         if ((rc = gemm_batched(y.w1, b->x, D, true, y.nw_1, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->h1, H, EPI_STORE, status, st))) return rc;
-        if ((rc = gemm_batched(y.w3, b->x, D, true, y.nw_3, m->eps, M, b->img[1], b->sv[1], b->osc[1], b->h3, H, EPI_STORE, status, st))) return rc;
+        if ((rc = gemm_batched(y.w3, b->x, D, true, y.nw_3, m->eps, M, b->img[1], b->sv[1], b->osc[1], b->h3, H, EPI_STORE, status, b->aux[0]))) return rc;
+        L2_CUDA(cudaEventRecord(b->join[0], b->aux[0]));
+        L2_CUDA(cudaStreamWaitEvent(st, b->join[0], 0));
         launch_swiglu(b->h1, b->h3, b->hb, (size_t)M * H, st);
         // w2 + residual (:279-285)
         if ((rc = gemm_batched(y.w2, b->hb, H, false, nullptr, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->x, D, EPI_RESID, status, st))) return rc;
