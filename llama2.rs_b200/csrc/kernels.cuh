@@ -78,6 +78,8 @@ struct TcParams {
     int tiles16, G, gs, rows;
     int m, mpad, n;        // tokens, tokens padded to a multiple of 4, n = 4 * mpad
     int ldo, epi;
+    int ksplit;            // > 1: the groups are split over gridDim.y CTAs, slice k writes out + k * kstride (plain stores)
+    size_t kstride;
 };
 
 struct QuantParams {
@@ -195,6 +197,8 @@ void launch_act_quant(const QuantParams& p, int M, cudaStream_t st);
 void launch_rope_append(const RopeParams& p, int n_heads, int M, cudaStream_t st);
 void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_t st);
 void launch_swiglu(const float* h1, const float* h3, float* hb, size_t n, cudaStream_t st);
+// out[m][o] (+)= sum over the K slices, in slice order: finishes a GEMM whose groups were split over several CTAs
+void launch_ksum(const float* part, size_t kstride, int ksplit, float* out, int ldo, int rows, int M, int epi, cudaStream_t st);
 cudaError_t launch_gemm_tc(const TcParams& p, cudaStream_t st);
 cudaError_t gemm_tc_init(int max_smem);
 size_t gemm_tc_smem_bytes(int gs, int n);

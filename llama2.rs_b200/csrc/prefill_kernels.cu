@@ -233,4 +233,21 @@ void launch_swiglu(const float* h1, const float* h3, float* hb, size_t n, cudaSt
     swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(h1, h3, hb, n);
 }
 
+__global__ void __launch_bounds__(256) ksum_kernel(const float* __restrict__ part, size_t kstride, int ksplit, float* __restrict__ out,
+                                                   int ldo, int rows, int M, int epi) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)M * rows) return;
+    const int m = (int)(i / rows), o = (int)(i % rows);
+    float v = 0.f;
+    for (int k = 0; k < ksplit; k++) v += part[(size_t)k * kstride + (size_t)m * rows + o];  // slice order: reproducible
+    float* dst = out + (size_t)m * ldo + o;
+    *dst = epi == EPI_RESID ? *dst + v : v;
+}
+
+void launch_ksum(const float* part, size_t kstride, int ksplit, float* out, int ldo, int rows, int M, int epi, cudaStream_t st) {
+    const size_t n = (size_t)M * rows;
+    g_launches++;
+    ksum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(part, kstride, ksplit, out, ldo, rows, M, epi);
+}
+
 }  // namespace l2
