@@ -47,7 +47,7 @@ constexpr int MAX_BATCH = 64;  // tokens of one batched forward (one tcgen05 til
 // Device buffers of the batched forward pass (transformer<B>, B >= 2).
 struct BatchBuffers {
     float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *h1 = nullptr, *h3 = nullptr, *hb = nullptr;
-    float* kpart = nullptr;                         // [4][tokens][DIM] partial results of GEMMs whose groups are split over CTAs
+    float* kpart[3] = {nullptr, nullptr, nullptr};  // [4][tokens][rows] partial results of GEMMs whose groups are split over CTAs, one per stream
     uint8_t* img[3] = {nullptr, nullptr, nullptr};  // digit images of up to three consumers
     int* sv[3] = {nullptr, nullptr, nullptr};
     float* osc[3] = {nullptr, nullptr, nullptr};
@@ -148,7 +148,7 @@ int tp_all_gather(l2_model* m, float* buf, size_t count, cudaStream_t st);
 void tp_disconnect(l2_model* m);
 void tp_rows(int total_rows, int rank, int world, int* row0, int* nrows);
 int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const float* nw, float eps, int M, uint8_t* img, int* sv, float* osc,
-                 float* out, int ldo, int epi, int* status, cudaStream_t st, float* kpart = nullptr, int sms = 148);
+                 float* out, int ldo, int epi, int* status, cudaStream_t st, float* kpart = nullptr, int sms = 148, int side_tiles = 0);
 int dev_alloc_bytes(void** p, size_t bytes, std::vector<void*>& allocs);
 void sk_set_matrix(SkJob& j, int seg, const DevQ& q, const float* x, const float* nw);
 }  // namespace l2
