@@ -135,6 +135,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-warmup", type=int, default=3, help="profiling runs may lower the warm-up floor")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model to this many layers (not a benchmark number)")
+    ap.add_argument("--tp-nccl", action="store_true", help="70b on N > 1 GPUs: NCCL all-gathers between per-operator kernels instead of peer-memory stores")
     ap.add_argument("--flags", type=int, default=0, help="L2_FLAG_* bits for the model (8 = one launch per operator instead of one kernel per token)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -147,7 +148,8 @@ def main():
                           % (size, gs, n_prompt, n_decode),
               "weights": "seeded synthetic checkpoint (seed %d) in the export.py .bin layout" % WEIGHT_SEED,
               "l2": "weights streamed per token (%s) exceed the 126 MB L2; no flush needed" % size,
-              "parallelism": ("tp%d: every QLinear split by output rows, NCCL all-gathers in the token graph" % world) if tp
+              "parallelism": ("tp%d: every QLinear split by output rows, %s" % (world, "NCCL all-gathers in the token graph" if args.tp_nccl else
+                                                                                   "token kernel storing into every rank's memory over NVLink")) if tp
               else ("replicas" if world > 1 else "single GPU")}
 
     if args.impl == "reference":
@@ -185,12 +187,18 @@ def main():
         model = l2.LlamaModel.from_blob(cfg, payload, device=dev, flags=args.flags)
     else:
         model = l2.LlamaModel.synthetic(cfg, WEIGHT_SEED, device=dev, flags=args.flags, tp=(rank, world) if tp else (0, 1))
-    if tp:
+    if tp and args.tp_nccl:
         ids = [l2.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         model.tp_connect(ids[0])
+    elif tp:
+        # peer memory: every rank maps every other rank's activation pool; the token kernel stores into all of them
+        handles = [None] * world
+        dist.all_gather_object(handles, model.tp_pool_handle())
+        for r in range(world):
+            model.tp_pool_attach(r, handles[r])
     # one persistent kernel per token on a single GPU; one launch per operator under tensor parallelism or on request
-    token_kernel = not tp and not (args.flags & 8) and not os.environ.get("L2_NO_TOKEN_KERNEL")
+    token_kernel = not (tp and args.tp_nccl) and not (args.flags & 8) and not os.environ.get("L2_NO_TOKEN_KERNEL")
     stream = torch.cuda.Stream(device=dev)
     model.set_stream(stream.cuda_stream)
     state = l2.RunState(model)

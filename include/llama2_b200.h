@@ -113,6 +113,15 @@ int l2_tp_unique_id(void* id128);
 int l2_model_tp_connect(l2_model* m, const void* id128);
 /* Rows [row0, row0 + nrows) of a matrix of total_rows rows owned by `rank`. */
 int l2_tp_rows(int total_rows, int rank, int world, int* row0, int* nrows);
+/* Tensor parallelism without NCCL on the token path: every rank makes a pool for the activations that cross
+ * ranks (l2_model_tp_pool_handle returns its 64-byte CUDA IPC handle), the host hands every rank's handle to
+ * every other rank, and each rank maps them with l2_model_tp_pool_attach(rank, handle).  Once all tp_world
+ * pools are attached, the first run state of the model runs its B=1 forwards as the one-kernel-per-token
+ * path, whose epilogues store straight into every rank's pool over NVLink (no collective, no barrier); all
+ * ranks must make the same calls in the same order.  Without this the NCCL path above is used.
+ * No counterpart in the reference (which has no multi-GPU path). */
+int l2_model_tp_pool_handle(l2_model* m, void* handle64);
+int l2_model_tp_pool_attach(l2_model* m, int rank, const void* handle64);
 
 /* ---- run state: RunState::new (src/models.rs:36-41) --------------------------------- */
 

@@ -165,6 +165,11 @@ __device__ __forceinline__ void store_tagged(void* base, size_t index, float v, 
     const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(static_cast<unsigned long long*>(base) + index), "l"(w) : "memory");
 }
+// The same word into a peer GPU's memory (over NVLink): system scope.
+__device__ __forceinline__ void store_tagged_peer(void* base, size_t index, float v, uint32_t tag) {
+    const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(static_cast<unsigned long long*>(base) + index), "l"(w) : "memory");
+}
 // One tagged value; returns false when the poll limit is reached.
 __device__ __forceinline__ bool load_tagged(const void* base, size_t index, uint32_t tag, float& v) {
     const unsigned long long* p = static_cast<const unsigned long long*>(base) + index;

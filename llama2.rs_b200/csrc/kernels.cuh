@@ -49,6 +49,7 @@ struct SkJob {
     // token kernel only: x / out / sdst point to (value, tag) pairs; the phases (indices into the phase
     // table) that write this job's inputs and the residual it adds to
     int in_phase[2], resid_phase;
+    int bcast;  // tensor parallel token kernel: the results are stored into every rank's buffers, not only this one's
 };
 
 struct alignas(16) SkParams {
@@ -132,6 +133,7 @@ struct AttnParams {
     int pos_fixed;                                   // >= 0: use this position instead of ctl->pos
     int kvh0, n_kv_local;                            // tensor parallelism: this launch covers kv heads [kvh0, kvh0 + n_kv_local); 0 local = all
     int in_phase;                                    // token kernel only: q/k/v/out are (value, tag) pairs, written by this phase
+    int bcast;                                       // tensor parallel token kernel: out goes to every rank
 };
 
 struct ClsParams {
@@ -180,6 +182,10 @@ struct TokenParams {
     int chunk, slots;           // ring geometry: unit records per slot, slots
     unsigned fixed_bytes;       // shared memory in front of the ring (digits, sums, scratch of the other phases)
     int skip;                   // debug: stream the weights but skip the GEMV arithmetic (results are wrong)
+    // tensor parallelism over peer memory: every rank's pool of tagged activations (same layout everywhere, this
+    // rank's own at pool[rank]); a phase that broadcasts stores at the same offset into each of them
+    char* pool[8];
+    int world, rank;
 };
 
 cudaError_t launch_token(const TokenParams& tk, int group_size, int attn_groups, int grid, size_t smem, cudaStream_t st);

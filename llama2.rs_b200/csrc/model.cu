@@ -269,7 +269,7 @@ static void set_scatter3(float** sdst, const int** sidx, int* n, l2_state* s, co
 }
 
 // The four GEMV launches of a layer; each also prefetches the next GEMV's weights into L2.
-static int plan_layer_gemv(l2_state* s, int l, int which, SkLaunch& L) {
+static int plan_layer_gemv(l2_state* s, int l, int which, SkLaunch& L, bool direct = false) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
     const DevLayer& y = m->layers[l];
@@ -277,7 +277,7 @@ static int plan_layer_gemv(l2_state* s, int l, int which, SkLaunch& L) {
     L.gs = c.group_size;
     L.p.eps = m->eps;
     SkJob* j = L.p.job;
-    const bool tp = m->tp_world > 1;
+    const bool tp = m->tp_world > 1 && !direct;  // direct: the token kernel stores into every rank's buffers itself
     switch (which) {
         case 0:  // rmsnorm + wq/wk/wv (src/models.rs:217-226)
             L.p.njobs = 3;
@@ -290,8 +290,8 @@ static int plan_layer_gemv(l2_state* s, int l, int which, SkLaunch& L) {
             L.p.njobs = 1;
             sk_set_matrix(j[0], 0, y.wo, s->att, nullptr); j[0].out = s->x + y.wo.row0; j[0].epi = EPI_RESID;
             if (!tp) {  // with tensor parallelism the copies are made after the all-gather of x
-                j[0].sdst[0] = s->x1; j[0].sidx[0] = y.w1.inv;
-                j[0].sdst[1] = s->x3; j[0].sidx[1] = y.w3.inv;
+                j[0].sdst[0] = s->x1; j[0].sidx[0] = y.w1.inv + y.wo.row0;  // indexed by the rows this process holds
+                j[0].sdst[1] = s->x3; j[0].sidx[1] = y.w3.inv + y.wo.row0;
                 j[0].nscatter = 2;
             }
             sk_prefetch_next(L, y.w1);
@@ -308,7 +308,10 @@ static int plan_layer_gemv(l2_state* s, int l, int which, SkLaunch& L) {
         default:  // w2 + residual (:279-285); the new x goes to the next layer's q/k/v K orders
             L.p.njobs = 1;
             sk_set_matrix(j[0], 0, y.w2, s->hb, nullptr); j[0].out = s->x + y.w2.row0; j[0].epi = EPI_RESID;
-            if (!tp) set_scatter3(j[0].sdst, j[0].sidx, &j[0].nscatter, s, l + 1 < c.n_layers ? &m->layers[l + 1] : nullptr);
+            if (!tp) {
+                set_scatter3(j[0].sdst, j[0].sidx, &j[0].nscatter, s, l + 1 < c.n_layers ? &m->layers[l + 1] : nullptr);
+                for (int i = 0; i < j[0].nscatter; i++) j[0].sidx[i] += y.w2.row0;
+            }
             if (l + 1 < c.n_layers) {
                 sk_prefetch_next(L, m->layers[l + 1].wq);
                 sk_prefetch_next(L, m->layers[l + 1].wk);
@@ -332,7 +335,7 @@ static void launch_w13(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_l
 static void launch_w2(l2_state* s, int l, cudaStream_t st, bool pdl) { launch_layer_gemv(s, l, 3, st, pdl); }
 
 // rope + cache append + attention (src/models.rs:228-256)
-static AttnParams attention_params(l2_state* s, int l) {
+static AttnParams attention_params(l2_state* s, int l, bool direct = false) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
     const DevLayer& y = m->layers[l];
@@ -342,7 +345,8 @@ static AttnParams attention_params(l2_state* s, int l) {
     a.kc = s->kc + (size_t)l * ls; a.vc = s->vc + (size_t)l * ls;
     a.rope_cos = m->rope_cos; a.rope_sin = m->rope_sin;
     a.ctl = s->ctl; a.part = s->part; a.counter = s->counter;
-    a.out = m->tp_world > 1 ? s->att_nat : s->att; a.oidx = m->tp_world > 1 ? nullptr : y.wo.inv;  // tensor parallel: natural order, gathered and permuted afterwards
+    const bool gathered = m->tp_world > 1 && !direct;  // tensor parallel over NCCL: natural order, gathered and permuted afterwards
+    a.out = gathered ? s->att_nat : s->att; a.oidx = gathered ? nullptr : y.wo.inv;
     a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups();
     a.n_kv_local = c.n_kv_heads / m->tp_world; a.kvh0 = m->tp_rank * a.n_kv_local;
     a.max_split = s->max_split; a.split_min = 64;
@@ -374,6 +378,28 @@ static EmbedParams embed_params(l2_state* s, int kind) {
 }
 
 // ---- the forward pass as one persistent kernel ---------------------------------------------------
+
+// The tagged activation vectors of the token kernel live in one pool with the same layout on every rank,
+// so that a rank can store into a peer's pool at the offset it uses in its own.
+struct TaggedLayout { size_t off[11], n[11], total; };
+static TaggedLayout tagged_layout(const l2_model* m) {
+    const l2_config& c = m->shape.c;
+    const size_t D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
+    const size_t n[11] = {D, D, D, D, D, KV, KV, D, D, D, H};  // x, xq, xk, xv, q, k, v, att, x1, x3, hb
+    TaggedLayout t{};
+    size_t at = 0;
+    for (int i = 0; i < 11; i++) { t.off[i] = at; t.n[i] = n[i]; at += (n[i] * 8 + 255) & ~(size_t)255; }
+    t.total = at;
+    return t;
+}
+
+// The forward of this state runs as the token kernel: always on one GPU; under tensor parallelism when the
+// peers' pools are attached and this state is the one that works in the model's pool.
+static bool token_path(const l2_state* s) {
+    const l2_model* m = s->m;
+    if (!m->use_token_kernel) return false;
+    return m->tp_world == 1 || (m->tp_direct && m->tp_pool_owner == s);
+}
 
 // Ring geometry and shared-memory carve-up shared by every phase of the token kernel.
 static int plan_token(l2_state* s) {
@@ -408,13 +434,20 @@ static int plan_token(l2_state* s) {
     if (int rc = dev_alloc(reinterpret_cast<void**>(&s->tk.bar), 256, s->allocs)) return rc;
     L2_CUDA(cudaMemset(s->tk.bar, 0, 256));
     {   // tagged activations, zeroed once: tag 0 is never expected
-        const size_t D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
-        struct { unsigned long long** p; size_t n; } bufs[] = {{&s->t_x, D}, {&s->t_xq, D}, {&s->t_xk, D}, {&s->t_xv, D}, {&s->t_q, D}, {&s->t_k, KV},
-                                                               {&s->t_v, KV}, {&s->t_att, D}, {&s->t_x1, D}, {&s->t_x3, D}, {&s->t_hb, H}};
-        for (auto& b : bufs) {
-            if (int rc = dev_alloc(reinterpret_cast<void**>(b.p), b.n * 8, s->allocs)) return rc;
-            L2_CUDA(cudaMemset(*b.p, 0, b.n * 8));
+        const TaggedLayout lay = tagged_layout(m);
+        char* pool = nullptr;
+        if (m->tp_world > 1) {
+            pool = m->tp_pool;  // made (and zeroed) by l2_model_tp_pool_handle, known to the peers
+        } else {
+            if (int rc = dev_alloc(reinterpret_cast<void**>(&pool), lay.total, s->allocs)) return rc;
+            L2_CUDA(cudaMemset(pool, 0, lay.total));
         }
+        if (!pool) return fail(L2_EINVAL, "token kernel: no activation pool");
+        unsigned long long** bufs[11] = {&s->t_x, &s->t_xq, &s->t_xk, &s->t_xv, &s->t_q, &s->t_k, &s->t_v, &s->t_att, &s->t_x1, &s->t_x3, &s->t_hb};
+        for (int i = 0; i < 11; i++) *bufs[i] = reinterpret_cast<unsigned long long*>(pool + lay.off[i]);
+        s->tk.world = m->tp_world;
+        s->tk.rank = m->tp_rank;
+        for (int r = 0; r < 8; r++) s->tk.pool[r] = r < m->tp_world ? (m->tp_world > 1 ? m->tp_peers[r] : pool) : nullptr;
     }
     return L2_OK;
 }
@@ -430,14 +463,16 @@ static int build_phase_table(l2_state* s, int kind) {
         return t.back();
     };
     // the token kernel's copies of the activation vectors: (value, tag) pairs instead of floats
-    auto tg = [&](const float* plain) -> float* {
-        const struct { const float* f; unsigned long long* t; } map[] = {{s->x, s->t_x}, {s->xq, s->t_xq}, {s->xk, s->t_xk}, {s->xv, s->t_xv},
-                                                                          {s->q, s->t_q}, {s->k, s->t_k}, {s->v, s->t_v}, {s->att, s->t_att},
-                                                                          {s->x1, s->t_x1}, {s->x3, s->t_x3}, {s->hb, s->t_hb}};
-        for (auto& e : map)
-            if (e.f == plain) return reinterpret_cast<float*>(e.t);
+    const TaggedLayout lay = tagged_layout(m);
+    auto tg = [&](const float* plain) -> float* {  // a pointer into a plain vector -> the same element of its tagged copy
+        const struct { const float* f; unsigned long long* t; } map[11] = {{s->x, s->t_x}, {s->xq, s->t_xq}, {s->xk, s->t_xk}, {s->xv, s->t_xv},
+                                                                            {s->q, s->t_q}, {s->k, s->t_k}, {s->v, s->t_v}, {s->att, s->t_att},
+                                                                            {s->x1, s->t_x1}, {s->x3, s->t_x3}, {s->hb, s->t_hb}};
+        for (int i = 0; i < 11; i++)
+            if (plain >= map[i].f && plain < map[i].f + lay.n[i]) return reinterpret_cast<float*>(map[i].t + (plain - map[i].f));
         return nullptr;
     };
+    const bool direct = m->tp_world > 1;
     bool bad = false;
     auto must = [&](float* p) { if (!p) bad = true; return p; };
     {
@@ -450,7 +485,8 @@ static int build_phase_table(l2_state* s, int kind) {
     for (int l = 0; l < c.n_layers; l++) {
         int qkv_phase = 0, attn_phase = 0, w13_phase = 0;
         for (int which = 0; which < 4; which++) {
-            const SkLaunch& L = s->plans[(size_t)l * 4 + which];
+            SkLaunch L;
+            if (int rc = plan_layer_gemv(s, l, which, L, direct)) return rc;
             const int me = (int)t.size();
             PhaseRec& r = add(L.nseg == 2 ? PH_GEMV2 : PH_GEMV1);
             r.u.sk = L.p;
@@ -466,14 +502,16 @@ static int build_phase_table(l2_state* s, int kind) {
                 J.out = must(tg(J.out));
                 for (int i = 0; i < J.nscatter; i++) J.sdst[i] = must(tg(J.sdst[i]));
                 J.resid_phase = x_phase;
+                J.bcast = direct && which != 0;  // q/k/v stay with the rank that owns the heads; everything else every rank needs
             }
             if (which == 0) {
                 qkv_phase = me;
                 attn_phase = (int)t.size();
-                AttnParams a = attention_params(s, l);
+                AttnParams a = attention_params(s, l, direct);
                 a.q = must(tg(a.q)); a.k = must(tg(a.k)); a.v = must(tg(a.v));
                 a.out = must(tg(a.out));
                 a.in_phase = qkv_phase;
+                a.bcast = direct;
                 add(PH_ATTN).u.at = a;
             } else if (which == 1) {
                 x_phase = me;  // wo wrote x (+ copies for w1/w3)
@@ -520,7 +558,7 @@ static int enqueue_token(l2_state* s, int kind, cudaStream_t st) {
 static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
-    if (m->use_token_kernel && m->tp_world == 1) return enqueue_token(s, kind, st);
+    if (token_path(s)) return enqueue_token(s, kind, st);
     const bool pdl = m->use_pdl;
     const int L = c.n_layers, D = c.dim;
     launch_embed(embed_params(s, kind), st, false);  // first node of the token: plain stream order
@@ -569,8 +607,9 @@ static int enqueue_forward(l2_state* s, int kind, cudaStream_t st) {
     return L2_OK;
 }
 
-static int nodes_per_forward(const l2_model* m, int kind) {
-    if (m->use_token_kernel && m->tp_world == 1) return 1;
+static int nodes_per_forward(const l2_state* s, int kind) {
+    const l2_model* m = s->m;
+    if (token_path(s)) return 1;
     const int L = m->shape.c.n_layers;
     int n = 1 + 5 * L;
     if (m->tp_world > 1) n += 3 * L - 1;  // the copies into the consumers' K orders after each all-gather
@@ -582,7 +621,8 @@ static int nodes_per_forward(const l2_model* m, int kind) {
 // Runs one forward of the given kind on the model's stream (graph replay unless disabled).
 static int run_forward(l2_state* s, int kind) {
     l2_model* m = s->m;
-    if (m->use_token_kernel && m->tp_world == 1 && !s->d_phases[kind]) {
+    if (m->tp_direct && !m->tp_pool_owner) m->tp_pool_owner = s;  // the first state that runs works in the model's pool
+    if (token_path(s) && !s->d_phases[kind]) {
         if (!s->tk.bar)
             if (int rc = plan_token(s)) return rc;
         if (int rc = build_phase_table(s, kind)) return rc;
@@ -603,7 +643,7 @@ static int run_forward(l2_state* s, int kind) {
         cudaGraphDestroy(graph);
         cudaStreamDestroy(cap);
         if (e != cudaSuccess) return fail(L2_ECUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
-        s->graph_nodes[kind] = nodes_per_forward(m, kind);
+        s->graph_nodes[kind] = nodes_per_forward(s, kind);
     }
     L2_CUDA(cudaGraphLaunch(s->graphs[kind], m->stream));
     g_launches += s->graph_nodes[kind];
@@ -716,10 +756,51 @@ extern "C" void l2_model_close(l2_model* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     if (m->gen_state) l2_state_free(m->gen_state);
+    for (int r = 0; r < 8; r++)
+        if (m->tp_peers[r] && r != m->tp_rank) cudaIpcCloseMemHandle(m->tp_peers[r]);
+    if (m->tp_pool) cudaFree(m->tp_pool);
     tp_disconnect(m);
     free_allocs(m->allocs);
     if (m->own_stream) cudaStreamDestroy(m->own_stream);
     delete m;
+}
+
+// ---- tensor parallelism over peer memory ----------------------------------------------------------
+extern "C" int l2_model_tp_pool_handle(l2_model* m, void* handle64) {
+    clear_error();
+    if (!m || !handle64) return fail(L2_EINVAL, "l2_model_tp_pool_handle: null argument");
+    if (m->tp_world <= 1) return fail(L2_EINVAL, "l2_model_tp_pool_handle: the model is not tensor parallel");
+    L2_CUDA(cudaSetDevice(m->device));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+    if (!m->tp_pool) {
+        const TaggedLayout lay = tagged_layout(m);
+        L2_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->tp_pool), lay.total));
+        L2_CUDA(cudaMemset(m->tp_pool, 0, lay.total));
+        m->tp_peers[m->tp_rank] = m->tp_pool;
+    }
+    cudaIpcMemHandle_t h;
+    L2_CUDA(cudaIpcGetMemHandle(&h, m->tp_pool));
+    memcpy(handle64, &h, sizeof h);
+    return L2_OK;
+}
+
+extern "C" int l2_model_tp_pool_attach(l2_model* m, int rank, const void* handle64) {
+    clear_error();
+    if (!m || !handle64) return fail(L2_EINVAL, "l2_model_tp_pool_attach: null argument");
+    if (rank < 0 || rank >= m->tp_world || m->tp_world > 8) return fail(L2_EINVAL, "l2_model_tp_pool_attach: rank %d outside 0..%d", rank, m->tp_world - 1);
+    if (!m->tp_pool) return fail(L2_EINVAL, "l2_model_tp_pool_attach: call l2_model_tp_pool_handle first");
+    L2_CUDA(cudaSetDevice(m->device));
+    if (rank != m->tp_rank && !m->tp_peers[rank]) {
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handle64, sizeof h);
+        void* p = nullptr;
+        L2_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        m->tp_peers[rank] = static_cast<char*>(p);
+    }
+    bool all = true;
+    for (int r = 0; r < m->tp_world; r++) all = all && m->tp_peers[r];
+    m->tp_direct = all;
+    return L2_OK;
 }
 
 extern "C" int l2_model_config(const l2_model* m, l2_config* out) {
@@ -829,6 +910,7 @@ extern "C" void l2_state_free(l2_state* s) {
         delete s->batch;
     }
     if (s->m->gen_state == s) s->m->gen_state = nullptr;
+    if (s->m->tp_pool_owner == s) s->m->tp_pool_owner = nullptr;
     delete s;
 }
 

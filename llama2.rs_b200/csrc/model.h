@@ -84,6 +84,12 @@ struct l2_model {
     bool use_token_kernel = true;    // B=1 forward as one persistent kernel (single GPU only)
     int tp_rank = 0, tp_world = 1;   // tensor parallelism: this process owns 1/tp_world of every matrix's rows
     void* nccl_comm = nullptr;
+    // tensor parallelism over peer memory (token kernel): one pool of tagged activations per rank, the peers'
+    // pools mapped through CUDA IPC; the first run state of the model works in the pool
+    char* tp_pool = nullptr;
+    char* tp_peers[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool tp_direct = false;          // every rank's pool is attached
+    l2_state* tp_pool_owner = nullptr;
 };
 
 struct l2_state {

@@ -76,6 +76,17 @@ __device__ __forceinline__ void ring_abort(const Ring& R, int code) {
     sts_volatile_i32(R.abort_flag, 1);
 }
 
+// A result that other ranks need as well (tensor parallelism): stored into this rank's buffer and at the
+// same offset into every peer's pool.  The consumers on every rank poll their own memory only.
+__device__ __forceinline__ void store_tagged_all(const TokenParams& tk, bool bcast, void* base, size_t index, float v, uint32_t tag) {
+    store_tagged(base, index, v, tag);
+    if (bcast && tk.world > 1) {
+        const size_t off = static_cast<char*>(base) - tk.pool[tk.rank];
+        for (int r = 0; r < tk.world; r++)
+            if (r != tk.rank) store_tagged_peer(tk.pool[r] + off, index, v, tag);
+    }
+}
+
 __device__ __forceinline__ void prefetch_line_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 // Producer side of one GEMV phase (called by the whole producer warp, lane 0 issues): streams this
@@ -198,8 +209,8 @@ __device__ __forceinline__ void warm_attention(const AttnParams& p, int pos_now,
 // Consumer side of one GEMV phase: stage the digits, multiply, reduce, epilogue.  Returns false
 // when a wait gave up.  `kbase` is the number of slot fills consumed before this phase.
 template <int W, int NSEG>
-__device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, const Ring& R, float* red, float* oscale, uint32_t& kbase,
-                           unsigned long long* stamp, uint32_t tagbase, int phase) {
+__device__ __forceinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P, uint8_t* smem, const Ring& R, float* red, float* oscale,
+                                           uint32_t& kbase, unsigned long long* stamp, uint32_t tagbase, int phase) {
     constexpr int GS = 32 * W;
     constexpr int ROWS = 16 * NSEG;
     constexpr uint32_t UB = 256u * W + 80u;
@@ -410,11 +421,11 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
             const float y3 = __shfl_down_sync(0xffffffffu, y, 16);
             if (lane < 16 && row < J.rows) {
                 const float sg = y * (1.0f / (1.0f + expf(-y)));
-                store_tagged(J.out, row, sg * y3, out_tag);
+                store_tagged_all(tk, J.bcast, J.out, row, sg * y3, out_tag);
             }
         } else if (lane < 16 && row < J.rows) {
             if (J.epi == EPI_STORE) {
-                store_tagged(J.out, row, y, out_tag);
+                store_tagged_all(tk, J.bcast, J.out, row, y, out_tag);
             } else {  // residual add (src/models.rs:47-51) + copies in the next consumers' K orders
                 const bool pre = e_pre && tl == warp;
                 int idx[3] = {e_idx[0], e_idx[1], e_idx[2]};
@@ -427,10 +438,10 @@ __device__ __forceinline__ bool gemv_phase(const SkParams& P, uint8_t* smem, con
                 if (!pre || (uint32_t)(e_res >> 32) != (tagbase | (uint32_t)J.resid_phase))  // not the early copy: poll
                     fine = load_tagged(J.out, row, tagbase | (uint32_t)J.resid_phase, res) && fine;
                 const float xv = res + y;
-                store_tagged(J.out, row, xv, out_tag);
+                store_tagged_all(tk, J.bcast, J.out, row, xv, out_tag);
 #pragma unroll
                 for (int s = 0; s < 3; s++)
-                    if (s < J.nscatter) store_tagged(J.sdst[s], idx[s], xv, out_tag);
+                    if (s < J.nscatter) store_tagged_all(tk, J.bcast, J.sdst[s], idx[s], xv, out_tag);
             }
         }
     }
@@ -469,7 +480,8 @@ __host__ __device__ constexpr size_t tk_att_bytes(int ag) {
 }
 
 template <int AG>
-__device__ __noinline__ bool attn_phase(const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp, uint32_t in_tag, uint32_t out_tag) {
+__device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp, uint32_t in_tag,
+                                        uint32_t out_tag) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* base = reinterpret_cast<float*>(scratch);
     float(*qs)[HS] = reinterpret_cast<float(*)[HS]>(base);
@@ -672,7 +684,7 @@ __device__ __noinline__ bool attn_phase(const AttnParams& p, uint8_t* scratch, i
                     aa += sm_acc[w][g][i] * e;
                 }
                 if (nsplit == 1) {
-                    store_tagged(p.out, oi[gi], aa / ll, out_tag);
+                    store_tagged_all(tk, p.bcast, p.out, oi[gi], aa / ll, out_tag);
                 } else {
                     float* dst = p.part + ((size_t)(kvh * AG + g) * p.max_split + split) * (HS + 2);
                     dst[i] = aa;
@@ -705,7 +717,7 @@ __device__ __noinline__ bool attn_phase(const AttnParams& p, uint8_t* scratch, i
                             ll += __ldcg(src + (size_t)s * (HS + 2) + HS + 1) * e;
                             aa += __ldcg(src + (size_t)s * (HS + 2) + i) * e;
                         }
-                        store_tagged(p.out, oi[gi], aa / ll, out_tag);
+                        store_tagged_all(tk, p.bcast, p.out, oi[gi], aa / ll, out_tag);
                     }
                 }
             }
@@ -993,9 +1005,9 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
         bool fine = true;
         switch (rec.type) {
             case PH_EMBED: embed_phase(rec.u.em, out_tag); break;
-            case PH_GEMV1: ok = gemv_phase<W, 1>(rec.u.sk, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
-            case PH_GEMV2: ok = gemv_phase<W, 2>(rec.u.sk, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
-            case PH_ATTN: fine = attn_phase<AG>(rec.u.at, smem, tok_pos, stamp, tagbase | (uint32_t)rec.u.at.in_phase, out_tag); break;
+            case PH_GEMV1: ok = gemv_phase<W, 1>(tk, rec.u.sk, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
+            case PH_GEMV2: ok = gemv_phase<W, 2>(tk, rec.u.sk, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
+            case PH_ATTN: fine = attn_phase<AG>(tk, rec.u.at, smem, tok_pos, stamp, tagbase | (uint32_t)rec.u.at.in_phase, out_tag); break;
             case PH_CLS: fine = cls_phase(rec.u.cl, reinterpret_cast<float*>(smem), red, tagbase | (uint32_t)rec.u.cl.in_phase); break;
             case PH_SELECT: if (blockIdx.x == 0) select_phase(rec.u.se, red); break;
             case PH_ADVANCE: if (blockIdx.x == 0 && threadIdx.x == 0) rec.u.se.ctl->pos = rec.u.se.ctl->pos + 1; break;

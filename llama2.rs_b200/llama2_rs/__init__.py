@@ -109,6 +109,17 @@ class LlamaModel:
         buf = C.create_string_buffer(bytes(id_bytes), 128)
         check(lib.l2_model_tp_connect(self._h, buf))
 
+    def tp_pool_handle(self):
+        """64-byte CUDA IPC handle of this rank's activation pool (tensor parallelism over peer memory)."""
+        buf = C.create_string_buffer(64)
+        check(lib.l2_model_tp_pool_handle(self._h, buf))
+        return buf.raw
+
+    def tp_pool_attach(self, rank, handle_bytes):
+        """Maps rank `rank`'s pool; when every rank's pool is attached the token path needs no NCCL."""
+        buf = C.create_string_buffer(bytes(handle_bytes), 64)
+        check(lib.l2_model_tp_pool_attach(self._h, rank, buf))
+
     def set_stream(self, cuda_stream):
         check(lib.l2_model_set_stream(self._h, C.c_void_p(cuda_stream)))
 

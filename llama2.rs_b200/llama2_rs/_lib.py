@@ -60,6 +60,8 @@ SIGNATURES = {
     "l2_tp_unique_id": (C.c_int, [_vp]),
     "l2_model_tp_connect": (C.c_int, [_vp, _vp]),
     "l2_tp_rows": (C.c_int, [C.c_int, C.c_int, C.c_int, _p(C.c_int), _p(C.c_int)]),
+    "l2_model_tp_pool_handle": (C.c_int, [_vp, _vp]),
+    "l2_model_tp_pool_attach": (C.c_int, [_vp, C.c_int, _vp]),
     "l2_state_new": (C.c_int, [_vp, _p(_vp)]),
     "l2_state_reset": (C.c_int, [_vp]),
     "l2_state_free": (None, [_vp]),

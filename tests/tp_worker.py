@@ -17,12 +17,19 @@ import oracle as orc  # noqa: E402
 from conftest import assert_close, tiny_config  # noqa: E402
 
 
-def run_case(cfg, rank, world, steps, n_prompt, seed):
+def run_case(cfg, rank, world, steps, n_prompt, seed, direct):
     payload = l2.synth_fill(cfg, seed)
     gpu = l2.LlamaModel.from_blob(cfg, payload, device=rank, tp=(rank, world))
-    ids = [l2.tp_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(ids, src=0)
-    gpu.tp_connect(ids[0])
+    if direct:
+        # peer memory: every rank maps every other rank's activation pool; the token kernel stores into all of them
+        handles = [None] * world
+        dist.all_gather_object(handles, gpu.tp_pool_handle())
+        for r in range(world):
+            gpu.tp_pool_attach(r, handles[r])
+    else:
+        ids = [l2.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        gpu.tp_connect(ids[0])
     prompt = np.random.default_rng(seed).integers(0, cfg.vocab_size, n_prompt).astype(np.int32)
     got = l2.generate_ids(gpu, prompt, steps, trace_logits=True)
     fast = l2.generate_ids(gpu, prompt, steps)
@@ -44,10 +51,14 @@ def main():
     torch.cuda.set_device(rank)
     cfg = tiny_config(l2, group_size=64, n_kv_heads=2, dim=512, hidden=1024, n_layers=2)
     cfg.n_heads, cfg.n_kv_heads = 4, world if world in (1, 2, 4) else 4
-    run_case(cfg, rank, world, steps=40, n_prompt=21, seed=11)
     big = l2.preset_config("70B", 64)  # the real 70B projection shapes and GQA, two layers, small vocabulary
     big.n_layers, big.vocab_size, big.seq_len = 2, 2048, 128
-    run_case(big, rank, world, steps=24, n_prompt=9, seed=12)
+    for direct in (False, True):  # NCCL all-gathers between per-operator kernels; stores into peer memory from the token kernel
+        run_case(cfg, rank, world, steps=40, n_prompt=21, seed=11, direct=direct)
+        run_case(big, rank, world, steps=24, n_prompt=9, seed=12, direct=direct)
+        dist.barrier()
+        if rank == 0:
+            print("tp parity ok (%s)" % ("peer memory" if direct else "nccl"), flush=True)
     dist.barrier()
     if rank == 0:
         print("tp parity ok on %d ranks" % world)
