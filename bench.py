@@ -36,7 +36,7 @@ WORKLOADS = {  # name: (model size, group size, prompt tokens, decode tokens)  -
     "70b": ("70B", 64, 64, 256),
 }
 WEIGHT_SEED, PROMPT_SEED = 20240, 7
-TOKEN_KERNEL_TRAFFIC_RATIO = 1.038  # DRAM bytes / algorithmic bytes of the token kernel, from its ncu capture
+TOKEN_KERNEL_TRAFFIC_RATIO = 1.024  # DRAM bytes / algorithmic bytes of the token kernel, from its ncu capture
 
 
 def measured_peaks():
@@ -282,7 +282,7 @@ def main():
                     "achieved": model.decode_bytes * tok_s / 1e9, "peak": peak, "unit": "GB/s",
                     "frac": model.decode_bytes * tok_s / 1e9 / peak, "peak_kind": peak_kind,
                     # DRAM bytes per launch: ncu capture of the 4-layer case (profiles/token_kernel_7B_4layers.md,
-                    # dram read+write = 1.038 x its algorithmic bytes), scaled to a full launch by the bytes processed
+                    # dram read+write = 1.024 x its algorithmic bytes), scaled to a full launch by the bytes processed
                     "traffic": int(TOKEN_KERNEL_TRAFFIC_RATIO * model.decode_bytes),
                     "bytes_per_launch": int(model.decode_bytes), "us_per_launch": 1e6 / tok_s}
     else:
