@@ -8,7 +8,7 @@ decodes its own token stream (batch-1 decode has nothing to exchange; `scaling` 
 ranks).  `--workload 70b` on N > 1 GPUs shards the 70B model over the ranks (tensor parallel, NCCL all-gathers).
 
 A step is one pass of the workload: a seeded random prompt through prefill, then the decode
-loop (BASELINE config 0 for 7B: 32 prompt tokens, 256 greedy tokens).  `value` is decode tok/s with
+loop (the headline configuration for 7B: 32 prompt tokens, 256 greedy tokens).  `value` is decode tok/s with
 weights, KV cache and the loop state resident in HBM (CUDA events on the launching stream);
 `e2e` is the same loop driven token by token through the C ABI with host buffers (l2_decode_step:
 token and position go host->device and the chosen token comes back every step).  Weights are a
@@ -30,7 +30,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "llama2.rs_b200"))
 sys.path.insert(0, os.path.join(ROOT, "oracle"))
 
-WORKLOADS = {  # name: (model size, group size, prompt tokens, decode tokens)  -- BASELINE configs 0, 2, 3
+WORKLOADS = {  # name: (model size, group size, prompt tokens, decode tokens)  -- the benchmark configurations
     "7b": ("7B", 128, 32, 256),
     "13b": ("13B", 128, 128, 512),
     "70b": ("70B", 64, 64, 256),
@@ -281,8 +281,8 @@ def main():
         roofline = {"bound": "hbm", "kernel": "token_kernel (whole B=1 forward, one launch per token)",
                     "achieved": model.decode_bytes * tok_s / 1e9, "peak": peak, "unit": "GB/s",
                     "frac": model.decode_bytes * tok_s / 1e9 / peak, "peak_kind": peak_kind,
-                    # DRAM bytes per launch: ncu capture of the 4-layer case (profiles/token_kernel_7B_4layers.md,
-                    # dram read+write = 1.024 x its algorithmic bytes), scaled to a full launch by the bytes processed
+                    # DRAM bytes per launch: ncu capture of the same kernel on a 4-layer model (dram read+write =
+                    # 1.024 x its algorithmic bytes), scaled to a full launch by the bytes processed
                     "traffic": int(TOKEN_KERNEL_TRAFFIC_RATIO * model.decode_bytes),
                     "bytes_per_launch": int(model.decode_bytes), "us_per_launch": 1e6 / tok_s}
     else:

@@ -122,7 +122,8 @@ def test_tokenizer_abb_merge_rule(l2, tmp_path):
 
 
 def test_reference_tokenizer_file_if_present(l2):
-    path = "/root/reference/tokenizer.bin"
+    # the reference checkout, when it sits next to this repository
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "tokenizer.bin")
     if not os.path.exists(path):
         pytest.skip("reference tokenizer.bin not available")
     t = l2.Tokenizer(path)
