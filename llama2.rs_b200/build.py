@@ -32,7 +32,7 @@ def build(verbose=False, force=False):
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(HERE, "..", "include", "llama2_b200.h"))
-    objs = []
+    objs, jobs = [], []
     for src in CU_SOURCES + CPP_SOURCES:
         path = os.path.join(CSRC, src)
         obj = os.path.join(HERE, "build", src + ".o")
@@ -43,11 +43,16 @@ def build(verbose=False, force=False):
             cmd = [NVCC] + NVCC_FLAGS + trace + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
             if not src.endswith(".cu"):
                 cmd = [NVCC] + NVCC_FLAGS + ["-x", "cu", "-c", path, "-o", obj]
-            r = subprocess.run(cmd, capture_output=True, text=True)
-            if verbose or r.returncode:
-                sys.stderr.write(r.stdout + r.stderr)
-            if r.returncode:
-                raise RuntimeError("nvcc failed on " + src)
+            jobs.append((src, cmd))
+    # the translation units compile side by side (the token kernel alone takes most of a minute)
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=max(1, min(8, os.cpu_count() or 1))) as pool:
+        results = list(pool.map(lambda j: (j[0], subprocess.run(j[1], capture_output=True, text=True)), jobs))
+    for src, r in results:
+        if verbose or r.returncode:
+            sys.stderr.write(r.stdout + r.stderr)
+        if r.returncode:
+            raise RuntimeError("nvcc failed on " + src)
     if force or _stale(OUT, objs):
         cmd = [NVCC, "-shared", "-o", OUT] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-ccbin", HOST_CXX, "-lpthread", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
