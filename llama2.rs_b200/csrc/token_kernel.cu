@@ -981,7 +981,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
     const int tok_pos = tk.ctl->pos;  // read once: the attention phases would pay a trip to the L2 each
     // Tags of this launch: (launches so far + 1) in the upper bits, the writing phase in the lower ten.
     const uint32_t epoch = tk.bar[32];
-    const uint32_t tagbase = (epoch + 1u) << 10;
+    const uint32_t tagbase = (epoch % 4194303u + 1u) << 10;  // 22 bits, never zero (zero means "not tagged")
     uint32_t kbase = 0;
     unsigned bar_target = tk.bar[33] * gridDim.x;  // arrivals of the grid barriers of earlier launches (the counter is never reset)
     unsigned bars_done = 0;
