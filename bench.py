@@ -155,6 +155,9 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
+        if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+            # the launcher pins every rank to one OpenMP thread; this arm is one process that should use the host's cores
+            os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
         steps = max(1, args.steps)
         arm = CpuArm(args.workload)
         vals = [arm.run() for _ in range(max(0, args.warmup) + steps)][-steps:]
