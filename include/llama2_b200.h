@@ -28,7 +28,9 @@ extern "C" {
 #define L2_ECUDA (-3)    /* CUDA runtime failure or no device */
 #define L2_EIO (-4)      /* file could not be opened / read / written */
 #define L2_ERANGE (-5)   /* position / steps beyond SEQ_LEN, token beyond VOCAB_SIZE */
-#define L2_ESTATUS (-6)  /* a device-side bounded wait gave up (status word set) */
+#define L2_ESTATUS (-6)  /* a device-side bounded wait gave up (status word set): the launch left early, its results are not
+                            valid, and the run state refuses further calls until l2_state_reset (which also evens out the
+                            kernel's barrier count).  Under tensor parallelism every rank of the group must reset. */
 
 #define L2_START 1 /* src/tokenizer.rs:10 */
 #define L2_RET 13  /* src/tokenizer.rs:11 */
@@ -56,6 +58,9 @@ typedef struct l2_options {
     int32_t flags;          /* L2_FLAG_* */
     int32_t tp_rank;        /* tensor parallelism: this process's rank ... */
     int32_t tp_world;       /* ... of tp_world processes, one per GPU of the box (0 or 1 = single GPU) */
+    int32_t poll_limit_log2; /* one-kernel-per-token path: log2 of the polls of an input another CTA (or rank) writes before the
+                                kernel gives up and the call returns L2_ESTATUS; 0 = default (20, about a second); 8..30.
+                                One value per device and process: the model opened last sets it. */
 } l2_options;
 
 #define L2_FLAG_NO_GRAPH 1 /* launch kernels directly instead of replaying the per-token CUDA graph */
@@ -122,6 +127,11 @@ int l2_tp_rows(int total_rows, int rank, int world, int* row0, int* nrows);
  * No counterpart in the reference (which has no multi-GPU path). */
 int l2_model_tp_pool_handle(l2_model* m, void* handle64);
 int l2_model_tp_pool_attach(l2_model* m, int rank, const void* handle64);
+/* Bytes of a rank's pool, and attaching a pool by device pointer instead of by IPC handle: for a rank whose pool lives in
+ * this process (several GPUs driven by one process with peer access enabled by the caller, or a buffer that stands in for a
+ * rank that never runs, as the bounded-wait tests use).  The memory must stay valid until the model is closed. */
+size_t l2_model_tp_pool_bytes(const l2_model* m);
+int l2_model_tp_pool_attach_ptr(l2_model* m, int rank, void* device_ptr);
 
 /* ---- run state: RunState::new (src/models.rs:36-41) --------------------------------- */
 

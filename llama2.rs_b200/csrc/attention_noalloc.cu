@@ -17,6 +17,8 @@
 //     before starting any stream capture.
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "host_common.h"
 #include "kernels.cuh"
 #include "model.h"
@@ -34,7 +36,7 @@ static __device__ __align__(256) unsigned char g_attention_scratch[L2_NOALLOC_SC
 
 namespace {
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {};  // device address of g_attention_scratch, per device
+std::atomic<void*> g_scratch_addr[kMaxDevices];  // device address of g_attention_scratch, per device (zero-initialised: static storage)
 }
 
 using namespace l2;
@@ -50,16 +52,15 @@ extern "C" int l2_attention_decode_noalloc(int n_heads, int n_kv_heads, int pos,
     int dev = 0;
     L2_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return fail(L2_EINVAL, "l2_attention_decode_noalloc: device ordinal %d unsupported", dev);
-    if (!g_scratch_addr[dev]) {  // set-up, once per device, with that device current
-        void* p = nullptr;
-        L2_CUDA(cudaGetSymbolAddress(&p, g_attention_scratch));
-        g_scratch_addr[dev] = p;
+    void* addr = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!addr) {  // set-up, once per device, with that device current (two threads racing here store the same value)
+        L2_CUDA(cudaGetSymbolAddress(&addr, g_attention_scratch));
+        g_scratch_addr[dev].store(addr, std::memory_order_release);
     }
-    char* base = static_cast<char*>(g_scratch_addr[dev]);
+    char* base = static_cast<char*>(addr);
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     // Same split geometry as l2_attention_decode_dev, capped by what the array holds.
-    int max_split = (2 * 148 + n_kv_heads - 1) / n_kv_heads;
-    if (max_split < 1) max_split = 1;
+    int max_split = attention_max_split(n_kv_heads);  // from the SM count of the current device (an attribute query, no allocation)
     if (max_split > L2_NOALLOC_MAX_SPLIT) max_split = L2_NOALLOC_MAX_SPLIT;
     L2_CUDA(cudaMemsetAsync(base, 0, L2_NOALLOC_TICKET_BYTES, st));  // the tickets must start at zero
     AttnParams a{};

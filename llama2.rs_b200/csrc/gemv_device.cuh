@@ -51,6 +51,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
 // it in the status word and stops using the data.
 constexpr uint32_t SK_WAIT_LIMIT = 1u << 17;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = SK_WAIT_LIMIT) {
+#pragma unroll 1
     for (uint32_t i = 0; i < limit; i++) {
         if (mbar_try_wait(bar, parity, 20000u)) return true;
         __nanosleep(200);
@@ -89,6 +90,7 @@ __device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_u32(uint32_t bar, uint32_t parity, uint32_t limit = SK_WAIT_LIMIT) {
+#pragma unroll 1
     for (uint32_t i = 0; i < limit; i++) {
         uint32_t ok;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
@@ -159,7 +161,11 @@ constexpr int SK_KEEP = 3;
 // (value, tag) pairs, one 64-bit word each: the reader polls until the tag is the one it expects (the
 // tag names the launch and the phase that writes the value), so no fence, flag or barrier has to
 // order the two sides.  Polls are bounded: after TAG_POLL_LIMIT tries the reader gives up.
-constexpr uint32_t TAG_POLL_LIMIT = 1u << 20;
+constexpr uint32_t TAG_POLL_LIMIT_DEFAULT = 1u << 20;
+// The limit lives in constant memory so that a host can shorten it (l2_options.poll_limit_log2): one value per
+// device and translation unit, set when a launch plan is made.
+static __constant__ uint32_t c_tag_poll_limit = TAG_POLL_LIMIT_DEFAULT;
+#define TAG_POLL_LIMIT c_tag_poll_limit
 
 __device__ __forceinline__ void store_tagged(void* base, size_t index, float v, uint32_t tag) {
     const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
@@ -173,6 +179,7 @@ __device__ __forceinline__ void store_tagged_peer(void* base, size_t index, floa
 // One tagged value; returns false when the poll limit is reached.
 __device__ __forceinline__ bool load_tagged(const void* base, size_t index, uint32_t tag, float& v) {
     const unsigned long long* p = static_cast<const unsigned long long*>(base) + index;
+#pragma unroll 1
     for (uint32_t it = 0; it < TAG_POLL_LIMIT; it++) {
         unsigned long long w;
         asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
@@ -184,6 +191,7 @@ __device__ __forceinline__ bool load_tagged(const void* base, size_t index, uint
 // Eight consecutive tagged values (64 bytes, 64-byte aligned).
 __device__ __forceinline__ bool load_tagged8(const void* base, size_t index, uint32_t tag, float4& v0, float4& v1) {
     const uint4* p = reinterpret_cast<const uint4*>(static_cast<const unsigned long long*>(base) + index);
+#pragma unroll 1
     for (uint32_t it = 0; it < TAG_POLL_LIMIT; it++) {
         uint4 a, b, c, d;
         asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p) : "memory");
@@ -364,6 +372,116 @@ __device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, flo
     }
     if (dbg && threadIdx.x == 0) dbg[2] = clock64();
     return rs / P;
+}
+
+// ---- one-pass staging with one exponent per quantisation group (token kernel) --------------------
+// X[k] = round(x[k] * nw[k] * 2^(26 - E_g)) with E_g the exponent of the largest |x * nw| of group g, so
+// every group uses the full 28 bits and no statistic of the whole vector has to be known before the
+// first digit is written: the vector is read once, a group is finished by the 4 * W lanes that hold it
+// (shuffles only), and the factor 2^-(26 - E_g) goes into the per-(row, group) scale of the GEMV.
+// The sum of squares for the rmsnorm is only needed by the epilogue and is collected on the side.
+//
+// Digits: X is written in balanced base 256, X = sum_j d_j 256^j with -128 <= d_j <= 127, which is two
+// integer operations per value: the bytes of (X + 0x80808080) ^ 0x80808080.  All four are legal s8
+// operands of the integer MMA.
+// digits: [4][in + 16], plane 0 the most significant digit; ss: [G][2] digit sums (256 * S0 + S1,
+// 256 * S2 + S3); pg: [G] the factors.
+struct StageLoad { uint4 q[4]; float4 w0, w1; };
+
+__device__ __forceinline__ void stage_issue(const SkSeg& sg, int blk, StageLoad& L) {
+    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned long long*>(sg.x) + (size_t)blk * 8);
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(L.q[i].x), "=r"(L.q[i].y), "=r"(L.q[i].z), "=r"(L.q[i].w) : "l"(p + i) : "memory");
+    if (sg.nw) {
+        const float4* n4 = reinterpret_cast<const float4*>(sg.nw);
+        L.w0 = __ldg(n4 + 2 * blk);
+        L.w1 = __ldg(n4 + 2 * blk + 1);
+    }
+}
+__device__ __forceinline__ bool stage_tags_ok(const StageLoad& L, uint32_t tag) {
+    return L.q[0].y == tag && L.q[0].w == tag && L.q[1].y == tag && L.q[1].w == tag && L.q[2].y == tag && L.q[2].w == tag && L.q[3].y == tag && L.q[3].w == tag;
+}
+
+template <int W>
+__device__ __noinline__ void stage_groups(const SkSeg& sg, int in, uint8_t* digits, int* ss, float* pg, uint32_t tag, bool want_sq, float* sq_out,
+                                          bool* fail, unsigned long long* stamp = nullptr) {
+    const int nblk = in / 8, stride = in + 16;
+    float sq = 0.f;
+    int blk = threadIdx.x;
+    StageLoad cur, nxt;
+    cur.w0 = cur.w1 = nxt.w0 = nxt.w1 = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (blk < nblk) stage_issue(sg, blk, cur);  // the first block's values and norm weights are on their way together
+#pragma unroll 1
+    for (; (blk & ~31) < nblk; blk += SK_THREADS) {
+        const bool valid = blk < nblk;
+        if (valid && !stage_tags_ok(cur, tag)) {  // not there yet: poll (bounded)
+            uint32_t it = 0;
+#pragma unroll 1
+            do {
+                const float4 w0 = cur.w0, w1 = cur.w1;
+                stage_issue(sg, blk, cur);
+                cur.w0 = w0; cur.w1 = w1;
+            } while (!stage_tags_ok(cur, tag) && ++it < TAG_POLL_LIMIT);
+            if (it >= TAG_POLL_LIMIT) *fail = true;
+        }
+        if (stamp && threadIdx.x == 0 && blk == 0) stamp[21] = clock64();
+        if (blk + SK_THREADS < nblk) stage_issue(sg, blk + SK_THREADS, nxt);  // in flight while this block is turned into digits
+        float v[8] = {__uint_as_float(cur.q[0].x), __uint_as_float(cur.q[0].z), __uint_as_float(cur.q[1].x), __uint_as_float(cur.q[1].z),
+                      __uint_as_float(cur.q[2].x), __uint_as_float(cur.q[2].z), __uint_as_float(cur.q[3].x), __uint_as_float(cur.q[3].z)};
+        if (!valid) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = 0.f;
+        }
+        if (want_sq) sq += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3] + v[4] * v[4] + v[5] * v[5] + v[6] * v[6] + v[7] * v[7];
+        v[0] *= cur.w0.x; v[1] *= cur.w0.y; v[2] *= cur.w0.z; v[3] *= cur.w0.w;
+        v[4] *= cur.w1.x; v[5] *= cur.w1.y; v[6] *= cur.w1.z; v[7] *= cur.w1.w;
+        float mx = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+                         fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
+#pragma unroll
+        for (int o = 1; o < 4 * W; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float P = stage_scale(mx);
+        if (stamp && threadIdx.x == 0 && blk == 0) stamp[22] = clock64() + (P == 1.2345f ? 1 : 0);
+        uint32_t E[8];  // per element: bytes d3, d2, d1, d0 (least significant digit first)
+#pragma unroll
+        for (int j = 0; j < 8; j++) E[j] = ((uint32_t)__float2int_rn(v[j] * P) + 0x80808080u) ^ 0x80808080u;
+        // 4x4 byte transposes: words of one digit for inputs (0,2,4,6) and (1,3,5,7), the order in
+        // which the nibbles of a weight word separate into its low and high halves
+        uint32_t lo[4], hi[4];
+        {
+            const uint32_t a = __byte_perm(E[0], E[2], 0x5140), b2 = __byte_perm(E[0], E[2], 0x7362);
+            const uint32_t c = __byte_perm(E[4], E[6], 0x5140), d = __byte_perm(E[4], E[6], 0x7362);
+            lo[3] = __byte_perm(a, c, 0x5410); lo[2] = __byte_perm(a, c, 0x7632);
+            lo[1] = __byte_perm(b2, d, 0x5410); lo[0] = __byte_perm(b2, d, 0x7632);
+        }
+        {
+            const uint32_t a = __byte_perm(E[1], E[3], 0x5140), b2 = __byte_perm(E[1], E[3], 0x7362);
+            const uint32_t c = __byte_perm(E[5], E[7], 0x5140), d = __byte_perm(E[5], E[7], 0x7362);
+            hi[3] = __byte_perm(a, c, 0x5410); hi[2] = __byte_perm(a, c, 0x7632);
+            hi[1] = __byte_perm(b2, d, 0x5410); hi[0] = __byte_perm(b2, d, 0x7632);
+        }
+        int sum[4];
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            if (valid) *reinterpret_cast<uint2*>(digits + (size_t)p * stride + (size_t)blk * 8) = make_uint2(lo[p], hi[p]);
+            sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
+        }
+        // a group is 4*W consecutive blocks = 4*W consecutive lanes: sum them with shuffles
+        int s01 = 256 * sum[0] + sum[1], s23 = 256 * sum[2] + sum[3];
+#pragma unroll
+        for (int o = 1; o < 4 * W; o <<= 1) {
+            s01 += __shfl_xor_sync(0xffffffffu, s01, o);
+            s23 += __shfl_xor_sync(0xffffffffu, s23, o);
+        }
+        if (valid && (threadIdx.x & (4 * W - 1)) == 0) {
+            const int g = blk / (4 * W);
+            *reinterpret_cast<int2*>(ss + 2 * g) = make_int2(s01, s23);
+            pg[g] = __uint_as_float((254u << 23) - __float_as_uint(P));  // 1 / P, exact
+        }
+        if (stamp && threadIdx.x == 0 && blk == 0) stamp[23] = clock64();
+        cur = nxt;
+    }
+    if (want_sq) *sq_out = sq;
 }
 
 // Asks the L2 to fetch [p, p + bytes) from HBM; nothing waits on it.

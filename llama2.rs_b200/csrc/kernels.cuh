@@ -172,13 +172,15 @@ struct alignas(16) PhaseRec {
     } u;
 };
 
+constexpr int TK_TRACE_W = 32;  // debugging clock stamps per (CTA, phase)
+
 struct TokenParams {
     const PhaseRec* phases;     // device table
     int nphases;
     unsigned* bar;              // bar[0]: arrivals at grid barriers (never reset), bar[32]: launches so far (tag epoch), bar[33]: barriers so far
     int* status;                // set non-zero when a bounded wait gives up
     const Ctl* ctl;             // loop state: the position of this token
-    unsigned long long* trace;  // debug: [grid][nphases][16] stamps, or null
+    unsigned long long* trace;  // debug: [grid][nphases][TK_TRACE_W] stamps, or null
     int chunk, slots;           // ring geometry: unit records per slot, slots
     unsigned fixed_bytes;       // shared memory in front of the ring (digits, sums, scratch of the other phases)
     int skip;                   // debug: stream the weights but skip the GEMV arithmetic (results are wrong)
@@ -189,6 +191,7 @@ struct TokenParams {
 };
 
 cudaError_t launch_token(const TokenParams& tk, int group_size, int attn_groups, int grid, size_t smem, cudaStream_t st);
+cudaError_t token_set_poll_limit(unsigned polls);  // polls of a tagged input before giving up; 0 = default
 cudaError_t token_init(int max_optin);     // max_optin: opt-in shared memory per block of the device
 size_t token_attn_scratch_bytes(int ag);   // shared memory the attention phase needs
 

@@ -15,6 +15,8 @@
 
 using namespace l2;
 
+extern "C" void l2_model_close(l2_model* m);
+
 namespace l2 {
 
 static int dev_alloc(void** p, size_t bytes, std::vector<void*>& allocs, size_t* total = nullptr) {
@@ -151,13 +153,17 @@ static int check_device(int device, int* out_dev, int* sms) {
 }
 
 // Builds the device model from a tensor source.
+// Frees what a partly built model holds when the open fails (device allocations, the stream).
+struct ModelDeleter { void operator()(l2_model* m) const { l2_model_close(m); } };
+
 static int build_model(const Shape& shape, Source& src, const l2_options* opt, l2_model** out) {
-    std::unique_ptr<l2_model> m(new l2_model);
+    std::unique_ptr<l2_model, ModelDeleter> m(new l2_model);
     m->shape = shape;
     if (opt) m->opt = *opt;
     if (int rc = check_device(opt ? opt->device : -1, &m->device, &m->sms)) return rc;
     m->tp_world = m->opt.tp_world > 1 ? m->opt.tp_world : 1;
     m->tp_rank = m->tp_world > 1 ? m->opt.tp_rank : 0;
+    if (m->tp_world > L2_MAX_TP) return fail(L2_EINVAL, "tp_world %d exceeds the %d ranks of one box", m->tp_world, L2_MAX_TP);
     if (m->tp_rank < 0 || m->tp_rank >= m->tp_world) return fail(L2_EINVAL, "tp_rank %d outside 0..%d", m->tp_rank, m->tp_world - 1);
     if (shape.c.n_kv_heads % m->tp_world || (shape.c.dim / m->tp_world) % 16 || (shape.c.hidden_dim / m->tp_world) % 16 || shape.c.hidden_dim % m->tp_world)
         return fail(L2_EINVAL, "tp_world %d does not divide the kv heads / leave whole 16-row tiles", m->tp_world);
@@ -410,17 +416,13 @@ static int plan_token(l2_state* s) {
         const SkLaunch& L = s->plans[which];  // every layer has the same shapes
         int max_g = 0;
         for (int i = 0; i < L.p.njobs; i++) max_g = std::max(max_g, L.p.job[i].G);
-        fixed = std::max(fixed, sk_smem_fixed(L.p.job[0].in, max_g, L.nseg, L.p.ptiles));
+        fixed = std::max(fixed, sk_smem_fixed(L.p.job[0].in, max_g, L.nseg, L.p.ptiles) + (size_t)L.nseg * max_g * 4);  // + one scaling factor per group
     }
     fixed = (fixed + 127) & ~(size_t)127;
     const size_t budget = 222 * 1024;
-    int su = 32;
-    if (const char* e = getenv("L2_SK_CHUNK")) su = std::max(2, std::min(32, atoi(e) & ~1));  // a warp takes one pair per slot
+    const int su = 2 * SK_WARPS;  // unit records per slot fill: every consumer warp takes one pair
     int slots = 0;
-    for (; su >= 2; su /= 2) {
-        if (fixed < budget) slots = (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(c.group_size, su));
-        if (slots >= 2) break;
-    }
+    if (fixed < budget) slots = (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(c.group_size, su));
     if (slots < 2) return fail(L2_EINVAL, "the token kernel needs %zu bytes of shared memory before its weight ring", fixed);
     if (const char* e = getenv("L2_SK_SLOTS")) slots = std::max(2, std::min(slots, atoi(e)));
     s->tk = TokenParams{};
@@ -429,8 +431,13 @@ static int plan_token(l2_state* s) {
     s->tk.fixed_bytes = (unsigned)fixed;
     s->tk.status = &s->ctl->status;
     s->tk.ctl = s->ctl;
-    s->tk.skip = getenv("L2_SK_SKIP") ? 1 : 0;
+    s->tk.skip = (getenv("L2_SK_SKIP") ? 1 : 0) | (getenv("L2_SK_NOCOPY") ? 2 : 0);  // debugging: no arithmetic / no weight copies (results are wrong)
     s->tk_smem = fixed + (size_t)slots * sk_slot_bytes(c.group_size, su);
+    {
+        const int lg = m->opt.poll_limit_log2;
+        if (lg && (lg < 8 || lg > 30)) return fail(L2_EINVAL, "poll_limit_log2 %d outside 8..30", lg);
+        L2_CUDA(token_set_poll_limit(lg ? 1u << lg : 0u));
+    }
     if (int rc = dev_alloc(reinterpret_cast<void**>(&s->tk.bar), 256, s->allocs)) return rc;
     L2_CUDA(cudaMemset(s->tk.bar, 0, 256));
     {   // tagged activations, zeroed once: tag 0 is never expected
@@ -445,6 +452,11 @@ static int plan_token(l2_state* s) {
         if (!pool) return fail(L2_EINVAL, "token kernel: no activation pool");
         unsigned long long** bufs[11] = {&s->t_x, &s->t_xq, &s->t_xk, &s->t_xv, &s->t_q, &s->t_k, &s->t_v, &s->t_att, &s->t_x1, &s->t_x3, &s->t_hb};
         for (int i = 0; i < 11; i++) *bufs[i] = reinterpret_cast<unsigned long long*>(pool + lay.off[i]);
+        // attention: the sequence of a kv head is split over the CTAs (one item per CTA at most); partial results per head and split
+        s->tk_max_split = std::max(1, std::min(32, m->sms / std::max(1, c.n_kv_heads / m->tp_world)));
+        const size_t part_bytes = (size_t)c.n_heads * s->tk_max_split * (HS + 2) * 8;
+        if (int rc = dev_alloc(reinterpret_cast<void**>(&s->t_part), part_bytes, s->allocs)) return rc;
+        L2_CUDA(cudaMemset(s->t_part, 0, part_bytes));
         s->tk.world = m->tp_world;
         s->tk.rank = m->tp_rank;
         for (int r = 0; r < 8; r++) s->tk.pool[r] = r < m->tp_world ? (m->tp_world > 1 ? m->tp_peers[r] : pool) : nullptr;
@@ -512,6 +524,10 @@ static int build_phase_table(l2_state* s, int kind) {
                 a.out = must(tg(a.out));
                 a.in_phase = qkv_phase;
                 a.bcast = direct;
+                a.part = reinterpret_cast<float*>(s->t_part);
+                a.max_split = s->tk_max_split;
+                a.split_min = 64;  // positions a split holds at least: one round of loads of a CTA
+                if (const char* e = getenv("L2_TK_SPLIT_MIN")) a.split_min = std::max(1, atoi(e));  // tuning knob
                 add(PH_ATTN).u.at = a;
             } else if (which == 1) {
                 x_phase = me;  // wo wrote x (+ copies for w1/w3)
@@ -550,7 +566,7 @@ static int enqueue_token(l2_state* s, int kind, cudaStream_t st) {
     TokenParams tk = s->tk;
     tk.phases = s->d_phases[kind];
     tk.nphases = s->n_phases[kind];
-    tk.trace = s->tk_trace && (size_t)m->sms * tk.nphases * 16 <= s->tk_trace_count ? s->tk_trace : nullptr;
+    tk.trace = s->tk_trace && (size_t)m->sms * tk.nphases * TK_TRACE_W <= s->tk_trace_count ? s->tk_trace : nullptr;
     L2_CUDA(launch_token(tk, m->shape.c.group_size, m->shape.attn_groups(), m->sms, s->tk_smem, st));
     return L2_OK;
 }
@@ -757,7 +773,7 @@ extern "C" void l2_model_close(l2_model* m) {
     cudaSetDevice(m->device);
     if (m->gen_state) l2_state_free(m->gen_state);
     for (int r = 0; r < 8; r++)
-        if (m->tp_peers[r] && r != m->tp_rank) cudaIpcCloseMemHandle(m->tp_peers[r]);
+        if (m->tp_peers[r] && r != m->tp_rank && !m->tp_peer_borrowed[r]) cudaIpcCloseMemHandle(m->tp_peers[r]);
     if (m->tp_pool) cudaFree(m->tp_pool);
     tp_disconnect(m);
     free_allocs(m->allocs);
@@ -797,6 +813,22 @@ extern "C" int l2_model_tp_pool_attach(l2_model* m, int rank, const void* handle
         L2_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
         m->tp_peers[rank] = static_cast<char*>(p);
     }
+    bool all = true;
+    for (int r = 0; r < m->tp_world; r++) all = all && m->tp_peers[r];
+    m->tp_direct = all;
+    return L2_OK;
+}
+
+extern "C" size_t l2_model_tp_pool_bytes(const l2_model* m) { return m && m->tp_world > 1 ? tagged_layout(m).total : 0; }
+
+extern "C" int l2_model_tp_pool_attach_ptr(l2_model* m, int rank, void* device_ptr) {
+    clear_error();
+    if (!m || !device_ptr) return fail(L2_EINVAL, "l2_model_tp_pool_attach_ptr: null argument");
+    if (rank < 0 || rank >= m->tp_world || rank == m->tp_rank) return fail(L2_EINVAL, "l2_model_tp_pool_attach_ptr: rank %d is not a peer (0..%d, own rank %d)", rank, m->tp_world - 1, m->tp_rank);
+    if (!m->tp_pool) return fail(L2_EINVAL, "l2_model_tp_pool_attach_ptr: call l2_model_tp_pool_handle first");
+    if (m->tp_peers[rank]) return fail(L2_EINVAL, "l2_model_tp_pool_attach_ptr: rank %d is attached already", rank);
+    m->tp_peers[rank] = static_cast<char*>(device_ptr);
+    m->tp_peer_borrowed[rank] = true;
     bool all = true;
     for (int r = 0; r < m->tp_world; r++) all = all && m->tp_peers[r];
     m->tp_direct = all;
@@ -891,6 +923,7 @@ extern "C" int l2_state_reset(l2_state* s) {
         L2_CUDA(cudaMemsetAsync(s->tk.bar + 33, 0, sizeof(unsigned), m->stream));
     }
     L2_CUDA(cudaStreamSynchronize(m->stream));
+    s->failed_status = 0;
     return L2_OK;
 }
 
@@ -930,11 +963,13 @@ extern "C" int l2_state_read_kv(l2_state* s, int layer, float* key_cache, float*
 static int check_state(l2_model* m, l2_state* s, const char* who) {
     if (!m || !s) return fail(L2_EINVAL, "%s: null handle", who);
     if (s->m != m) return fail(L2_EINVAL, "%s: the state belongs to another model", who);
+    if (s->failed_status) return fail(L2_ESTATUS, "%s: an earlier call on this state ended with device status %d; call l2_state_reset first", who, s->failed_status);
     L2_CUDA(cudaSetDevice(m->device));
     return L2_OK;
 }
 
 static int check_status(l2_state* s);
+static int report_status(l2_state* s);
 
 extern "C" int l2_forward(l2_model* m, l2_state* s, const int32_t* tokens, const int32_t* pos, int B, float* logits) {
     clear_error();
@@ -997,11 +1032,19 @@ static int prefill_async(l2_model* m, l2_state* s, const int32_t* prompt, int n_
     return L2_OK;
 }
 
+// A device-side bounded wait gave up (h_ctl holds the record read back).  The launch left early: the
+// grid-barrier count of the token kernel is uneven and, under tensor parallelism, the ranks' launch
+// counts may differ.  The state refuses further forwards until l2_state_reset.
+static int report_status(l2_state* s) {
+    s->failed_status = s->h_ctl->status;
+    return fail(L2_ESTATUS, "device status %d (a bounded wait on the device gave up); reset the state before using it again", s->h_ctl->status);
+}
+
 // Synchronises the stream and reports a device-side bounded wait that gave up.
 static int check_status(l2_state* s) {
     L2_CUDA(cudaMemcpyAsync(s->h_ctl, s->ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, s->m->stream));
     L2_CUDA(cudaStreamSynchronize(s->m->stream));
-    if (s->h_ctl->status) return fail(L2_ESTATUS, "device status %d", s->h_ctl->status);
+    if (s->h_ctl->status) return report_status(s);
     return L2_OK;
 }
 
@@ -1026,7 +1069,7 @@ extern "C" int l2_decode_step(l2_model* m, l2_state* s, int32_t token, int32_t p
     L2_CUDA(cudaMemcpyAsync(s->h_ctl, s->ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, m->stream));
     if (logits) L2_CUDA(cudaMemcpyAsync(logits, s->logits, sizeof(float) * c.vocab_size, cudaMemcpyDeviceToHost, m->stream));
     L2_CUDA(cudaStreamSynchronize(m->stream));
-    if (s->h_ctl->status) return fail(L2_ESTATUS, "device status %d", s->h_ctl->status);
+    if (s->h_ctl->status) return report_status(s);
     if (next) *next = s->h_ctl->last_next;
     if (rng_seed) *rng_seed = s->h_ctl->rng;
     return L2_OK;
@@ -1054,7 +1097,7 @@ extern "C" int l2_decode_run(l2_model* m, l2_state* s, const int32_t* prompt, in
     if (n && out_tokens) L2_CUDA(cudaMemcpyAsync(out_tokens, s->out_tokens + pos0, sizeof(int) * n, cudaMemcpyDeviceToHost, m->stream));
     L2_CUDA(cudaMemcpyAsync(s->h_ctl, s->ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, m->stream));
     L2_CUDA(cudaStreamSynchronize(m->stream));
-    if (s->h_ctl->status) return fail(L2_ESTATUS, "device status %d", s->h_ctl->status);
+    if (s->h_ctl->status) return report_status(s);
     if (rng_seed) *rng_seed = s->h_ctl->rng;
     return L2_OK;
 }
@@ -1091,6 +1134,7 @@ extern "C" int l2_generate_ids(l2_model* m, const int32_t* prompt, int n_prompt,
             cudaMemcpyAsync(s->h_ctl, s->ctl, sizeof(Ctl), cudaMemcpyDeviceToHost, m->stream);
             cudaEventRecord(e2, m->stream);
             if (cudaStreamSynchronize(m->stream) != cudaSuccess) { rc = fail(L2_ECUDA, "decode failed: %s", cudaGetErrorString(cudaGetLastError())); break; }
+            if (s->h_ctl->status) { rc = report_status(s); break; }  // a bounded wait gave up: the tokens are not valid
             rng = s->h_ctl->rng;
         } else {
             int token = pos0 == 0 ? L2_START : prompt[pos0 - 1];
@@ -1195,7 +1239,20 @@ extern "C" uint64_t l2_projection_bytes(const l2_model* m, int which) {
 
 // ---- C ABI: attention of one position on caller-owned device buffers ------------------------------
 
-static int attention_max_split(int n_kv_heads) { return std::max(1, std::min(32, (2 * 148 + n_kv_heads - 1) / n_kv_heads)); }
+// Splits per kv head of the stand-alone attention entry points: enough (kv head, split) CTAs to cover the
+// SMs of the current device about twice.  The SM count is read once per device.
+int l2::device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+int l2::attention_max_split(int n_kv_heads) { return std::max(1, std::min(32, (2 * device_sm_count() + n_kv_heads - 1) / n_kv_heads)); }
 
 extern "C" int l2_rope_table(int seq_len, float* cos_out, float* sin_out) {
     clear_error();

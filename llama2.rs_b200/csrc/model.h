@@ -42,6 +42,7 @@ struct DevLayer {
 };
 
 constexpr int CTL_RING = 128;
+constexpr int L2_MAX_TP = 8;   // ranks of a tensor-parallel group (the GPUs of one box)
 constexpr int MAX_BATCH = 64;  // tokens of one batched forward (one tcgen05 tile holds 4 digits x 64 tokens)
 
 // Device buffers of the batched forward pass (transformer<B>, B >= 2).
@@ -88,6 +89,7 @@ struct l2_model {
     // pools mapped through CUDA IPC; the first run state of the model works in the pool
     char* tp_pool = nullptr;
     char* tp_peers[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool tp_peer_borrowed[8] = {false, false, false, false, false, false, false, false};  // attached by pointer: not an IPC mapping to close
     bool tp_direct = false;          // every rank's pool is attached
     l2_state* tp_pool_owner = nullptr;
 };
@@ -107,6 +109,7 @@ struct l2_state {
     int* prompt = nullptr;
     int* out_tokens = nullptr;
     int max_split = 1;
+    int failed_status = 0;              // device status of a launch that gave up; cleared by l2_state_reset
     std::vector<l2::SkLaunch> plans;     // [layer][4] GEMV launches, planned once
     l2::SkParams* d_plans = nullptr;     // their parameter records on the device
     l2::BatchBuffers* batch = nullptr;   // activations of the batched forward, allocated on first use
@@ -117,6 +120,8 @@ struct l2_state {
     // activations of the token kernel as (value, tag) pairs, 8 bytes per element (see token_kernel.cu)
     unsigned long long *t_x = nullptr, *t_xq = nullptr, *t_xk = nullptr, *t_xv = nullptr, *t_q = nullptr, *t_k = nullptr, *t_v = nullptr;
     unsigned long long *t_att = nullptr, *t_x1 = nullptr, *t_x3 = nullptr, *t_hb = nullptr;
+    unsigned long long* t_part = nullptr;  // [n_heads][tk_max_split][HS + 2] partial attention results of the sequence splits, tagged
+    int tk_max_split = 1;
     unsigned long long* tk_trace = nullptr;
     size_t tk_trace_count = 0;
     cudaGraphExec_t graphs[l2::G_COUNT] = {nullptr, nullptr, nullptr, nullptr};
@@ -145,6 +150,8 @@ int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vecto
 void launch_permute(const float* x, const int* perm, float* xp, int n, cudaStream_t st);
 int check_attention_args(int n_heads, int n_kv_heads, int pos, const void* q, const void* k, const void* v, const void* kc,
                          const void* vc, const void* rc, const void* rs, const void* out);
+int device_sm_count();
+int attention_max_split(int n_kv_heads);
 int run_gemv_single(const DevQ& q, const float* xp, float* y, int sms, SkParams* d_plan, cudaStream_t st);
 int sk_plan(SkLaunch& L, int sms);
 void sk_prefetch_next(SkLaunch& L, const DevQ& q);

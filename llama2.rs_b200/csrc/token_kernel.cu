@@ -30,8 +30,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 #ifdef L2_TK_TRACE
-#define TK_STAMP_NS(p, i) do { if (tk.trace && threadIdx.x == 0) tk.trace[((size_t)blockIdx.x * tk.nphases + (p)) * 16 + (i)] = global_ns(); } while (0)
-#define TK_STAMP(p, i) do { if (tk.trace && threadIdx.x == 0) tk.trace[((size_t)blockIdx.x * tk.nphases + (p)) * 16 + (i)] = clock64(); } while (0)
+#define TK_STAMP_NS(p, i) do { if (tk.trace && threadIdx.x == 0) tk.trace[((size_t)blockIdx.x * tk.nphases + (p)) * TK_TRACE_W + (i)] = global_ns(); } while (0)
+#define TK_STAMP(p, i) do { if (tk.trace && threadIdx.x == 0) tk.trace[((size_t)blockIdx.x * tk.nphases + (p)) * TK_TRACE_W + (i)] = clock64(); } while (0)
 #else
 #define TK_STAMP_NS(p, i) do { } while (0)
 #define TK_STAMP(p, i) do { } while (0)
@@ -40,6 +40,12 @@ __device__ __forceinline__ unsigned long long global_ns() {
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float tk_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
 
@@ -96,13 +102,14 @@ __device__ __forceinline__ void prefetch_line_l2(const void* p) { asm volatile("
 // the L2 and the latency-critical loads of a phase (its input vector, the K/V rows) queue behind
 // whatever has been requested ahead.
 template <int W>
-__device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const Ring& R, uint32_t& kfill) {
+__device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const Ring& R, uint32_t& kfill, unsigned long long* pstamp = nullptr) {
     constexpr uint32_t UB = 256u * W + 80u;
     const int lane = threadIdx.x & 31;
     const CtaRange c = sk_cta_range(P);
     const SkJob& J = P.job[c.ji];
     const int G = J.G, n = c.nt * NSEG * G;
-    const int nslots = (n + R.SU - 1) / R.SU;
+    constexpr int SU = 2 * SK_WARPS;
+    const int nslots = (n + SU - 1) / SU;
     struct Cur { int tl, seg, g; };
     // visits the runs of records (contiguous in memory) that the next `count` units consist of
     auto walk = [&](Cur& cu, int count, auto&& visit) {
@@ -117,28 +124,44 @@ __device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const
         }
     };
     Cur cf{0, 0, 0};
+    unsigned long long waited = 0;
+    if (pstamp && lane == 0) pstamp[10] = clock64();
+    // kfill: slot of the next fill in the low half, its round (how often the ring has wrapped) in the high half
+    uint32_t slot = kfill & 0xFFFFu, round = kfill >> 16;
+#pragma unroll 1
     for (int k = 0; k < nslots; k++) {
-        const uint32_t f = kfill + (uint32_t)k;
-        const int slot = (int)(f % (uint32_t)R.NS);
         int good = 1;
+        const unsigned long long w0 = pstamp ? clock64() : 0;
         if (lane == 0) {
-            if (f >= (uint32_t)R.NS && !mbar_wait_u32(R.empty + 8u * slot, (f / (uint32_t)R.NS - 1u) & 1u)) {
-                ring_abort(R, 1002);
-                good = 0;
+            if (round > 0) {  // in short pieces: an abort raised by the consumers is seen within a millisecond
+                bool free_now = false;
+#pragma unroll 1
+                for (uint32_t piece = 0; piece < SK_WAIT_LIMIT / 32u && !free_now && !ring_aborted(R); piece++)
+                    free_now = mbar_wait_u32(R.empty + 8u * slot, (round - 1u) & 1u, 32u);
+                if (!free_now) {
+                    if (!ring_aborted(R)) ring_abort(R, 1002);
+                    good = 0;
+                }
             }
             if (ring_aborted(R)) good = 0;
         }
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) return false;
-        const int left = min(R.SU, n - k * R.SU);
-        if (lane == 0) mbar_expect_tx_u32(R.full + 8u * slot, (uint32_t)left * UB);
-        uint32_t dst = R.base + (uint32_t)slot * R.slot_bytes;
-        walk(cf, left, [&](const uint32_t* src, uint32_t bytes) {
-            if (lane == 0) bulk_g2s_u32(dst, src, bytes, R.full + 8u * slot);
-            dst += bytes;
-        });
+        const int left = min(SU, n - k * SU);
+        if (pstamp && lane == 0) { waited += clock64() - w0; if (k == 0) pstamp[11] = clock64(); pstamp[12] = clock64(); pstamp[13] = waited; }
+        if (R.skip & 2) {  // debug: no copies at all, the consumers multiply whatever the slot holds
+            if (lane == 0) mbar_arrive_u32(R.full + 8u * slot);
+        } else {
+            if (lane == 0) mbar_expect_tx_u32(R.full + 8u * slot, (uint32_t)left * UB);
+            uint32_t dst = R.base + slot * R.slot_bytes;
+            walk(cf, left, [&](const uint32_t* src, uint32_t bytes) {
+                if (lane == 0) bulk_g2s_u32(dst, src, bytes, R.full + 8u * slot);
+                dst += bytes;
+            });
+        }
+        if (++slot == (uint32_t)R.NS) { slot = 0; round++; }
     }
-    kfill += (uint32_t)nslots;
+    kfill = slot | (round << 16);
     return true;
 }
 
@@ -163,96 +186,58 @@ __device__ __forceinline__ void warm_operands(const SkParams& P, int NSEG) {
     }
 }
 
-// Producer warp, ahead of the consumers: brings the K/V rows this CTA will read in an attention phase
-// (the same item split as attn_phase) and the output positions of its heads into the L2.  These are
-// real loads, not prefetch hints: hints were found to leave the rows in HBM, and the attention phase
-// has nothing to hide that latency behind.  The values are folded into a word that is stored only
-// if it has a value it cannot have.
-__device__ __forceinline__ void warm_attention(const AttnParams& p, int pos_now, int* sink) {
-    const int lane = threadIdx.x & 31;
-    const int pos = p.pos_fixed >= 0 ? p.pos_fixed : pos_now;
-    const int T = pos + 1;
-    const int nkv = p.n_kv_local > 0 ? p.n_kv_local : p.n_kv_heads;
-    int nsplit = (T + 255) / 256;
-    nsplit = min(nsplit, min(p.max_split, max(1, (int)gridDim.x / nkv)));
-    const int chunk = (T + nsplit - 1) / nsplit;
-    nsplit = (T + chunk - 1) / chunk;
-    const int KV = p.n_kv_heads * HS;
-    float fold = 0.f;
-    for (int item = blockIdx.x; item < nkv * nsplit; item += gridDim.x) {
-        const int kvh = item % nkv + p.kvh0, split = item / nkv;
-        const int t0 = split * chunk, t1 = min(pos, t0 + chunk);  // row `pos` is written by the phase itself
-        const float4* kc4 = reinterpret_cast<const float4*>(p.kc) + (size_t)kvh * (HS / 4) + lane;
-        const float4* vc4 = reinterpret_cast<const float4*>(p.vc) + (size_t)kvh * (HS / 4) + lane;
-        const size_t rs = (size_t)KV / 4;
-        for (int tb = t0; tb < t1; tb += 8) {
-            float4 a[8], b[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const int tt = min(tb + u, t1 - 1);
-                a[u] = __ldcg(kc4 + (size_t)tt * rs);
-                b[u] = __ldcg(vc4 + (size_t)tt * rs);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; u++) fold += a[u].x + b[u].x;
-        }
-        if (p.oidx && split == 0) {  // output positions of the group's heads: ag * 128 indices
-            for (int i = lane; i < p.ag * (HS / 4); i += 32) {
-                const int4 v = __ldg(reinterpret_cast<const int4*>(p.oidx + (size_t)kvh * p.ag * HS) + i);
-                fold += (float)v.x;
-            }
-        }
-    }
-    if (fold == 1.2345678e38f && sink) *sink = 1;  // never true in practice; keeps the loads alive
-}
-
 // Consumer side of one GEMV phase: stage the digits, multiply, reduce, epilogue.  Returns false
-// when a wait gave up.  `kbase` is the number of slot fills consumed before this phase.
-template <int W, int NSEG>
-__device__ __forceinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P, uint8_t* smem, const Ring& R, float* red, float* oscale,
-                                           uint32_t& kbase, unsigned long long* stamp, uint32_t tagbase, int phase) {
+// when a wait gave up.  `kbase` is the number of slot fills consumed before this phase.  nseg = 2
+// pairs w1 with w3 (SwiGLU).  One copy of this code serves every GEMV phase of the token (the kernel
+// runs each phase's code once per layer, so what is not shared is fetched from the L2 every time:
+// the instruction cache of an SM holds far less than an unrolled copy per phase type would need).
+template <int W>
+__device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P, const int nseg, uint8_t* smem, const Ring& R, float* red, float* oscale,
+                                        uint32_t& kbase, unsigned long long* stamp, uint32_t tagbase, int phase) {
     constexpr int GS = 32 * W;
-    constexpr int ROWS = 16 * NSEG;
     constexpr uint32_t UB = 256u * W + 80u;
+    const int ROWS = 16 * nseg;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const CtaRange cr = sk_cta_range(P);
     const SkJob& J = P.job[cr.ji];
-    const int G = J.G, Gs = NSEG * G, nt = cr.nt, tau_first = cr.tau_first;
+    const int G = J.G, Gs = nseg * G, nt = cr.nt, tau_first = cr.tau_first;
     const int n = nt * Gs;
-    const int SU = R.SU, NS = R.NS;
+    constexpr int SU = 2 * SK_WARPS;  // units per slot fill: a pair per warp
+    const int NS = R.NS;
     const int nslots = (n + SU - 1) / SU;
 
     const int dstride = J.in + 16;
-    uint8_t* digits = smem;                                               // [NSEG][4][in + 16]
-    int* ss = reinterpret_cast<int*>(smem + (size_t)NSEG * 4 * dstride);   // [NSEG][G][2]
-    float* partial = reinterpret_cast<float*>(ss + NSEG * G * 2);         // [nt][SK_WARPS][ROWS]
+    uint8_t* digits = smem;                                              // [nseg][4][in + 16]
+    int* ss = reinterpret_cast<int*>(smem + (size_t)nseg * 4 * dstride);  // [nseg][G][2]
+    float* pg = reinterpret_cast<float*>(ss + Gs * 2);                   // [nseg][G] 2^-(26 - E_g)
+    float* partial = pg + Gs;                                            // [nt][SK_WARPS][ROWS]
 
     for (int i = threadIdx.x; i < nt * SK_WARPS * ROWS; i += SK_THREADS) partial[i] = 0.f;
     bool stage_failed = false;  // a poll for a tagged input gave up
-    if (n > 0) {  // the first barrier inside also orders the zeroing of `partial`
-        if (NSEG == 2 && J.in <= 2 * 8 * SK_THREADS) {
-            // w1 and w3 read the same x, each in its own K order: one pass over the statistics
-            const float f = stage_digits_pair<W>(J.seg[0], J.seg[NSEG - 1], J.in, P.eps, digits, digits + (size_t)4 * dstride, ss, ss + G * 2, red,
-                                                 stamp ? stamp + 10 : nullptr, tagbase | (uint32_t)J.in_phase[0], &stage_failed);
-            if (threadIdx.x == 0) oscale[0] = oscale[1] = f;
-        } else {
-#pragma unroll
-            for (int s = 0; s < NSEG; s++) {
-                const float f = stage_digits<W>(J.seg[s], J.in, P.eps, digits + (size_t)s * 4 * dstride, ss + s * G * 2, red,
-                                                stamp ? stamp + 10 : nullptr, tagbase | (uint32_t)J.in_phase[s], &stage_failed);
-                if (threadIdx.x == 0) oscale[s] = f;
-            }
-        }
+    float sq = 0.f;
+    if (stamp && threadIdx.x == 0) stamp[16] = clock64();
+    if (n > 0) {
+        // w1 and w3 read the same x, each in its own K order: the sum of squares is taken from the first
+        for (int s = 0; s < nseg; s++)
+            stage_groups<W>(J.seg[s], J.in, digits + (size_t)s * 4 * dstride, ss + s * G * 2, pg + s * G, tagbase | (uint32_t)J.in_phase[s], s == 0, &sq,
+                            &stage_failed, s == 0 ? stamp : nullptr);
+        if (stamp && threadIdx.x == 0) stamp[17] = clock64();
+        sq = tk_warp_sum(sq);
+        if (lane == 0) red[warp] = sq;
     }
     if (stage_failed) ring_abort(R, 1010);
-    consumer_sync();
+    consumer_sync();  // digits, sums and factors are in place; so are the zeroed tile sums
+    if (warp == 0) {  // rmsnorm factor of the input (src/models.rs:58-60), read by the epilogue; the digit scaling is already in the sums
+        float total = tk_warp_sum(lane < SK_WARPS ? red[lane] : 0.f);
+        if (lane == 0) oscale[0] = J.seg[0].nw ? 1.0f / sqrtf(total / (float)J.in + P.eps) : 1.0f;
+    }
     if (stamp && threadIdx.x == 0) stamp[1] = clock64();
 
     // Epilogue operands of this warp's first tile that are known long before the epilogue (the scatter
     // positions, and the residual value, written phases ago): requested now, so that their trip to the
     // L2 overlaps the main loop.
     const int e_row = (tau_first + warp) * 16 + (lane & 15);
-    const bool e_pre = NSEG == 1 && warp < nt && lane < 16 && e_row < J.rows && J.epi == EPI_RESID;
+    const bool e_pre = nseg == 1 && warp < nt && lane < 16 && e_row < J.rows && J.epi == EPI_RESID;
     int e_idx[3] = {0, 0, 0};
     unsigned long long e_res = 0;
     if (e_pre) {
@@ -264,26 +249,25 @@ __device__ __forceinline__ bool gemv_phase(const TokenParams& tk, const SkParams
 
     // ---- main loop.  In every slot fill this warp owns units 2*warp and 2*warp + 1.  With four warps
     // per scheduler the loop lives on instruction count and on the length of its dependent chain, so
-    //  * the common case (a full slot: every warp has its pair) is straight-line code without
-    //    data-dependent branches: all lanes run the scale / zero-point step (lanes t >= 2 hold the
-    //    unused MMA columns and are ignored when the sums are flushed), lanes r >= 4 read their digits
-    //    from a block of zeros instead of skipping the load;
-    //  * tile and group are carried from fill to fill instead of being recomputed;
-    //  * the loop is software-pipelined by hand: the MMAs of the current pair are issued, then the
-    //    scale / zero-point step of the previous pair runs while they are in flight, and only then is
-    //    the previous slot handed back to the producer.
+    //  * it is straight-line code without data-dependent branches: all lanes run the scale / zero-point
+    //    step (lanes t >= 2 hold the unused MMA columns and are ignored when the sums are flushed), lanes
+    //    r >= 4 read their digits from a block of zeros instead of skipping the load; in the last,
+    //    partial fill of a phase the units beyond the end are multiplied all the same (the slot holds
+    //    older records there) and only their sums are left out;
+    //  * tile and group are carried from fill to fill instead of being recomputed.
     const int r = lane >> 2, t = lane & 3;
     float tot0 = 0.f, tot1 = 0.f;
-    int cur_key = -1;  // 2 * tile + segment the row sums belong to
+    int cur_key = -1;  // nseg * tile + segment the row sums belong to
     bool ok = true;
     auto flush = [&]() {
         if (cur_key >= 0) {
-            // lanes t = 0 hold digits 0,1 (weight 2^14 relative to digits 2,3 held by lanes t = 1)
-            float a = t == 0 ? tot0 * 16384.0f : tot0, b = t == 0 ? tot1 * 16384.0f : tot1;
+            // lanes t = 0 hold digits 0,1 (weight 2^16 relative to digits 2,3 held by lanes t = 1)
+            float a = t == 0 ? tot0 * 65536.0f : tot0, b = t == 0 ? tot1 * 65536.0f : tot1;
             a += __shfl_xor_sync(0xffffffffu, a, 1);
             b += __shfl_xor_sync(0xffffffffu, b, 1);
             if (t == 0) {
-                float* dst = partial + ((size_t)(cur_key >> 1) * SK_WARPS + warp) * ROWS + (cur_key & 1) * 16;
+                const int tl = nseg == 2 ? cur_key >> 1 : cur_key, sg = nseg == 2 ? cur_key & 1 : 0;
+                float* dst = partial + ((size_t)tl * SK_WARPS + warp) * ROWS + sg * 16;
                 dst[r] = a;
                 dst[r + 8] = b;
             }
@@ -295,15 +279,16 @@ __device__ __forceinline__ bool gemv_phase(const TokenParams& tk, const SkParams
     const uint32_t ring_a = R.base + (uint32_t)(2 * warp) * UB;   // this warp's pair inside slot 0
     const uint32_t full_a = R.full, empty_a = R.empty;
     const uint32_t ss_a = smem_u32(ss) + 4u * (uint32_t)(t & 1);
+    const uint32_t pg_a = smem_u32(pg);
     // this lane's digits of the group at position gg; lanes r >= 4 (MMA columns 4..7) read zeros
     const uint32_t dg_a = r < 4 ? smem_u32(digits) + (uint32_t)(r * dstride + t * (8 * W)) : R.zeros;
     const uint32_t dmul = r < 4 ? 1u : 0u;
     constexpr uint32_t META = 256u * W;  // scales, then the two zero-point words
     auto digits_of = [&](int gg) {
-        const int seg = NSEG == 2 && gg >= G ? 1 : 0;
+        const int seg = gg >= G ? 1 : 0;
         return dg_a + (uint32_t)(seg * 4 * dstride + (gg - seg * G) * GS) * dmul;
     };
-    auto key_of = [&](int tl, int gg) { return 2 * tl + (NSEG == 2 && gg >= G ? 1 : 0); };
+    auto key_of = [&](int tl, int gg) { return nseg == 2 ? 2 * tl + (gg >= G ? 1 : 0) : tl; };
     struct Unit { uint32_t a[W], b[W], d[2 * W]; };
     auto unit_load = [&](uint32_t rec, uint32_t dg, Unit& u) {
         if constexpr (W == 4) {
@@ -323,37 +308,63 @@ __device__ __forceinline__ bool gemv_phase(const TokenParams& tk, const SkParams
         }
     };
     constexpr uint32_t M = 0x0F0F0F0Fu;
-    auto unit_mma = [&](const Unit& u, int (&c)[4]) {
-        mma_u8s8_first(c, u.a[0] & M, u.b[0] & M, (u.a[0] >> 4) & M, (u.b[0] >> 4) & M, u.d[0], u.d[1]);
-#pragma unroll
-        for (int i = 1; i < W; i++) mma_u8s8(c, u.a[i] & M, u.b[i] & M, (u.a[i] >> 4) & M, (u.b[i] >> 4) & M, u.d[2 * i], u.d[2 * i + 1]);
+    // The MMAs of the two units of a pair are issued as independent instructions, back to back: on this
+    // part an integer mma.sync that depends on the previous one of its warp (or that follows another
+    // warp's) occupies the tensor pipe about four times as long as one that follows an independent one
+    // of the same warp.  Even and odd K steps of a unit therefore have their own accumulators.
+    auto mma_step = [&](const Unit& u, int i, int (&c)[4], bool first) {
+        if (first) mma_u8s8_first(c, u.a[i] & M, u.b[i] & M, (u.a[i] >> 4) & M, (u.b[i] >> 4) & M, u.d[2 * i], u.d[2 * i + 1]);
+        else mma_u8s8(c, u.a[i] & M, u.b[i] & M, (u.a[i] >> 4) & M, (u.b[i] >> 4) & M, u.d[2 * i], u.d[2 * i + 1]);
     };
-    struct Meta { uint32_t s0, s1, sv; uint2 zz; };
+    auto pair_mma = [&](const Unit& u0, const Unit& u1, int (&c0)[4], int (&c1)[4]) {
+        if constexpr (W == 1) {
+            mma_step(u0, 0, c0, true);
+            mma_step(u1, 0, c1, true);
+        } else {
+            int e0[4], e1[4];  // odd steps
+            mma_step(u0, 0, c0, true);
+            mma_step(u0, 1, e0, true);
+            mma_step(u1, 0, c1, true);
+            mma_step(u1, 1, e1, true);
+#pragma unroll
+            for (int i = 2; i < W; i += 2) {
+                mma_step(u0, i, c0, false);
+                mma_step(u0, i + 1, e0, false);
+                mma_step(u1, i, c1, false);
+                mma_step(u1, i + 1, e1, false);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) { c0[j] += e0[j]; c1[j] += e1[j]; }
+        }
+    };
+    struct Meta { uint32_t s0, s1, sv, pf; uint2 zz; };
     auto meta_load = [&](uint32_t rec, int gg, Meta& mt) {
         mt.s0 = lds32(rec + META + 4 * r);
         mt.s1 = lds32(rec + META + 32 + 4 * r);
         mt.zz = lds64(rec + META + 64);
         mt.sv = lds32(ss_a + 8u * (uint32_t)gg);
+        mt.pf = lds32(pg_a + 4u * (uint32_t)gg);
     };
     // scale, zero point and digit sums of one finished unit (exact integers up to the final FMA)
     auto unit_finish = [&](const Meta& mt, int key, const int (&c)[4]) {
         if (key != cur_key) { flush(); cur_key = key; }  // warp-uniform
         const int z0 = (int)((mt.zz.x >> zshift) & 15u) + 1, z1 = (int)((mt.zz.y >> zshift) & 15u) + 1;  // src/gptq.rs:148
         const int sv = (int)mt.sv;
-        tot0 = fmaf(__uint_as_float(mt.s0), (float)(c[0] * 128 + c[1] - z0 * sv), tot0);
-        tot1 = fmaf(__uint_as_float(mt.s1), (float)(c[2] * 128 + c[3] - z1 * sv), tot1);
-    };
-    auto release = [&](uint32_t slot) {
-        __syncwarp();  // every lane has read the slot
-        if (lane == 0) mbar_arrive_u32(empty_a + 8u * slot);
+        const float pf = __uint_as_float(mt.pf);  // a power of two: the products below are exact scalings
+        tot0 = fmaf(__uint_as_float(mt.s0) * pf, (float)(c[0] * 256 + c[1] - z0 * sv), tot0);
+        tot1 = fmaf(__uint_as_float(mt.s1) * pf, (float)(c[2] * 256 + c[3] - z1 * sv), tot1);
     };
     // position of this warp's first unit of the current fill; advanced by SU units per fill
-    int tl0 = (2 * warp) / Gs, gg0 = (2 * warp) % Gs;
-    uint32_t fslot = kbase % (uint32_t)NS, fpar = (kbase / (uint32_t)NS) & 1u;  // slot and parity of the next fill
+    int tl0 = 0, gg0 = 2 * warp;
+    while (gg0 >= Gs) { gg0 -= Gs; tl0++; }
+    uint32_t fslot = kbase & 0xFFFFu, fpar = kbase >> 16;  // slot and parity of the next fill, carried from phase to phase
+#pragma unroll 1
     for (int k = 0; k < nslots; k++) {
         const uint32_t slot = fslot;
-        const int m = min(SU, n - k * SU);
+        const int m = n - k * SU;  // units of this fill (all of them valid if >= SU)
+        const unsigned long long cw0 = stamp ? clock64() : 0;
         bool got = mbar_try_wait_u32(full_a + 8u * slot, fpar);
+        if (stamp && threadIdx.x == 0 && !got) stamp[15] += 1;
         if (!__all_sync(0xffffffffu, got)) {  // not there yet: the bounded wait
             got = !ring_aborted(R) && mbar_wait_u32(full_a + 8u * slot, fpar);
             if (!__all_sync(0xffffffffu, got)) {
@@ -362,100 +373,80 @@ __device__ __forceinline__ bool gemv_phase(const TokenParams& tk, const SkParams
                 break;
             }
         }
-        if (!R.skip) {
+        if (stamp && threadIdx.x == 0) stamp[14] += clock64() - cw0;
+        if (!(R.skip & 1)) {
             const uint32_t rec0 = ring_a + slot * R.slot_bytes;
             int tl1 = tl0, gg1 = gg0 + 1;
             if (gg1 == Gs) { gg1 = 0; tl1++; }
             int c0[4], c1[4];
-            if (m == 2 * SK_WARPS) {  // a full slot: straight-line, all loads first
-                Unit u0, u1;
-                Meta m0, m1;
-                unit_load(rec0, digits_of(gg0), u0);
-                unit_load(rec0 + UB, digits_of(gg1), u1);
-                meta_load(rec0, gg0, m0);
-                meta_load(rec0 + UB, gg1, m1);
-                unit_mma(u0, c0);
-                unit_mma(u1, c1);
-                unit_finish(m0, key_of(tl0, gg0), c0);
-                unit_finish(m1, key_of(tl1, gg1), c1);
-            } else {  // the last, partial fill
-                const int j = 2 * warp;
-                if (j < m) {
-                    Unit u; Meta mt;
-                    unit_load(rec0, digits_of(gg0), u);
-                    meta_load(rec0, gg0, mt);
-                    unit_mma(u, c0);
-                    unit_finish(mt, key_of(tl0, gg0), c0);
-                }
-                if (j + 1 < m) {
-                    Unit u; Meta mt;
-                    unit_load(rec0 + UB, digits_of(gg1), u);
-                    meta_load(rec0 + UB, gg1, mt);
-                    unit_mma(u, c1);
-                    unit_finish(mt, key_of(tl1, gg1), c1);
-                }
-            }
+            Unit u0, u1;
+            Meta m0, m1;
+            unit_load(rec0, digits_of(gg0), u0);
+            unit_load(rec0 + UB, digits_of(gg1), u1);
+            meta_load(rec0, gg0, m0);
+            meta_load(rec0 + UB, gg1, m1);
+            pair_mma(u0, u1, c0, c1);
+            if (2 * warp < m) unit_finish(m0, key_of(tl0, gg0), c0);
+            if (2 * warp + 1 < m) unit_finish(m1, key_of(tl1, gg1), c1);
         }
-        release(slot);
+        __syncwarp();  // every lane has read the slot
+        if (lane == 0) mbar_arrive_u32(empty_a + 8u * slot);
         gg0 += SU;
         while (gg0 >= Gs) { gg0 -= Gs; tl0++; }
         if (++fslot == (uint32_t)NS) { fslot = 0; fpar ^= 1u; }
     }
-    kbase += (uint32_t)nslots;
+    kbase = fslot | (fpar << 16);
     flush();
     if (stamp && threadIdx.x == 0) { stamp[2] = clock64(); stamp[9] = (unsigned long long)nslots; }
     consumer_sync();
+    if (stamp && threadIdx.x == 0) stamp[18] = clock64();
     if (ring_aborted(R)) return false;
 
+    const float rs = oscale[0];
     // Results leave as (value, tag) pairs: whoever needs them polls for the tag of this phase.
     const uint32_t out_tag = tagbase | (uint32_t)phase;
     bool fine = true;
+#pragma unroll 1
     for (int tl = warp; tl < nt; tl += SK_WARPS) {
-        const int tau = tau_first + tl;
         float v = 0.f;
         if (lane < ROWS)
             for (int w = 0; w < SK_WARPS; w++) v += partial[((size_t)tl * SK_WARPS + w) * ROWS + lane];
-        const float y = v * oscale[lane >> 4 & (NSEG - 1)];
-        const int row = tau * 16 + (lane & 15);
-        if (NSEG == 2) {  // SwiGLU (src/models.rs:92-98)
+        float y = v * rs;
+        if (stamp && threadIdx.x == 0) stamp[19] = clock64() + (y == 1.2345f ? 1 : 0);
+        const int row = (tau_first + tl) * 16 + (lane & 15);
+        if (nseg == 2) {  // SwiGLU (src/models.rs:92-98)
             const float y3 = __shfl_down_sync(0xffffffffu, y, 16);
-            if (lane < 16 && row < J.rows) {
-                const float sg = y * (1.0f / (1.0f + expf(-y)));
-                store_tagged_all(tk, J.bcast, J.out, row, sg * y3, out_tag);
+            y = y * (1.0f / (1.0f + expf(-y))) * y3;
+        }
+        if (lane >= 16 || row >= J.rows) continue;
+        int ndst = 1;
+        const bool pre = e_pre && tl == warp;
+        int idx0 = e_idx[0], idx1 = e_idx[1], idx2 = e_idx[2];
+        if (nseg == 1 && J.epi == EPI_RESID) {  // residual add (src/models.rs:47-51) + copies in the next consumers' K orders
+            ndst += J.nscatter;
+            if (!pre) {
+                if (J.nscatter > 0) idx0 = __ldg(J.sidx[0] + row);
+                if (J.nscatter > 1) idx1 = __ldg(J.sidx[1] + row);
+                if (J.nscatter > 2) idx2 = __ldg(J.sidx[2] + row);
             }
-        } else if (lane < 16 && row < J.rows) {
-            if (J.epi == EPI_STORE) {
-                store_tagged_all(tk, J.bcast, J.out, row, y, out_tag);
-            } else {  // residual add (src/models.rs:47-51) + copies in the next consumers' K orders
-                const bool pre = e_pre && tl == warp;
-                int idx[3] = {e_idx[0], e_idx[1], e_idx[2]};
-                if (!pre) {
-#pragma unroll
-                    for (int s = 0; s < 3; s++)
-                        if (s < J.nscatter) idx[s] = __ldg(J.sidx[s] + row);
-                }
-                float res = __uint_as_float((uint32_t)e_res);
-                if (!pre || (uint32_t)(e_res >> 32) != (tagbase | (uint32_t)J.resid_phase))  // not the early copy: poll
-                    fine = load_tagged(J.out, row, tagbase | (uint32_t)J.resid_phase, res) && fine;
-                const float xv = res + y;
-                store_tagged_all(tk, J.bcast, J.out, row, xv, out_tag);
-#pragma unroll
-                for (int s = 0; s < 3; s++)
-                    if (s < J.nscatter) store_tagged_all(tk, J.bcast, J.sdst[s], idx[s], xv, out_tag);
-            }
+            float res = __uint_as_float((uint32_t)e_res);
+            if (!pre || (uint32_t)(e_res >> 32) != (tagbase | (uint32_t)J.resid_phase))  // not the early copy: poll
+                fine = load_tagged(J.out, row, tagbase | (uint32_t)J.resid_phase, res) && fine;
+            y += res;
+        }
+#pragma unroll 1
+        for (int d = 0; d < ndst; d++) {
+            float* base = d == 0 ? J.out : J.sdst[d - 1];
+            const int at = d == 0 ? row : d == 1 ? idx0 : d == 2 ? idx1 : idx2;
+            store_tagged_all(tk, J.bcast, base, at, y, out_tag);
         }
     }
+    if (stamp && threadIdx.x == 0) stamp[20] = clock64();
     if (!fine) ring_abort(R, 1008);
     return true;
 }
 
 // ---- the other phases ------------------------------------------------------------------------------
-
-__device__ __forceinline__ float tk_warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
 
 __device__ __forceinline__ void embed_phase(const EmbedParams& p, uint32_t out_tag) {
     const int pos = p.ctl->pos;
@@ -469,14 +460,84 @@ __device__ __forceinline__ void embed_phase(const EmbedParams& p, uint32_t out_t
     }
 }
 
-// RoPE + KV append + attention (src/models.rs:100-176, 228-256).  A CTA (16 consumer warps) takes
-// (kv head, sequence split) items; short sequences are not split at all, so that the common case has
-// no cross-CTA merge; otherwise the CTA that finishes the last split of a kv head merges the splits
-// in split order.
+// RoPE + KV append + attention (src/models.rs:100-176, 228-256).  A CTA (16 consumer warps) takes one
+// (kv head, sequence split) item; the sequence is split over as many CTAs as there are (so that a CTA
+// reads its K/V rows in one or two rounds of loads, all requested before q has arrived), and the partial
+// results (unnormalised sums with their maximum and denominator) travel as tagged values to the CTA
+// that merges the head's splits in split order.  A short sequence is not split: no second exchange.
 constexpr int TK_ATT_WARPS = SK_WARPS;
 
 __host__ __device__ constexpr size_t tk_att_bytes(int ag) {
-    return ((size_t)ag * HS + (size_t)TK_ATT_WARPS * ag * HS + 2 * (size_t)TK_ATT_WARPS * ag + 4 + 2 * HS + ag) * 4;
+    const size_t work = ((size_t)ag * HS + (size_t)TK_ATT_WARPS * ag * HS + 2 * (size_t)TK_ATT_WARPS * ag + 4 + 2 * HS + ag) * 4;
+    const size_t merge = (size_t)32 * (HS + 2) * 4;  // up to 32 splits of one head
+    return work > merge ? work : merge;
+}
+
+struct AttSplit { int nsplit, chunk; };
+// How the T positions of a token are cut: rows_min positions per split at least, no more splits than the
+// CTAs can take in one round (or than the partial buffer holds).
+__device__ __forceinline__ AttSplit att_split(const AttnParams& p, int T, int nkv) {
+    AttSplit a;
+    int ns = T / max(1, p.split_min);
+    ns = max(1, min(ns, min(p.max_split, max(1, (int)gridDim.x / nkv))));
+    a.chunk = (T + ns - 1) / ns;
+    a.nsplit = (T + a.chunk - 1) / a.chunk;
+    return a;
+}
+
+// Producer warp, ahead of the consumers: brings the K/V rows this CTA will read in an attention phase
+// (the same item split as attn_phase) and the output positions of its heads into the L2.  These are
+// real loads, not prefetch hints: hints were found to leave the rows in HBM, and the attention phase
+// has nothing to hide that latency behind.  The values are folded into a word that is stored only
+// if it has a value it cannot have.
+__device__ __noinline__ void warm_attention(const AttnParams& p, int pos_now, int* sink) {
+    const int lane = threadIdx.x & 31;
+    const int pos = p.pos_fixed >= 0 ? p.pos_fixed : pos_now;
+    const int T = pos + 1;
+    const int nkv = p.n_kv_local > 0 ? p.n_kv_local : p.n_kv_heads;
+    const AttSplit sp = att_split(p, T, nkv);
+    const int KV = p.n_kv_heads * HS;
+    float fold = 0.f;
+#pragma unroll 1
+    for (int item = blockIdx.x; item < nkv * sp.nsplit; item += gridDim.x) {
+        const int kvh = item % nkv + p.kvh0, split = item / nkv;
+        const int t0 = split * sp.chunk, t1 = min(pos, t0 + sp.chunk);  // row `pos` is written by the phase itself
+        const float4* kc4 = reinterpret_cast<const float4*>(p.kc) + (size_t)kvh * (HS / 4) + lane;
+        const float4* vc4 = reinterpret_cast<const float4*>(p.vc) + (size_t)kvh * (HS / 4) + lane;
+        const size_t rs = (size_t)KV / 4;
+#pragma unroll 1
+        for (int tb = t0; tb < t1; tb += 8) {
+            float4 a[8], b[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int tt = min(tb + u, t1 - 1);
+                a[u] = __ldcg(kc4 + (size_t)tt * rs);
+                b[u] = __ldcg(vc4 + (size_t)tt * rs);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) fold += a[u].x + b[u].x;
+        }
+    }
+    if (fold == 1.2345678e38f && sink) *sink = 1;  // never true in practice; keeps the loads alive
+}
+
+// Three tagged words that become valid together (an element of a partial sum with the split's maximum
+// and denominator): one trip to the L2 once they are there.
+__device__ __forceinline__ bool load_tagged3(const unsigned long long* pa, const unsigned long long* pm, const unsigned long long* pl, uint32_t tag,
+                                             float& a, float& m, float& l) {
+#pragma unroll 1
+    for (uint32_t it = 0; it < TAG_POLL_LIMIT; it++) {
+        unsigned long long wa, wm, wl;
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(wa) : "l"(pa) : "memory");
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(wm) : "l"(pm) : "memory");
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(wl) : "l"(pl) : "memory");
+        if ((uint32_t)(wa >> 32) == tag && (uint32_t)(wm >> 32) == tag && (uint32_t)(wl >> 32) == tag) {
+            a = __uint_as_float((uint32_t)wa); m = __uint_as_float((uint32_t)wm); l = __uint_as_float((uint32_t)wl);
+            return true;
+        }
+    }
+    a = 0.f; m = 0.f; l = 1.f;
+    return false;
 }
 
 template <int AG>
@@ -488,19 +549,16 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
     float(*sm_acc)[AG][HS] = reinterpret_cast<float(*)[AG][HS]>(base + AG * HS);
     float(*sm_m)[AG] = reinterpret_cast<float(*)[AG]>(base + AG * HS + TK_ATT_WARPS * AG * HS);
     float(*sm_l)[AG] = reinterpret_cast<float(*)[AG]>(base + AG * HS + TK_ATT_WARPS * AG * HS + TK_ATT_WARPS * AG);
-    volatile int* sm_last = reinterpret_cast<volatile int*>(base + AG * HS + TK_ATT_WARPS * AG * HS + 2 * TK_ATT_WARPS * AG);
     float* new_k = base + AG * HS + TK_ATT_WARPS * AG * HS + 2 * TK_ATT_WARPS * AG + 4;  // the row of `pos`: k (rotated), then v
     float* new_v = new_k + HS;
     float* sm_mx = new_v + HS;  // [AG] maximum over the warps
+    unsigned long long* part = reinterpret_cast<unsigned long long*>(p.part);  // [head][max_split][HS + 2] tagged
 
     if (p.pos_fixed >= 0) pos = p.pos_fixed;
     const int T = pos + 1;
     const int nkv = p.n_kv_local > 0 ? p.n_kv_local : p.n_kv_heads;
-    // splits: about 256 positions each, no more than the CTAs can take in one round
-    int nsplit = (T + 255) / 256;
-    nsplit = min(nsplit, min(p.max_split, max(1, (int)gridDim.x / nkv)));
-    const int chunk = (T + nsplit - 1) / nsplit;
-    nsplit = (T + chunk - 1) / chunk;
+    const AttSplit sp = att_split(p, T, nkv);
+    const int nsplit = sp.nsplit, chunk = sp.chunk;
     const int nitems = nkv * nsplit;
     const int KV = p.n_kv_heads * HS;
     const float inv_div = sqrtf((float)HS);
@@ -509,13 +567,14 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
     // combine: thread (j0, i) owns element i of heads j0, j0 + 4, ...
     const int i = tid & (HS - 1), j0 = tid >> 7;
 
+#pragma unroll 1
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
         const int kvh = item % nkv + p.kvh0, split = item / nkv;
         const int t0 = split * chunk, t1 = min(T, t0 + chunk);
         const int nwarps = min(TK_ATT_WARPS, (t1 - t0 + U - 1) / U);  // warps that have rows in the first round
         // Loads that do not depend on this token's projections are issued first, so that their latency
         // overlaps the loads of q/k/v and the RoPE below: the first round of K/V rows (except the row
-        // of `pos` itself) and the output positions.
+        // of `pos` itself).
         const float4* kc4 = reinterpret_cast<const float4*>(p.kc) + (size_t)kvh * (HS / 4) + lane;
         const float4* vc4 = reinterpret_cast<const float4*>(p.vc) + (size_t)kvh * (HS / 4) + lane;
         const size_t rs = (size_t)KV / 4;
@@ -531,15 +590,9 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
                 kk[u] = vv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        int oi[(AG + 3) / 4];
-#pragma unroll
-        for (int gi = 0; gi < (AG + 3) / 4; gi++) {
-            const int g = j0 + 4 * gi;
-            const int o = (kvh * AG + min(g, AG - 1)) * HS + i;
-            oi[gi] = p.oidx ? __ldg(p.oidx + o) : o;
-        }
         if (stamp && tid == 0) stamp[10] = clock64();
         // rotate-half RoPE updated in place: the second half uses the already rotated first half (src/models.rs:106-116)
+#pragma unroll 1
         for (int idx = tid; idx < AG * (HS / 2); idx += SK_THREADS) {
             const int g = idx / (HS / 2), e = idx % (HS / 2);
             const int h = kvh * AG + g;
@@ -594,6 +647,7 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
             const int tt = min(tb0 + u, t1 - 1);
             if (tt == pos && tb0 < t1) { load_k(tt, kk[u]); load_v(tt, vv[u]); }
         }
+#pragma unroll 1
         for (int tb = tb0; tb < t1; tb += TK_ATT_WARPS * U) {
             const int tbn = tb + TK_ATT_WARPS * U;  // the next round's rows are requested as soon as a register is free
             // all scores of the round first (independent warp reductions), then the running softmax in row order
@@ -673,57 +727,58 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
             if (w == 0) sm_mx[g] = fmax_g;
         }
         consumer_sync();
-#pragma unroll
-        for (int gi = 0; gi < (AG + 3) / 4; gi++) {
-            const int g = j0 + 4 * gi;
-            if (g < AG) {
-                float ll = 0.f, aa = 0.f;
-                for (int w = 0; w < nwarps; w++) {
-                    const float e = sm_m[w][g];
-                    ll += sm_l[w][g] * e;
-                    aa += sm_acc[w][g][i] * e;
-                }
-                if (nsplit == 1) {
-                    store_tagged_all(tk, p.bcast, p.out, oi[gi], aa / ll, out_tag);
-                } else {
-                    float* dst = p.part + ((size_t)(kvh * AG + g) * p.max_split + split) * (HS + 2);
-                    dst[i] = aa;
-                    if (i == 0) { dst[HS] = sm_mx[g]; dst[HS + 1] = ll; }
-                }
+#pragma unroll 1
+        for (int g = j0; g < AG; g += 4) {
+            float ll = 0.f, aa = 0.f;
+            for (int w = 0; w < nwarps; w++) {
+                const float e = sm_m[w][g];
+                ll += sm_l[w][g] * e;
+                aa += sm_acc[w][g][i] * e;
             }
-        }
-        if (nsplit > 1) {
-            __threadfence();
-            consumer_sync();
-            if (tid == 0) {
-                const unsigned ticket = atomicAdd(p.counter + kvh, 1u);
-                const int last = ticket == (unsigned)nsplit - 1u;
-                if (last) p.counter[kvh] = 0;  // ready for the next use
-                *sm_last = last;
-            }
-            consumer_sync();
-            if (*sm_last) {  // the CTA that finishes the last split merges the splits in split order
-                __threadfence();
-#pragma unroll
-                for (int gi = 0; gi < (AG + 3) / 4; gi++) {
-                    const int g = j0 + 4 * gi;
-                    if (g < AG) {
-                        const float* src = p.part + (size_t)(kvh * AG + g) * p.max_split * (HS + 2);
-                        float mm = -INFINITY;
-                        for (int s = 0; s < nsplit; s++) mm = fmaxf(mm, __ldcg(src + (size_t)s * (HS + 2) + HS));
-                        float ll = 0.f, aa = 0.f;
-                        for (int s = 0; s < nsplit; s++) {
-                            const float e = expf(__ldcg(src + (size_t)s * (HS + 2) + HS) - mm);
-                            ll += __ldcg(src + (size_t)s * (HS + 2) + HS + 1) * e;
-                            aa += __ldcg(src + (size_t)s * (HS + 2) + i) * e;
-                        }
-                        store_tagged_all(tk, p.bcast, p.out, oi[gi], aa / ll, out_tag);
-                    }
-                }
+            const int o = (kvh * AG + g) * HS + i;
+            if (nsplit == 1) {
+                store_tagged_all(tk, p.bcast, p.out, p.oidx ? __ldg(p.oidx + o) : o, aa / ll, out_tag);
+            } else {  // this rank's own partial buffer: the merging CTA is on this GPU
+                unsigned long long* dst = part + ((size_t)(kvh * AG + g) * p.max_split + split) * (HS + 2);
+                store_tagged(dst, i, aa, out_tag);
+                if (i == 0) { store_tagged(dst, HS, sm_mx[g], out_tag); store_tagged(dst, HS + 1, ll, out_tag); }
             }
         }
         consumer_sync();  // the scratch is reused by the next item
         if (stamp && tid == 0) stamp[13] = clock64();
+    }
+    if (nsplit > 1) {
+        // ---- merge: CTA c takes the local heads c, c + grid, ...; the splits are combined in split order
+        float* mg_a = base;                                  // [nsplit][HS]
+        float* mg_m = base + 32 * HS;                        // [nsplit]
+        float* mg_l = mg_m + 32;
+        const int sgrp = tid >> 7;                           // thread (sgrp, i) fetches element i of splits sgrp, sgrp + 4, ...
+#pragma unroll 1
+        for (int hl = blockIdx.x; hl < nkv * AG; hl += gridDim.x) {
+            const int h = p.kvh0 * AG + hl;
+            const unsigned long long* src = part + (size_t)h * p.max_split * (HS + 2);
+#pragma unroll 1
+            for (int s = sgrp; s < nsplit; s += 4) {
+                float a, mm, ll;
+                fine = load_tagged3(src + (size_t)s * (HS + 2) + i, src + (size_t)s * (HS + 2) + HS, src + (size_t)s * (HS + 2) + HS + 1, out_tag, a, mm, ll) && fine;
+                mg_a[s * HS + i] = a;
+                if (i == 0) { mg_m[s] = mm; mg_l[s] = ll; }
+            }
+            consumer_sync();
+            if (tid < HS) {
+                float mm = -INFINITY;
+                for (int s = 0; s < nsplit; s++) mm = fmaxf(mm, mg_m[s]);
+                float ll = 0.f, aa = 0.f;
+                for (int s = 0; s < nsplit; s++) {
+                    const float e = expf(mg_m[s] - mm);
+                    ll += mg_l[s] * e;
+                    aa += mg_a[s * HS + i] * e;
+                }
+                const int o = h * HS + i;
+                store_tagged_all(tk, p.bcast, p.out, p.oidx ? __ldg(p.oidx + o) : o, aa / ll, out_tag);
+            }
+            consumer_sync();
+        }
     }
     return fine;
 }
@@ -971,7 +1026,12 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
                     if (got1 && recs[(p + 1) % TK_NREC].type == PH_ATTN) warm_attention(recs[(p + 1) % TK_NREC].u.at, prod_pos, nullptr);
                 }
                 warm_operands(rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1);
-                if (!produce_units<W>(rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1, R, kfill)) break;
+                #ifdef L2_TK_TRACE
+                unsigned long long* pstamp = tk.trace ? tk.trace + ((size_t)blockIdx.x * tk.nphases + p) * TK_TRACE_W : nullptr;
+#else
+                unsigned long long* const pstamp = nullptr;
+#endif
+                if (!produce_units<W>(rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1, R, kfill, pstamp)) break;
             }
         }
         return;
@@ -995,7 +1055,7 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
         if (abort_flag) { ok = false; break; }
         const PhaseRec& rec = recs[p % TK_NREC];
 #ifdef L2_TK_TRACE
-        unsigned long long* stamp = tk.trace ? tk.trace + ((size_t)blockIdx.x * tk.nphases + p) * 16 : nullptr;
+        unsigned long long* stamp = tk.trace ? tk.trace + ((size_t)blockIdx.x * tk.nphases + p) * TK_TRACE_W : nullptr;
 #else
         unsigned long long* const stamp = nullptr;  // clock stamps are compiled in with -DL2_TK_TRACE only: they cost registers
 #endif
@@ -1005,8 +1065,8 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
         bool fine = true;
         switch (rec.type) {
             case PH_EMBED: embed_phase(rec.u.em, out_tag); break;
-            case PH_GEMV1: ok = gemv_phase<W, 1>(tk, rec.u.sk, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
-            case PH_GEMV2: ok = gemv_phase<W, 2>(tk, rec.u.sk, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
+            case PH_GEMV1: ok = gemv_phase<W>(tk, rec.u.sk, 1, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
+            case PH_GEMV2: ok = gemv_phase<W>(tk, rec.u.sk, 2, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
             case PH_ATTN: fine = attn_phase<AG>(tk, rec.u.at, smem, tok_pos, stamp, tagbase | (uint32_t)rec.u.at.in_phase, out_tag); break;
             case PH_CLS: fine = cls_phase(rec.u.cl, reinterpret_cast<float*>(smem), red, tagbase | (uint32_t)rec.u.cl.in_phase); break;
             case PH_SELECT: if (blockIdx.x == 0) select_phase(rec.u.se, red); break;
@@ -1056,6 +1116,12 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
 
 size_t token_attn_scratch_bytes(int ag) { return tk_att_bytes(ag); }
 
+// Polls of a tagged input before the token kernel gives up (0 = the default, about a second).
+cudaError_t token_set_poll_limit(unsigned polls) {
+    const uint32_t v = polls ? polls : TAG_POLL_LIMIT_DEFAULT;
+    return cudaMemcpyToSymbol(c_tag_poll_limit, &v, sizeof v);
+}
+
 template <int W, int AG>
 static cudaError_t launch_token_t(const TokenParams& tk, int grid, size_t smem, cudaStream_t st) {
     cudaLaunchConfig_t cfg{};
@@ -1076,9 +1142,11 @@ template <int W>
 static cudaError_t launch_token_w(const TokenParams& tk, int ag, int grid, size_t smem, cudaStream_t st) {
     switch (ag) {
         case 1: return launch_token_t<W, 1>(tk, grid, smem, st);
+#ifndef L2_TK_ONE
         case 2: return launch_token_t<W, 2>(tk, grid, smem, st);
         case 4: return launch_token_t<W, 4>(tk, grid, smem, st);
         case 8: return launch_token_t<W, 8>(tk, grid, smem, st);
+#endif
         default: return cudaErrorInvalidValue;
     }
 }
@@ -1089,8 +1157,12 @@ static cudaError_t launch_token_w(const TokenParams& tk, int ag, int grid, size_
 cudaError_t launch_token(const TokenParams& tk, int group_size, int ag, int grid, size_t smem, cudaStream_t st) {
     switch (group_size) {
         case 128: return launch_token_w<4>(tk, ag, grid, smem, st);
+#ifndef L2_TK_ONE
         case 64: return launch_token_w<2>(tk, ag, grid, smem, st);
         default: return launch_token_w<1>(tk, ag, grid, smem, st);
+#else
+        default: return cudaErrorInvalidValue;  // a development build that holds the 128-wide, one-head-per-kv-head kernel only
+#endif
     }
 }
 
@@ -1102,8 +1174,13 @@ cudaError_t token_init(int max_optin) {
     if ((e = cudaFuncGetAttributes(&fa, token_kernel<W, AG>)) != cudaSuccess) return e;                   \
     if ((e = cudaFuncSetAttribute(token_kernel<W, AG>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
                                   max_optin - (int)fa.sharedSizeBytes)) != cudaSuccess) return e;
+#ifndef L2_TK_ONE
 #define L2_TK_ATTR_W(W) L2_TK_ATTR(W, 1) L2_TK_ATTR(W, 2) L2_TK_ATTR(W, 4) L2_TK_ATTR(W, 8)
     L2_TK_ATTR_W(4) L2_TK_ATTR_W(2) L2_TK_ATTR_W(1)
+#else
+#define L2_TK_ATTR_W(W) L2_TK_ATTR(W, 1)
+    L2_TK_ATTR_W(4)
+#endif
 #undef L2_TK_ATTR_W
 #undef L2_TK_ATTR
     return cudaSuccess;

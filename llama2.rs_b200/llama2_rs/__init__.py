@@ -54,7 +54,7 @@ def synth_write_file(config, seed, path, threads=0):
     check(lib.l2_synth_write_file(C.byref(config), seed, str(path).encode(), threads))
 
 
-def _options(model_size, group_size, attn_groups, device, debug, max_batch, flags, tp=(0, 1)):
+def _options(model_size, group_size, attn_groups, device, debug, max_batch, flags, tp=(0, 1), poll_limit_log2=0):
     o = Options()
     o.model_size = model_size.encode() if model_size else None
     o.group_size = group_size
@@ -64,6 +64,7 @@ def _options(model_size, group_size, attn_groups, device, debug, max_batch, flag
     o.max_batch = max_batch
     o.flags = flags
     o.tp_rank, o.tp_world = tp
+    o.poll_limit_log2 = poll_limit_log2
     return o
 
 
@@ -86,10 +87,10 @@ class LlamaModel:
         return cls(checkpoint, debug, **kw)
 
     @classmethod
-    def from_blob(cls, config, payload, *, device=-1, debug=False, max_batch=0, flags=0, tp=(0, 1)):
+    def from_blob(cls, config, payload, *, device=-1, debug=False, max_batch=0, flags=0, tp=(0, 1), poll_limit_log2=0):
         """The same on the bytes after the header (numpy uint8 array in the export.py layout)."""
         h = C.c_void_p()
-        o = _options(None, config.group_size, config.n_heads // config.n_kv_heads, device, debug, max_batch, flags, tp)
+        o = _options(None, config.group_size, config.n_heads // config.n_kv_heads, device, debug, max_batch, flags, tp, poll_limit_log2)
         check(lib.l2_model_open_blob(C.byref(config), payload.ctypes.data_as(C.c_void_p), payload.nbytes, C.byref(o), C.byref(h)))
         return cls(_handle=h)
 
@@ -119,6 +120,13 @@ class LlamaModel:
         """Maps rank `rank`'s pool; when every rank's pool is attached the token path needs no NCCL."""
         buf = C.create_string_buffer(bytes(handle_bytes), 64)
         check(lib.l2_model_tp_pool_attach(self._h, rank, buf))
+
+    def tp_pool_bytes(self):
+        return int(lib.l2_model_tp_pool_bytes(self._h))
+
+    def tp_pool_attach_ptr(self, rank, device_ptr):
+        """Attaches a pool that lives in this process (device pointer) as rank `rank`'s."""
+        check(lib.l2_model_tp_pool_attach_ptr(self._h, rank, C.c_void_p(device_ptr)))
 
     def set_stream(self, cuda_stream):
         check(lib.l2_model_set_stream(self._h, C.c_void_p(cuda_stream)))

@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "libllama2_b200.so")
+# LLAMA2_B200_LIB names another build of the same library (for example one with the debugging clock stamps compiled in)
+LIB_PATH = os.environ.get("LLAMA2_B200_LIB") or os.path.join(os.path.dirname(_HERE), "libllama2_b200.so")
 
 
 class L2Error(RuntimeError):
@@ -28,7 +29,7 @@ class Config(C.Structure):
 class Options(C.Structure):
     _fields_ = [("model_size", C.c_char_p), ("group_size", C.c_int32), ("attn_groups", C.c_int32),
                 ("device", C.c_int32), ("debug", C.c_int32), ("max_batch", C.c_int32), ("flags", C.c_int32),
-                ("tp_rank", C.c_int32), ("tp_world", C.c_int32)]
+                ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("poll_limit_log2", C.c_int32)]
 
 
 FLAG_NO_GRAPH = 1
@@ -62,6 +63,8 @@ SIGNATURES = {
     "l2_tp_rows": (C.c_int, [C.c_int, C.c_int, C.c_int, _p(C.c_int), _p(C.c_int)]),
     "l2_model_tp_pool_handle": (C.c_int, [_vp, _vp]),
     "l2_model_tp_pool_attach": (C.c_int, [_vp, C.c_int, _vp]),
+    "l2_model_tp_pool_bytes": (C.c_size_t, [_vp]),
+    "l2_model_tp_pool_attach_ptr": (C.c_int, [_vp, C.c_int, _vp]),
     "l2_state_new": (C.c_int, [_vp, _p(_vp)]),
     "l2_state_reset": (C.c_int, [_vp]),
     "l2_state_free": (None, [_vp]),

@@ -58,6 +58,23 @@ def test_model_shapes(l2, orc, gs, K, N):
     assert np.array_equal(q.matvec(x1), q.matvec(x1))
 
 
+@pytest.mark.parametrize("gs", [64, 128])
+@pytest.mark.parametrize("K,N", SHAPES)
+def test_model_shapes_batched(l2, orc, gs, K, N):
+    # the batched (tcgen05) path at the benchmark's batch sizes: one pass, a full pass, several passes, and a ragged batch;
+    # on the large shapes the groups of a matrix are split over several CTAs per tile as well
+    rng = np.random.default_rng(K * 11 + N + gs)
+    qw, qz, sc, gi = random_qlinear(rng, K, N, gs)
+    q = l2.QLinear(qw, qz, sc, gi, gs)
+    for M in (16, 64, 256, 37):
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        y = q.matvec(x)
+        assert_close(y, orc.qlinear_matvec(qw, qz, sc, gi, gs, x), rel=1e-4, abs_=1e-3, what="K%d N%d M%d" % (K, N, M))
+    # a row of a batch equals the same row alone (B = 1 goes through the GEMV kernel): same integers, same scale order
+    x = rng.standard_normal((5, K)).astype(np.float32)
+    assert_close(q.matvec(x)[3], q.matvec(x[3]), rel=1e-5, abs_=1e-4, what="batched row vs single row")
+
+
 def test_bad_arguments(l2):
     rng = np.random.default_rng(0)
     qw, qz, sc, gi = random_qlinear(rng, 256, 64, 64)

@@ -9,6 +9,9 @@ makes two different calls in a row and checks both.  It is collected last on pur
 import numpy as np
 import pytest
 
+from conftest import assert_close
+from test_gpu_attention import oracle_attention
+
 pytestmark = pytest.mark.gpu
 HS = 128
 
@@ -24,7 +27,7 @@ def _inputs(rng, n_heads, n_kv_heads, pos, seq):
     return q, k, v, kc, vc
 
 
-def test_noalloc_matches_workspace_entry_point_twice(l2):
+def test_noalloc_matches_workspace_entry_point_twice(l2, orc):
     import torch
     seq = 1024
     cos, sin = np.zeros((seq, HS // 2), np.float32), np.zeros((seq, HS // 2), np.float32)
@@ -41,10 +44,18 @@ def test_noalloc_matches_workspace_entry_point_twice(l2):
             dq, dk, dv, dkc, dvc = map(d, (q, k, v, kc, vc))
             out = torch.zeros(n_heads * HS, device="cuda")
             if noalloc:
-                before = torch.cuda.memory_allocated()
-                rc = l2.lib.l2_attention_decode_noalloc(n_heads, n_kv_heads, pos, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                                        dkc.data_ptr(), dvc.data_ptr(), dcos.data_ptr(), dsin.data_ptr(), out.data_ptr(), st)
-                assert torch.cuda.memory_allocated() == before
+                call = lambda kcache, vcache, o: l2.lib.l2_attention_decode_noalloc(
+                    n_heads, n_kv_heads, pos, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), kcache.data_ptr(), vcache.data_ptr(),
+                    dcos.data_ptr(), dsin.data_ptr(), o.data_ptr(), st)
+                # a warm-up call on scratch copies first (the very first call on a device looks the array's address up and
+                # may load the module), then the device's free memory as the driver reports it must not move across the
+                # checked call: torch's own counters would not see a cudaMalloc made inside the library
+                l2.check(call(dkc.clone(), dvc.clone(), torch.zeros_like(out)))
+                torch.cuda.synchronize()
+                free_before = torch.cuda.mem_get_info()[0]
+                rc = call(dkc, dvc, out)
+                torch.cuda.synchronize()
+                assert torch.cuda.mem_get_info()[0] == free_before
             else:
                 ws = torch.empty(l2.lib.l2_attention_workspace_bytes(n_heads, n_kv_heads), dtype=torch.uint8, device="cuda")
                 rc = l2.lib.l2_attention_decode_dev(n_heads, n_kv_heads, pos, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dkc.data_ptr(),
@@ -58,6 +69,11 @@ def test_noalloc_matches_workspace_entry_point_twice(l2):
         assert np.array_equal(outs[1], outs[0])
         assert np.array_equal(caches[1][0], caches[0][0]) and np.array_equal(caches[1][1], caches[0][1])
         assert np.abs(outs[1]).max() > 0
+        # and against the CPU oracle's rope + multihead_attention (src/models.rs:100-176), the tolerance of the attention tests
+        want, want_kc, want_vc = oracle_attention(orc, q, k, v, kc, vc, pos, n_heads, n_kv_heads)
+        assert_close(outs[1], want, rel=1e-4, abs_=1e-5, what="no-alloc attention vs oracle, %d heads pos %d" % (n_heads, pos))
+        assert_close(caches[1][0][pos], want_kc[pos], rel=1e-6, abs_=1e-6, what="appended key (RoPE)")
+        assert np.array_equal(caches[1][1][pos], want_vc[pos])
 
 
 def test_noalloc_rejects_shapes_beyond_the_builtin_scratch(l2):
