@@ -93,34 +93,70 @@ class ClockSampler:
                 "samples": len(self.rows)}
 
 
+def visible_gpus():
+    try:
+        out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=20).stdout
+        n = sum(1 for line in out.splitlines() if line.startswith("GPU "))
+    except Exception:
+        n = 0
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis is not None and vis.strip() != "":
+        n = min(n, len([v for v in vis.split(",") if v.strip()])) if n else len([v for v in vis.split(",") if v.strip()])
+    return n
+
+
 def make_prompt(np, n, vocab):
     return np.random.default_rng(PROMPT_SEED).integers(0, vocab, n).astype(np.int32)
 
 
 class CpuArm:
-    """The CPU restatement on a bounded sample of the workload: the prompt through the reference's
-    prefill ladder, then `sample_tokens` greedy decode tokens; decode tok/s over the B=1 positions."""
+    """The CPU restatement on a bounded sample of the workload.  Set-up (untimed, once): the checkpoint in host memory
+    and the prompt through the reference's 64/32/16/8/4/2 prefill ladder (its own tok/s is reported).  One run() = the
+    next `sample_tokens` positions of the greedy B=1 loop; decode tok/s over those positions."""
 
     def __init__(self, workload, payload=None, cfg=None):
         import numpy as np
         import llama2_rs as l2
         import oracle as orc
+        self.np, self.orc = np, orc
         self.size, gs, self.n_prompt, _ = WORKLOADS[workload]
         self.cfg = cfg if cfg is not None else l2.preset_config(self.size, gs)
         self.payload = payload if payload is not None else l2.synth_fill(self.cfg, WEIGHT_SEED)
         self.model = orc.Model(self.cfg, self.payload)
-        self.sample_tokens = {"7b": 6, "13b": 4, "70b": 2}[workload]
+        self.sample_tokens = {"7b": 8, "13b": 4, "70b": 1}[workload]
         self.prompt = make_prompt(np, self.n_prompt, self.cfg.vocab_size)
         self.cores = orc.lib().orc_num_threads()
+        self.state = orc.State(self.model)
+        # prefill<A> ladder (src/inference.rs:78-127): batches of A rows while pos + A < n_prompt
+        self.pos = 0
+        t0 = time.perf_counter()
+        for a in (64, 32, 16, 8, 4, 2):
+            while self.pos + a < self.n_prompt:
+                positions = np.arange(self.pos, self.pos + a, dtype=np.int32)
+                tokens = np.array([1 if p == 0 else self.prompt[p - 1] for p in positions], np.int32)
+                self.model.transformer(self.state, tokens, positions)
+                self.pos += a
+        self.prefill_s = time.perf_counter() - t0
+        self.prefill_positions = self.pos
+        self.token = 1 if self.pos == 0 else int(self.prompt[self.pos - 1])
+        self.first_pos = self.pos
 
     def run(self):
-        r = self.model.generate_ids(self.prompt, self.n_prompt + self.sample_tokens)
-        n = len(r["tokens"])
-        decode_ms = r["elapsed_ms"] - r["prefill_ms"]
-        prefill_tok_s = r["pos0"] / max(r["prefill_ms"], 1e-9) * 1e3
-        return {"value": n / decode_ms * 1e3, "unit": "tok/s", "cores": self.cores, "kind": "port",
-                "sample": "%s synthetic checkpoint, %d-token prompt through the 64/32/16/8/4/2 prefill ladder (%.0f ms, %.1f tok/s), then %d B=1 positions"
-                          % (self.size, self.n_prompt, r["prefill_ms"], prefill_tok_s, n),
+        np = self.np
+        n, t0 = 0, time.perf_counter()
+        for _ in range(self.sample_tokens):
+            if self.pos + 1 >= self.cfg.seq_len:
+                break
+            logits = self.model.transformer(self.state, np.array([self.token], np.int32), np.array([self.pos], np.int32))
+            nxt = int(self.prompt[self.pos]) if self.pos < self.n_prompt else int(len(logits) - 1 - np.argmax(logits[::-1]))  # last maximum wins (src/util.rs:39-46)
+            self.token, self.pos, n = nxt, self.pos + 1, n + 1
+        dt = time.perf_counter() - t0
+        prefill_tok_s = self.prefill_positions / max(self.prefill_s, 1e-9)
+        return {"value": n / dt, "unit": "tok/s", "cores": self.cores, "kind": "port",
+                "sample": "%s synthetic checkpoint; set-up (untimed): %d-token prompt, %d positions through the 64/32/16/8/4/2 prefill ladder (%.0f ms, %.1f tok/s); "
+                          "timed: %d B=1 positions per step, context %d..%d so far (the GPU arm averages over contexts up to %d)"
+                          % (self.size, self.n_prompt, self.prefill_positions, self.prefill_s * 1e3, prefill_tok_s, self.sample_tokens,
+                             self.first_pos, self.pos, self.n_prompt + WORKLOADS[self.size.lower()][3]),
                 "prefill_tok_s": prefill_tok_s}
 
 
@@ -140,12 +176,19 @@ def main():
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.workload == "auto":
-        args.workload = "7b"  # the configuration the metric is quoted on, at every N (N > 1: one token stream per GPU)
+    auto = args.workload == "auto"
+    if auto:
+        # One GPU visible: the 7B configuration the metric is quoted on.  Inside a scaling run (launched by torch.distributed.run,
+        # or with several GPUs visible -- the N = 1 leg of such a run is a plain `python bench.py --gpus 1` on the multi-GPU box):
+        # the 70B configuration, which is the one that shards, at every N including 1, so that the per-N values form the
+        # strong-scaling curve of tensor parallelism.
+        args.workload = "70b" if ("WORLD_SIZE" in os.environ or visible_gpus() > 1) else "7b"
     tp = world > 1 and args.workload == "70b"  # 70B is sharded over the ranks (tensor parallel); smaller models run as replicas
     size, gs, n_prompt, n_decode = WORKLOADS[args.workload]
     config = {"workload": "Llama2-%s GPTQ 4-bit g%d act-order, %d-token random prompt, %d greedy decode tokens, batch 1"
-                          % (size, gs, n_prompt, n_decode),
+                          % (size, gs, n_prompt, n_decode) +
+                          (" (default of a scaling run: more than one GPU visible or launched by torch.distributed.run; with one GPU visible the default is the 7B configuration)"
+                           if auto and args.workload == "70b" else ""),
               "weights": "seeded synthetic checkpoint (seed %d) in the export.py .bin layout" % WEIGHT_SEED,
               "l2": "weights streamed per token (%s) exceed the 126 MB L2; no flush needed" % size,
               "parallelism": ("tp%d: every QLinear split by output rows, %s" % (world, "NCCL all-gathers in the token graph" if args.tp_nccl else

@@ -176,13 +176,21 @@ __device__ __forceinline__ void store_tagged_peer(void* base, size_t index, floa
     const unsigned long long w = (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(static_cast<unsigned long long*>(base) + index), "l"(w) : "memory");
 }
+// The polls are system-scope loads: under tensor parallelism a value may have been stored by another GPU
+// (st.relaxed.sys over NVLink into this GPU's memory), and a load only synchronises with a store whose
+// scope it shares.  Device memory is served by this GPU's L2 either way.
+#ifdef L2_POLL_GPU_SCOPE  // development switch: device-scope polls (single-GPU timing comparisons only)
+#define L2_POLL_LD "ld.relaxed.gpu.global"
+#else
+#define L2_POLL_LD "ld.relaxed.sys.global"
+#endif
 // One tagged value; returns false when the poll limit is reached.
 __device__ __forceinline__ bool load_tagged(const void* base, size_t index, uint32_t tag, float& v) {
     const unsigned long long* p = static_cast<const unsigned long long*>(base) + index;
 #pragma unroll 1
     for (uint32_t it = 0; it < TAG_POLL_LIMIT; it++) {
         unsigned long long w;
-        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+        asm volatile(L2_POLL_LD ".u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
         if ((uint32_t)(w >> 32) == tag) { v = __uint_as_float((uint32_t)w); return true; }
     }
     v = 0.f;
@@ -194,10 +202,10 @@ __device__ __forceinline__ bool load_tagged8(const void* base, size_t index, uin
 #pragma unroll 1
     for (uint32_t it = 0; it < TAG_POLL_LIMIT; it++) {
         uint4 a, b, c, d;
-        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p) : "memory");
-        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p + 1) : "memory");
-        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(c.x), "=r"(c.y), "=r"(c.z), "=r"(c.w) : "l"(p + 2) : "memory");
-        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "l"(p + 3) : "memory");
+        asm volatile(L2_POLL_LD ".v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p) : "memory");
+        asm volatile(L2_POLL_LD ".v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p + 1) : "memory");
+        asm volatile(L2_POLL_LD ".v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(c.x), "=r"(c.y), "=r"(c.z), "=r"(c.w) : "l"(p + 2) : "memory");
+        asm volatile(L2_POLL_LD ".v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "l"(p + 3) : "memory");
         if (a.y == tag && a.w == tag && b.y == tag && b.w == tag && c.y == tag && c.w == tag && d.y == tag && d.w == tag) {
             v0 = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
             v1 = make_float4(__uint_as_float(c.x), __uint_as_float(c.z), __uint_as_float(d.x), __uint_as_float(d.z));
@@ -392,7 +400,7 @@ __device__ __forceinline__ void stage_issue(const SkSeg& sg, int blk, StageLoad&
     const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned long long*>(sg.x) + (size_t)blk * 8);
 #pragma unroll
     for (int i = 0; i < 4; i++)
-        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(L.q[i].x), "=r"(L.q[i].y), "=r"(L.q[i].z), "=r"(L.q[i].w) : "l"(p + i) : "memory");
+        asm volatile(L2_POLL_LD ".v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(L.q[i].x), "=r"(L.q[i].y), "=r"(L.q[i].z), "=r"(L.q[i].w) : "l"(p + i) : "memory");
     if (sg.nw) {
         const float4* n4 = reinterpret_cast<const float4*>(sg.nw);
         L.w0 = __ldg(n4 + 2 * blk);
@@ -404,7 +412,7 @@ __device__ __forceinline__ bool stage_tags_ok(const StageLoad& L, uint32_t tag) 
 }
 
 template <int W>
-__device__ __noinline__ void stage_groups(const SkSeg& sg, int in, uint8_t* digits, int* ss, float* pg, uint32_t tag, bool want_sq, float* sq_out,
+__device__ __forceinline__ void stage_groups(const SkSeg& sg, int in, uint8_t* digits, int* ss, float* pg, uint32_t tag, bool want_sq, float* sq_out,
                                           bool* fail, unsigned long long* stamp = nullptr) {
     const int nblk = in / 8, stride = in + 16;
     float sq = 0.f;
@@ -482,6 +490,126 @@ __device__ __noinline__ void stage_groups(const SkSeg& sg, int in, uint8_t* digi
         cur = nxt;
     }
     if (want_sq) *sq_out = sq;
+}
+
+// ---- staging of a vector that arrives in natural order and is consumed in a matrix's K order -------
+// Values cross CTAs fastest when every 128-byte line has one writer: a vector whose elements are scattered
+// by their producers into a consumer's K order (eight writers per line polled) takes about three times as
+// long to arrive as the same vector written tile by tile.  So producers store in natural order, and the
+// consumer (1) polls the natural vector into shared memory as plain floats, taking the sum of squares on the
+// way, and (2) gathers its K order from there through the matrix's g_index while it writes the digits.
+
+// (1) n / 8 blocks of 8 tagged values, times the norm weight (natural order, or null) -> xs[n]; returns this
+// thread's share of the sum of squares of the raw values.
+__device__ __forceinline__ float stage_poll_natural(const void* x_tagged, const float* nw_natural, int n, float* xs, uint32_t tag, bool* fail) {
+    const int nblk = n / 8;
+    float sq = 0.f;
+#pragma unroll 1
+    for (int blk = threadIdx.x; blk < nblk; blk += SK_THREADS) {
+        float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
+        if (nw_natural) {  // requested before the poll: it does not depend on the awaited values
+            w0 = __ldg(reinterpret_cast<const float4*>(nw_natural) + 2 * blk);
+            w1 = __ldg(reinterpret_cast<const float4*>(nw_natural) + 2 * blk + 1);
+        }
+        float4 v0, v1;
+        if (!load_tagged8(x_tagged, (size_t)blk * 8, tag, v0, v1)) *fail = true;
+        sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+        v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
+        v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
+        reinterpret_cast<float4*>(xs)[2 * blk] = v0;
+        reinterpret_cast<float4*>(xs)[2 * blk + 1] = v1;
+    }
+    return sq;
+}
+
+// Turns 8 values of K-order block `blk` into balanced base-256 digits (see stage_groups) and finishes the group.
+template <int W>
+__device__ __forceinline__ void stage_emit8(float (&v)[8], bool valid, int blk, uint8_t* digits, int stride, int* ss, float* pg) {
+    float mx = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+                     fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
+#pragma unroll
+    for (int o = 1; o < 4 * W; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float P = stage_scale(mx);
+    uint32_t E[8];  // per element: bytes d3, d2, d1, d0 (least significant digit first)
+#pragma unroll
+    for (int j = 0; j < 8; j++) E[j] = ((uint32_t)__float2int_rn(v[j] * P) + 0x80808080u) ^ 0x80808080u;
+    // 4x4 byte transposes: words of one digit for inputs (0,2,4,6) and (1,3,5,7), the order in
+    // which the nibbles of a weight word separate into its low and high halves
+    uint32_t lo[4], hi[4];
+    {
+        const uint32_t a = __byte_perm(E[0], E[2], 0x5140), b2 = __byte_perm(E[0], E[2], 0x7362);
+        const uint32_t c = __byte_perm(E[4], E[6], 0x5140), d = __byte_perm(E[4], E[6], 0x7362);
+        lo[3] = __byte_perm(a, c, 0x5410); lo[2] = __byte_perm(a, c, 0x7632);
+        lo[1] = __byte_perm(b2, d, 0x5410); lo[0] = __byte_perm(b2, d, 0x7632);
+    }
+    {
+        const uint32_t a = __byte_perm(E[1], E[3], 0x5140), b2 = __byte_perm(E[1], E[3], 0x7362);
+        const uint32_t c = __byte_perm(E[5], E[7], 0x5140), d = __byte_perm(E[5], E[7], 0x7362);
+        hi[3] = __byte_perm(a, c, 0x5410); hi[2] = __byte_perm(a, c, 0x7632);
+        hi[1] = __byte_perm(b2, d, 0x5410); hi[0] = __byte_perm(b2, d, 0x7632);
+    }
+    int sum[4];
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        if (valid) *reinterpret_cast<uint2*>(digits + (size_t)p * stride + (size_t)blk * 8) = make_uint2(lo[p], hi[p]);
+        sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
+    }
+    // a group is 4*W consecutive blocks = 4*W consecutive lanes: sum them with shuffles
+    int s01 = 256 * sum[0] + sum[1], s23 = 256 * sum[2] + sum[3];
+#pragma unroll
+    for (int o = 1; o < 4 * W; o <<= 1) {
+        s01 += __shfl_xor_sync(0xffffffffu, s01, o);
+        s23 += __shfl_xor_sync(0xffffffffu, s23, o);
+    }
+    if (valid && (threadIdx.x & (4 * W - 1)) == 0) {
+        const int g = blk / (4 * W);
+        *reinterpret_cast<int2*>(ss + 2 * g) = make_int2(s01, s23);
+        pg[g] = __uint_as_float((254u << 23) - __float_as_uint(P));  // 1 / P, exact
+    }
+}
+
+// (2) K-order block b of a matrix: positions perm[8b .. 8b+7] of xs (16-bit indices: IN < 65536).
+template <int W>
+__device__ __forceinline__ void gather_emit(const uint4& idx, const float* xs, bool valid, int blk, uint8_t* digits, int stride, int* ss, float* pg) {
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (valid) {
+        v[0] = xs[idx.x & 0xFFFFu]; v[1] = xs[idx.x >> 16]; v[2] = xs[idx.y & 0xFFFFu]; v[3] = xs[idx.y >> 16];
+        v[4] = xs[idx.z & 0xFFFFu]; v[5] = xs[idx.z >> 16]; v[6] = xs[idx.w & 0xFFFFu]; v[7] = xs[idx.w >> 16];
+    }
+    stage_emit8<W>(v, valid, blk, digits, stride, ss, pg);
+}
+
+// The whole staging of a GEMV phase whose input arrives in natural order: nseg matrices (w1 with w3) read the
+// same vector, each through its own g_index (seg[s].perm: 16-bit indices here); seg[0].nw is the norm weight
+// in natural order.  Returns this thread's share of the sum of squares.
+template <int W>
+__device__ __forceinline__ float stage_natural(const SkSeg* seg, int nseg, int in, int G, uint8_t* digits, int* ss, float* pg, float* xs, uint32_t tag, bool* fail,
+                                               unsigned long long* stamp = nullptr) {
+    const int nblk = in / 8, stride = in + 16;
+    // the indices of this thread's first K-order block of each matrix: requested before the vector is awaited
+    uint4 first0 = make_uint4(0, 0, 0, 0), first1 = first0;
+    const int blk0 = threadIdx.x;
+    if (blk0 < nblk) {
+        first0 = __ldg(reinterpret_cast<const uint4*>(seg[0].perm) + blk0);
+        if (nseg == 2) first1 = __ldg(reinterpret_cast<const uint4*>(seg[1].perm) + blk0);
+    }
+    const float sq = stage_poll_natural(seg[0].x, seg[0].nw, in, xs, tag, fail);
+    if (stamp && threadIdx.x == 0) stamp[21] = clock64();
+    consumer_sync();
+    if (stamp && threadIdx.x == 0) stamp[22] = clock64();
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+        if (s >= nseg) break;
+        uint8_t* dg = digits + (size_t)s * 4 * stride;
+#pragma unroll 1
+        for (int blk = blk0; (blk & ~31) < nblk; blk += SK_THREADS) {
+            uint4 idx = s ? first1 : first0;
+            if (blk != blk0 && blk < nblk) idx = __ldg(reinterpret_cast<const uint4*>(seg[s].perm) + blk);
+            gather_emit<W>(idx, xs, blk < nblk, blk, dg, stride, ss + s * G * 2, pg + s * G);
+        }
+    }
+    if (stamp && threadIdx.x == 0) stamp[23] = clock64();
+    return sq;
 }
 
 // Asks the L2 to fetch [p, p + bytes) from HBM; nothing waits on it.

@@ -31,8 +31,10 @@ constexpr int SK_MAX_SLOTS = 16;           // ring slots of a CTA (upper bound)
 // One 4-bit matrix in device layout (see repack.cpp) with its input vector.
 struct SkSeg {
     const uint32_t* rec;  // [tile][group] unit records of 64*W + 20 words (see repack.cpp)
-    const float* x;       // input in this matrix's K order (the producer scatters it)
-    const float* nw;      // rmsnorm weight in the same order, or null
+    const float* x;       // input in this matrix's K order (the producer scatters it); token kernel: tagged, see perm
+    const float* nw;      // rmsnorm weight in the matrix's K order, or null
+    const int* perm;      // token kernel: x is in natural order and position p of the K order reads x[perm[p]], perm as packed 16-bit
+                          // indices, and nw is in natural order too (null: x is in K order already)
 };
 
 // One fused dequant+GEMV problem of a launch.  nseg == 2 pairs w1 with w3 for SwiGLU.
@@ -155,8 +157,9 @@ struct SelectParams {
 };
 
 // ---- the whole token as one persistent kernel (token_kernel.cu) --------------------------------
-// A token is a list of phases; all CTAs run every phase and meet at a grid-wide barrier between
-// two phases.  A phase record is what the stand-alone kernel of the same name takes as parameters.
+// A token is a list of phases; all CTAs run every phase.  A phase polls the tagged values of the
+// phases it depends on; only where barrier_after is set do the CTAs meet at a grid-wide barrier.
+// A phase record is what the stand-alone kernel of the same name takes as parameters.
 enum : int { PH_EMBED = 0, PH_GEMV1, PH_GEMV2, PH_ATTN, PH_CLS, PH_SELECT, PH_ADVANCE };
 
 struct alignas(16) PhaseRec {

@@ -6,6 +6,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -26,9 +27,61 @@ static int dev_alloc(void** p, size_t bytes, std::vector<void*>& allocs, size_t*
     return L2_OK;
 }
 
+// Host -> device copies of a checkpoint load: the bytes go through two pinned staging buffers in chunks, one
+// cudaMemcpyAsync per chunk, so that reading the next chunk from the mmap (page faults, disk) or repacking the next
+// matrix overlaps the DMA of the previous one and 70B does not stage 41 GB synchronously (the reference maps the
+// file and "loads instantly", README.md:12; here the file is streamed once onto the device).
+class Uploader {
+public:
+    static constexpr size_t CHUNK = (size_t)16 << 20;
+    ~Uploader() { release(); }
+    int copy(void* dst, const void* src, size_t bytes) {
+        if (int rc = init()) return rc;
+        const char* s = static_cast<const char*>(src);
+        char* d = static_cast<char*>(dst);
+        for (size_t off = 0; off < bytes; off += CHUNK) {
+            const size_t n = std::min(CHUNK, bytes - off);
+            L2_CUDA(cudaEventSynchronize(done_[cur_]));  // the copy that used this buffer last has finished
+            memcpy(pinned_[cur_], s + off, n);
+            L2_CUDA(cudaMemcpyAsync(d + off, pinned_[cur_], n, cudaMemcpyHostToDevice, stream_));
+            L2_CUDA(cudaEventRecord(done_[cur_], stream_));
+            cur_ ^= 1;
+        }
+        return L2_OK;
+    }
+    int finish() {
+        if (stream_) L2_CUDA(cudaStreamSynchronize(stream_));
+        return L2_OK;
+    }
+private:
+    int init() {
+        if (stream_) return L2_OK;
+        L2_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; i++) {
+            L2_CUDA(cudaMallocHost(reinterpret_cast<void**>(&pinned_[i]), CHUNK));
+            L2_CUDA(cudaEventCreateWithFlags(&done_[i], cudaEventDisableTiming));
+        }
+        return L2_OK;
+    }
+    void release() {
+        if (stream_) cudaStreamSynchronize(stream_);
+        for (int i = 0; i < 2; i++) {
+            if (pinned_[i]) cudaFreeHost(pinned_[i]);
+            if (done_[i]) cudaEventDestroy(done_[i]);
+        }
+        if (stream_) cudaStreamDestroy(stream_);
+    }
+    cudaStream_t stream_ = nullptr;
+    char* pinned_[2] = {nullptr, nullptr};
+    cudaEvent_t done_[2] = {nullptr, nullptr};
+    int cur_ = 0;
+};
+static thread_local Uploader* g_uploader = nullptr;  // set while build_model runs: its uploads go through it
+
 template <class T>
 static int dev_upload(T** p, const void* src, size_t count, std::vector<void*>& allocs, size_t* total = nullptr) {
     if (int rc = dev_alloc(reinterpret_cast<void**>(p), count * sizeof(T), allocs, total)) return rc;
+    if (g_uploader) return g_uploader->copy(*p, src, count * sizeof(T));  // the source may be reused as soon as this returns
     L2_CUDA(cudaMemcpy(*p, src, count * sizeof(T), cudaMemcpyHostToDevice));
     return L2_OK;
 }
@@ -40,6 +93,10 @@ int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vecto
         if (int rc = dev_upload(&d.perm, g_index, (size_t)p.in, allocs, bytes)) return rc;
         std::vector<int32_t> inv = inverse_permutation(g_index, p.in);
         if (int rc = dev_upload(&d.inv, inv.data(), (size_t)p.in, allocs, bytes)) return rc;
+        if (p.in < 65536) {
+            std::vector<uint16_t> p16(g_index, g_index + p.in);
+            if (int rc = dev_upload(&d.perm16, p16.data(), (size_t)p.in, allocs, bytes)) return rc;
+        }
     }
     return L2_OK;
 }
@@ -158,6 +215,8 @@ struct ModelDeleter { void operator()(l2_model* m) const { l2_model_close(m); } 
 
 static int build_model(const Shape& shape, Source& src, const l2_options* opt, l2_model** out) {
     std::unique_ptr<l2_model, ModelDeleter> m(new l2_model);
+    Uploader uploader;
+    struct Scope { Scope(Uploader* u) { g_uploader = u; } ~Scope() { g_uploader = nullptr; } } scope(&uploader);
     m->shape = shape;
     if (opt) m->opt = *opt;
     if (int rc = check_device(opt ? opt->device : -1, &m->device, &m->sms)) return rc;
@@ -232,6 +291,7 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
         DevLayer& y = m->layers[l];
         const float* att = reinterpret_cast<const float*>(src.get(T_RMS_ATT, l, S_DENSE, sn));
         nw.assign(att, att + D);
+        if (int rc = dev_upload(&y.rms_att, nw.data(), (size_t)D, m->allocs, tot)) return rc;
         if (int rc = load_q(T_WQ, l, y.wq, nullptr, &gi)) return rc;
         if (int rc = permuted_norm(nw.data(), gi, &y.nw_q)) return rc;
         if (int rc = load_q(T_WK, l, y.wk, nullptr, &gi)) return rc;
@@ -241,6 +301,7 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
         if (int rc = load_q(T_WO, l, y.wo, nullptr, nullptr)) return rc;
         const float* ffn = reinterpret_cast<const float*>(src.get(T_RMS_FFN, l, S_DENSE, sn));
         nw.assign(ffn, ffn + D);
+        if (int rc = dev_upload(&y.rms_ffn, nw.data(), (size_t)D, m->allocs, tot)) return rc;
         // w2 first: its act-order permutation becomes the row order of w1 and w3, so that the
         // SwiGLU output is produced directly in w2's K order.
         if (int rc = load_q(T_W2, l, y.w2, nullptr, &gi2)) return rc;
@@ -249,6 +310,7 @@ static int build_model(const Shape& shape, Source& src, const l2_options* opt, l
         if (int rc = load_q(T_W3, l, y.w3, gi2.data(), &gi)) return rc;
         if (int rc = permuted_norm(nw.data(), gi, &y.nw_3)) return rc;
     }
+    if (int rc = uploader.finish()) return rc;
     m->decode_bytes = qbytes + (uint64_t)V * D * 4 + (uint64_t)(2 * L + 1) * D * 4;
     if (m->opt.debug) {
         printf("Configuration: Config { dim: %d, hidden_dim: %d, n_layers: %d, n_heads: %d, n_kv_heads: %d, vocab_size: %d, seq_len: %d, group_size: %d }\n",
@@ -416,7 +478,8 @@ static int plan_token(l2_state* s) {
         const SkLaunch& L = s->plans[which];  // every layer has the same shapes
         int max_g = 0;
         for (int i = 0; i < L.p.njobs; i++) max_g = std::max(max_g, L.p.job[i].G);
-        fixed = std::max(fixed, sk_smem_fixed(L.p.job[0].in, max_g, L.nseg, L.p.ptiles) + (size_t)L.nseg * max_g * 4);  // + one scaling factor per group
+        // + one scaling factor per group; + the input vector as plain floats where it arrives in natural order (all but w2)
+        fixed = std::max(fixed, sk_smem_fixed(L.p.job[0].in, max_g, L.nseg, L.p.ptiles) + (((size_t)L.nseg * max_g * 4 + 15) & ~(size_t)15) + (which != 3 ? (size_t)L.p.job[0].in * 4 : 0));
     }
     fixed = (fixed + 127) & ~(size_t)127;
     const size_t budget = 222 * 1024;
@@ -490,7 +553,7 @@ static int build_phase_table(l2_state* s, int kind) {
     {
         EmbedParams e = embed_params(s, kind);
         e.x = must(tg(e.x));
-        for (int i = 0; i < e.nscatter; i++) e.sdst[i] = must(tg(e.sdst[i]));
+        e.nscatter = 0;
         add(PH_EMBED).u.em = e;
     }
     int x_phase = 0;  // the phase that last wrote the residual stream (and its copies for the next consumer)
@@ -505,14 +568,25 @@ static int build_phase_table(l2_state* s, int kind) {
             r.u.sk.trace = nullptr;
             r.u.sk.n_next = 0;
             const int in_phase = which == 0 ? x_phase : which == 1 ? attn_phase : which == 2 ? x_phase : w13_phase;
+            // Inputs travel in natural order (one writer per 128-byte line) and are gathered into each matrix's K order by
+            // the consumer through its g_index; only w2 reads a vector that its producers (w1/w3, whose rows are stored in
+            // w2's K order) already write in the right order.
+            const DevLayer& y = m->layers[l];
+            auto p16 = [](const DevQ& q) { return reinterpret_cast<const int*>(q.perm16); };
+            const int* perms[4][3] = {{p16(y.wq), p16(y.wk), p16(y.wv)}, {p16(y.wo), nullptr, nullptr}, {p16(y.w1), p16(y.w3), nullptr}, {nullptr, nullptr, nullptr}};
+            const float* norms[4] = {y.rms_att, nullptr, y.rms_ffn, nullptr};
+            if (c.dim >= 65536) return fail(L2_EINVAL, "token kernel: DIM %d does not fit 16-bit gather indices", c.dim);
+            float* inputs[4] = {reinterpret_cast<float*>(s->t_x), reinterpret_cast<float*>(s->t_att), reinterpret_cast<float*>(s->t_x), reinterpret_cast<float*>(s->t_hb)};
             for (int j = 0; j < r.u.sk.njobs; j++) {
                 SkJob& J = r.u.sk.job[j];
                 for (int sg = 0; sg < L.nseg; sg++) {
-                    J.seg[sg].x = must(tg(J.seg[sg].x));
+                    J.seg[sg].x = inputs[which];
+                    J.seg[sg].perm = perms[which][which == 2 ? sg : j];
+                    J.seg[sg].nw = norms[which];
                     J.in_phase[sg] = in_phase;
                 }
                 J.out = must(tg(J.out));
-                for (int i = 0; i < J.nscatter; i++) J.sdst[i] = must(tg(J.sdst[i]));
+                J.nscatter = 0;
                 J.resid_phase = x_phase;
                 J.bcast = direct && which != 0;  // q/k/v stay with the rank that owns the heads; everything else every rank needs
             }
@@ -521,7 +595,8 @@ static int build_phase_table(l2_state* s, int kind) {
                 attn_phase = (int)t.size();
                 AttnParams a = attention_params(s, l, direct);
                 a.q = must(tg(a.q)); a.k = must(tg(a.k)); a.v = must(tg(a.v));
-                a.out = must(tg(a.out));
+                a.out = reinterpret_cast<float*>(s->t_att);  // natural order: wo gathers it through its g_index
+                a.oidx = nullptr;
                 a.in_phase = qkv_phase;
                 a.bcast = direct;
                 a.part = reinterpret_cast<float*>(s->t_part);

@@ -24,6 +24,7 @@ struct DevQ {
     uint32_t* rec = nullptr;   // [tiles][G] unit records: weights, scales, zero nibbles (see repack.cpp)
     int* perm = nullptr;  // g_index: permuted position j reads input perm[j]
     int* inv = nullptr;   // inverse: input o is written to permuted position inv[o]
+    uint16_t* perm16 = nullptr;  // perm as 16-bit indices (IN < 65536), what the token kernel's gather reads
     int in = 0, out = 0, tiles = 0, G = 0, gs = 0;  // out / tiles: the rows held by this process
     int row0 = 0;                                   // first row held (tensor parallelism), else 0
 };
@@ -39,6 +40,7 @@ struct DevLayer {
     DevQ wq, wk, wv, wo, w1, w2, w3;
     float *nw_q = nullptr, *nw_k = nullptr, *nw_v = nullptr;  // rms_att_weight in each consumer's K order
     float *nw_1 = nullptr, *nw_3 = nullptr;                   // rms_ffn_weight likewise
+    float *rms_att = nullptr, *rms_ffn = nullptr;             // the two norm weights in natural order (token kernel)
 };
 
 constexpr int CTL_RING = 128;

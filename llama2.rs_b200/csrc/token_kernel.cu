@@ -4,17 +4,25 @@
 //   embed | per layer: wq/wk/wv GEMV | rope + KV append + attention | wo GEMV + residual |
 //   w1/w3 GEMV + SwiGLU | w2 GEMV + residual | final rmsnorm + classifier | select
 //
-// and all CTAs meet at a grid-wide barrier between two phases.  Compared with one launch per phase
-// this removes the launch gaps and, above all, lets the weights stream without a break: warp 16 of
-// every CTA is a producer that walks the phase list ahead of the 16 consumer warps and keeps a ring
-// of shared-memory slots filled with the CTA's next unit records (large cp.async.bulk copies,
-// mbarrier per slot), across phase boundaries, while the consumers are still in the previous
-// phase, at the grid barrier, or staging the next activation vector.
+// Compared with one launch per phase this removes the launch gaps and lets the weights stream
+// without a break: warp 16 of every CTA is a producer that walks the phase list ahead of the 16
+// consumer warps and keeps a ring of shared-memory slots filled with the CTA's next unit records
+// (large cp.async.bulk copies, one mbarrier per slot), across phase boundaries, while the consumers
+// are still in the previous phase's epilogue or staging the next activation vector.
 //
-// Waits are bounded everywhere (mbarriers, the grid barrier, the producer's wait for a free record
-// buffer): a wait that gives up writes a status word, raises the CTA's abort flag, lets copies in
-// flight land and leaves; the other CTAs see the status word at their next barrier and leave too.
-// The launch is cooperative, so all CTAs are resident together.
+// There is no grid-wide barrier between phases.  Values that cross CTAs travel as (value, tag)
+// pairs that the reader polls (see gemv_device.cuh); one grid barrier per token remains, between the
+// classifier and the selection of the next token, which reads every logit.
+//
+// The kernel is bound by instruction issue and by the latency of each exchange, not by HBM: every
+// phase's code runs once per layer, so it is kept small (one GEMV phase for all four projections,
+// no unrolled polling loops) and each exchange is arranged so that everything that does not depend
+// on the awaited values (norm weights, scatter positions, K/V rows) is already in flight.
+//
+// Waits are bounded everywhere (mbarriers, tag polls, the grid barrier, the producer's wait for a
+// free slot or record buffer): a wait that gives up writes a status word, raises the CTA's abort
+// flag, lets copies in flight land and leaves; the other CTAs run into their own limits or see the
+// flag at their next wait and leave too.  The launch is cooperative, so all CTAs are resident together.
 #include "gemv_device.cuh"
 #include "kernels.cuh"
 
@@ -104,6 +112,8 @@ __device__ __forceinline__ void prefetch_line_l2(const void* p) { asm volatile("
 template <int W>
 __device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const Ring& R, uint32_t& kfill, unsigned long long* pstamp = nullptr) {
     constexpr uint32_t UB = 256u * W + 80u;
+    const uint32_t r_base = R.base, r_full = R.full, r_empty = R.empty;
+    const int r_NS = R.NS, r_skip = R.skip;
     const int lane = threadIdx.x & 31;
     const CtaRange c = sk_cta_range(P);
     const SkJob& J = P.job[c.ji];
@@ -137,7 +147,7 @@ __device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const
                 bool free_now = false;
 #pragma unroll 1
                 for (uint32_t piece = 0; piece < SK_WAIT_LIMIT / 32u && !free_now && !ring_aborted(R); piece++)
-                    free_now = mbar_wait_u32(R.empty + 8u * slot, (round - 1u) & 1u, 32u);
+                    free_now = mbar_wait_u32(r_empty + 8u * slot, (round - 1u) & 1u, 32u);
                 if (!free_now) {
                     if (!ring_aborted(R)) ring_abort(R, 1002);
                     good = 0;
@@ -149,17 +159,17 @@ __device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const
         if (!good) return false;
         const int left = min(SU, n - k * SU);
         if (pstamp && lane == 0) { waited += clock64() - w0; if (k == 0) pstamp[11] = clock64(); pstamp[12] = clock64(); pstamp[13] = waited; }
-        if (R.skip & 2) {  // debug: no copies at all, the consumers multiply whatever the slot holds
-            if (lane == 0) mbar_arrive_u32(R.full + 8u * slot);
+        if (r_skip & 2) {  // debug: no copies at all, the consumers multiply whatever the slot holds
+            if (lane == 0) mbar_arrive_u32(r_full + 8u * slot);
         } else {
-            if (lane == 0) mbar_expect_tx_u32(R.full + 8u * slot, (uint32_t)left * UB);
-            uint32_t dst = R.base + slot * R.slot_bytes;
+            if (lane == 0) mbar_expect_tx_u32(r_full + 8u * slot, (uint32_t)left * UB);
+            uint32_t dst = r_base + slot * ((uint32_t)SU * UB);
             walk(cf, left, [&](const uint32_t* src, uint32_t bytes) {
-                if (lane == 0) bulk_g2s_u32(dst, src, bytes, R.full + 8u * slot);
+                if (lane == 0) bulk_g2s_u32(dst, src, bytes, r_full + 8u * slot);
                 dst += bytes;
             });
         }
-        if (++slot == (uint32_t)R.NS) { slot = 0; round++; }
+        if (++slot == (uint32_t)r_NS) { slot = 0; round++; }
     }
     kfill = slot | (round << 16);
     return true;
@@ -177,13 +187,7 @@ __device__ __forceinline__ void warm_operands(const SkParams& P, int NSEG) {
     for (int s = 0; s < NSEG; s++)
         if (J.seg[s].nw)
             for (int i = blockIdx.x + lane * gridDim.x; i < lines; i += 32 * gridDim.x) prefetch_line_l2(J.seg[s].nw + (size_t)i * 32);
-    if (J.epi == EPI_RESID && c.nt > 0) {
-        const int row0 = c.tau_first * 16, nrows = min(c.nt * 16, J.rows - row0);
-        for (int i = lane * 32; i < nrows; i += 32 * 32) {
-            prefetch_line_l2(J.out + row0 + i);
-            for (int sc = 0; sc < J.nscatter; sc++) prefetch_line_l2(J.sidx[sc] + row0 + i);
-        }
-    }
+
 }
 
 // Consumer side of one GEMV phase: stage the digits, multiply, reduce, epilogue.  Returns false
@@ -203,24 +207,32 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
     const int G = J.G, Gs = nseg * G, nt = cr.nt, tau_first = cr.tau_first;
     const int n = nt * Gs;
     constexpr int SU = 2 * SK_WARPS;  // units per slot fill: a pair per warp
-    const int NS = R.NS;
+    constexpr uint32_t SLOT_BYTES = (uint32_t)SU * UB;
+    // the ring's constants as plain values: the record itself lives in the caller's local memory, and a load from it
+    // inside the main loop would cost a trip to the L2 whenever the small L1 has dropped the line
+    const uint32_t r_base = R.base, r_full = R.full, r_empty = R.empty, r_zeros = R.zeros, r_abort = R.abort_flag;
+    const int NS = R.NS, skip = R.skip;
+    auto aborted = [&]() { return lds_volatile_i32(r_abort) != 0; };
+    uint32_t kb = kbase;
     const int nslots = (n + SU - 1) / SU;
 
     const int dstride = J.in + 16;
     uint8_t* digits = smem;                                              // [nseg][4][in + 16]
     int* ss = reinterpret_cast<int*>(smem + (size_t)nseg * 4 * dstride);  // [nseg][G][2]
     float* pg = reinterpret_cast<float*>(ss + Gs * 2);                   // [nseg][G] 2^-(26 - E_g)
-    float* partial = pg + Gs;                                            // [nt][SK_WARPS][ROWS]
+    const bool natural = J.seg[0].perm != nullptr;                       // the input arrives in natural order and is gathered into the K order
+    float* xs = pg + ((Gs + 3) & ~3);                                    // [in] the natural-order vector as plain floats (only then); 16-byte aligned
+    float* partial = xs + (natural ? J.in : 0);                          // [nt][SK_WARPS][ROWS]
 
     for (int i = threadIdx.x; i < nt * SK_WARPS * ROWS; i += SK_THREADS) partial[i] = 0.f;
     bool stage_failed = false;  // a poll for a tagged input gave up
     float sq = 0.f;
     if (stamp && threadIdx.x == 0) stamp[16] = clock64();
     if (n > 0) {
-        // w1 and w3 read the same x, each in its own K order: the sum of squares is taken from the first
-        for (int s = 0; s < nseg; s++)
-            stage_groups<W>(J.seg[s], J.in, digits + (size_t)s * 4 * dstride, ss + s * G * 2, pg + s * G, tagbase | (uint32_t)J.in_phase[s], s == 0, &sq,
-                            &stage_failed, s == 0 ? stamp : nullptr);
+        if (natural)  // w1 and w3 read the same x, each through its own g_index
+            sq = stage_natural<W>(J.seg, nseg, J.in, G, digits, ss, pg, xs, tagbase | (uint32_t)J.in_phase[0], &stage_failed, stamp);
+        else          // the producer's row order is this matrix's K order (w2 after w1/w3)
+            stage_groups<W>(J.seg[0], J.in, digits, ss, pg, tagbase | (uint32_t)J.in_phase[0], true, &sq, &stage_failed, stamp);
         if (stamp && threadIdx.x == 0) stamp[17] = clock64();
         sq = tk_warp_sum(sq);
         if (lane == 0) red[warp] = sq;
@@ -233,18 +245,13 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
     }
     if (stamp && threadIdx.x == 0) stamp[1] = clock64();
 
-    // Epilogue operands of this warp's first tile that are known long before the epilogue (the scatter
-    // positions, and the residual value, written phases ago): requested now, so that their trip to the
-    // L2 overlaps the main loop.
+    // The residual value of this warp's first tile was written phases ago: requested now, so that its trip
+    // to the L2 overlaps the main loop.
     const int e_row = (tau_first + warp) * 16 + (lane & 15);
     const bool e_pre = nseg == 1 && warp < nt && lane < 16 && e_row < J.rows && J.epi == EPI_RESID;
-    int e_idx[3] = {0, 0, 0};
     unsigned long long e_res = 0;
     if (e_pre) {
-#pragma unroll
-        for (int s = 0; s < 3; s++)
-            if (s < J.nscatter) e_idx[s] = __ldg(J.sidx[s] + e_row);
-        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(e_res) : "l"(reinterpret_cast<const unsigned long long*>(J.out) + e_row) : "memory");
+        asm volatile(L2_POLL_LD ".u64 %0, [%1];" : "=l"(e_res) : "l"(reinterpret_cast<const unsigned long long*>(J.out) + e_row) : "memory");
     }
 
     // ---- main loop.  In every slot fill this warp owns units 2*warp and 2*warp + 1.  With four warps
@@ -276,12 +283,12 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
     };
     const int zshift = 4 * r;
     // 32-bit shared-space addresses of everything the loop touches
-    const uint32_t ring_a = R.base + (uint32_t)(2 * warp) * UB;   // this warp's pair inside slot 0
-    const uint32_t full_a = R.full, empty_a = R.empty;
+    const uint32_t ring_a = r_base + (uint32_t)(2 * warp) * UB;   // this warp's pair inside slot 0
+    const uint32_t full_a = r_full, empty_a = r_empty;
     const uint32_t ss_a = smem_u32(ss) + 4u * (uint32_t)(t & 1);
     const uint32_t pg_a = smem_u32(pg);
     // this lane's digits of the group at position gg; lanes r >= 4 (MMA columns 4..7) read zeros
-    const uint32_t dg_a = r < 4 ? smem_u32(digits) + (uint32_t)(r * dstride + t * (8 * W)) : R.zeros;
+    const uint32_t dg_a = r < 4 ? smem_u32(digits) + (uint32_t)(r * dstride + t * (8 * W)) : r_zeros;
     const uint32_t dmul = r < 4 ? 1u : 0u;
     constexpr uint32_t META = 256u * W;  // scales, then the two zero-point words
     auto digits_of = [&](int gg) {
@@ -357,7 +364,7 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
     // position of this warp's first unit of the current fill; advanced by SU units per fill
     int tl0 = 0, gg0 = 2 * warp;
     while (gg0 >= Gs) { gg0 -= Gs; tl0++; }
-    uint32_t fslot = kbase & 0xFFFFu, fpar = kbase >> 16;  // slot and parity of the next fill, carried from phase to phase
+    uint32_t fslot = kb & 0xFFFFu, fpar = kb >> 16;  // slot and parity of the next fill, carried from phase to phase
 #pragma unroll 1
     for (int k = 0; k < nslots; k++) {
         const uint32_t slot = fslot;
@@ -366,16 +373,16 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
         bool got = mbar_try_wait_u32(full_a + 8u * slot, fpar);
         if (stamp && threadIdx.x == 0 && !got) stamp[15] += 1;
         if (!__all_sync(0xffffffffu, got)) {  // not there yet: the bounded wait
-            got = !ring_aborted(R) && mbar_wait_u32(full_a + 8u * slot, fpar);
+            got = !aborted() && mbar_wait_u32(full_a + 8u * slot, fpar);
             if (!__all_sync(0xffffffffu, got)) {
-                if (!ring_aborted(R)) ring_abort(R, 1001);
+                if (!aborted()) ring_abort(R, 1001);
                 ok = false;
                 break;
             }
         }
         if (stamp && threadIdx.x == 0) stamp[14] += clock64() - cw0;
-        if (!(R.skip & 1)) {
-            const uint32_t rec0 = ring_a + slot * R.slot_bytes;
+        if (!(skip & 1)) {
+            const uint32_t rec0 = ring_a + slot * SLOT_BYTES;
             int tl1 = tl0, gg1 = gg0 + 1;
             if (gg1 == Gs) { gg1 = 0; tl1++; }
             int c0[4], c1[4];
@@ -400,7 +407,7 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
     if (stamp && threadIdx.x == 0) { stamp[2] = clock64(); stamp[9] = (unsigned long long)nslots; }
     consumer_sync();
     if (stamp && threadIdx.x == 0) stamp[18] = clock64();
-    if (ring_aborted(R)) return false;
+    if (aborted()) return false;
 
     const float rs = oscale[0];
     // Results leave as (value, tag) pairs: whoever needs them polls for the tag of this phase.
@@ -419,27 +426,14 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
             y = y * (1.0f / (1.0f + expf(-y))) * y3;
         }
         if (lane >= 16 || row >= J.rows) continue;
-        int ndst = 1;
-        const bool pre = e_pre && tl == warp;
-        int idx0 = e_idx[0], idx1 = e_idx[1], idx2 = e_idx[2];
-        if (nseg == 1 && J.epi == EPI_RESID) {  // residual add (src/models.rs:47-51) + copies in the next consumers' K orders
-            ndst += J.nscatter;
-            if (!pre) {
-                if (J.nscatter > 0) idx0 = __ldg(J.sidx[0] + row);
-                if (J.nscatter > 1) idx1 = __ldg(J.sidx[1] + row);
-                if (J.nscatter > 2) idx2 = __ldg(J.sidx[2] + row);
-            }
+        if (nseg == 1 && J.epi == EPI_RESID) {  // residual add (src/models.rs:47-51)
+            const bool pre = e_pre && tl == warp;
             float res = __uint_as_float((uint32_t)e_res);
             if (!pre || (uint32_t)(e_res >> 32) != (tagbase | (uint32_t)J.resid_phase))  // not the early copy: poll
                 fine = load_tagged(J.out, row, tagbase | (uint32_t)J.resid_phase, res) && fine;
             y += res;
         }
-#pragma unroll 1
-        for (int d = 0; d < ndst; d++) {
-            float* base = d == 0 ? J.out : J.sdst[d - 1];
-            const int at = d == 0 ? row : d == 1 ? idx0 : d == 2 ? idx1 : idx2;
-            store_tagged_all(tk, J.bcast, base, at, y, out_tag);
-        }
+        store_tagged_all(tk, J.bcast, J.out, row, y, out_tag);  // a tile is one 128-byte line: one writer per line
     }
     if (stamp && threadIdx.x == 0) stamp[20] = clock64();
     if (!fine) ring_abort(R, 1008);
@@ -456,7 +450,6 @@ __device__ __forceinline__ void embed_phase(const EmbedParams& p, uint32_t out_t
     for (int i = blockIdx.x * SK_THREADS + threadIdx.x; i < p.dim; i += gridDim.x * SK_THREADS) {
         const float v = __ldg(p.table + (size_t)token * p.dim + i);
         store_tagged(p.x, i, v, out_tag);
-        for (int s = 0; s < p.nscatter; s++) store_tagged(p.sdst[s], __ldg(p.sidx[s] + i), v, out_tag);
     }
 }
 
@@ -528,9 +521,9 @@ __device__ __forceinline__ bool load_tagged3(const unsigned long long* pa, const
 #pragma unroll 1
     for (uint32_t it = 0; it < TAG_POLL_LIMIT; it++) {
         unsigned long long wa, wm, wl;
-        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(wa) : "l"(pa) : "memory");
-        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(wm) : "l"(pm) : "memory");
-        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(wl) : "l"(pl) : "memory");
+        asm volatile(L2_POLL_LD ".u64 %0, [%1];" : "=l"(wa) : "l"(pa) : "memory");
+        asm volatile(L2_POLL_LD ".u64 %0, [%1];" : "=l"(wm) : "l"(pm) : "memory");
+        asm volatile(L2_POLL_LD ".u64 %0, [%1];" : "=l"(wl) : "l"(pl) : "memory");
         if ((uint32_t)(wa >> 32) == tag && (uint32_t)(wm >> 32) == tag && (uint32_t)(wl >> 32) == tag) {
             a = __uint_as_float((uint32_t)wa); m = __uint_as_float((uint32_t)wm); l = __uint_as_float((uint32_t)wl);
             return true;

@@ -99,7 +99,12 @@ def qlinear_matvec(qweight, qzeros, scales, g_index, group_size, x):
     out_f, in_f = qweight.shape[0], qweight.shape[1] * 8
     xb = x.reshape(-1, in_f)
     y = np.zeros((xb.shape[0], out_f), np.float32)
-    lib().orc_qlinear_matvec(in_f, out_f, group_size, _i(qweight), _i(qzeros), _f(scales), _i(g_index), xb.shape[0], _f(xb), _f(y))
+    # the restated matvec<B> holds at most 64 rows (the reference's largest prefill chunk); rows are independent of one another
+    for b0 in range(0, xb.shape[0], 64):
+        part = np.ascontiguousarray(xb[b0:b0 + 64])
+        out = np.zeros((part.shape[0], out_f), np.float32)
+        lib().orc_qlinear_matvec(in_f, out_f, group_size, _i(qweight), _i(qzeros), _f(scales), _i(g_index), part.shape[0], _f(part), _f(out))
+        y[b0:b0 + 64] = out
     return y[0] if x.ndim == 1 else y
 
 

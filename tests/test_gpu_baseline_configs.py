@@ -64,7 +64,7 @@ def test_text_generate_matches_generate_ids(l2, tmp_path):
     # generate(model, tokenizer, prompt, steps, random, temperature) (src/inference.rs:49-57, src/lib.rs:111-131):
     # encodes " " + prompt, runs the id-level loop and maps ids to pieces with the leading-space rule after START
     cfg = tiny_config(l2, group_size=64, n_kv_heads=1)
-    letters = " Theonlyhigabcdfmprsuvw"
+    letters = " Theonlytigabcdfmprsuvw"
     vocab = [("<f%d>" % i, 0.0) for i in range(260)] + [(ch, -10.0 - i) for i, ch in enumerate(letters)]
     vocab += [(" T", -1.0), ("he", -1.5), (" The", -0.5), (" o", -2.0), ("nl", -2.5), (" on", -1.8), ("ly", -2.2), (" only", -0.7), (" th", -1.2), ("in", -1.4), ("ing", -0.9), (" thing", -0.6)]
     vocab += [("<p%d>" % i, -50.0) for i in range(cfg.vocab_size - len(vocab))]
