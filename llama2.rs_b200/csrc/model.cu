@@ -482,10 +482,17 @@ static int plan_token(l2_state* s) {
         fixed = std::max(fixed, sk_smem_fixed(L.p.job[0].in, max_g, L.nseg, L.p.ptiles) + (((size_t)L.nseg * max_g * 4 + 15) & ~(size_t)15) + (which != 3 ? (size_t)L.p.job[0].in * 4 : 0));
     }
     fixed = (fixed + 127) & ~(size_t)127;
-    const size_t budget = 222 * 1024;
     const int su = 2 * SK_WARPS;  // unit records per slot fill: every consumer warp takes one pair
+    // Shared memory: the next smaller carve-out (196 KB) leaves 60 KB of L1 instead of 28 KB, which the kernel's local
+    // memory (stack, the few spilled registers of 544 threads) and read-only operands need more than a fourth or fifth
+    // ring slot (measured: 3 slots of 35 KB beat 5 on the 7B model); the largest carve-out only where the ring would
+    // otherwise be shorter than three slots.
     int slots = 0;
-    if (fixed < budget) slots = (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(c.group_size, su));
+    size_t budget = 190 * 1024;
+    for (int attempt = 0; attempt < 2; attempt++, budget = 222 * 1024) {
+        slots = fixed < budget ? (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(c.group_size, su)) : 0;
+        if (slots >= 3) break;
+    }
     if (slots < 2) return fail(L2_EINVAL, "the token kernel needs %zu bytes of shared memory before its weight ring", fixed);
     if (const char* e = getenv("L2_SK_SLOTS")) slots = std::max(2, std::min(slots, atoi(e)));
     s->tk = TokenParams{};
@@ -601,7 +608,7 @@ static int build_phase_table(l2_state* s, int kind) {
                 a.bcast = direct;
                 a.part = reinterpret_cast<float*>(s->t_part);
                 a.max_split = s->tk_max_split;
-                a.split_min = 64;  // positions a split holds at least: one round of loads of a CTA
+                a.split_min = 32;  // positions a split holds at least (measured: 16..32 is best, a split costs a second exchange)
                 if (const char* e = getenv("L2_TK_SPLIT_MIN")) a.split_min = std::max(1, atoi(e));  // tuning knob
                 add(PH_ATTN).u.at = a;
             } else if (which == 1) {

@@ -28,6 +28,12 @@
 
 namespace l2 {
 
+// The phase functions have one call site each: inlined, they share the kernel's register allocation and no
+// registers are saved to local memory around a call (with most of the L1 given to shared memory that is a trip to the L2).
+#ifndef L2_TK_PHASE_INLINE
+#define L2_TK_PHASE_INLINE __forceinline__
+#endif
+constexpr int TK_BLOCK = SK_THREADS + 32;  // 16 consumer warps + the producer warp
 constexpr int TK_NREC = 4;                    // phase records buffered in shared memory
 static_assert(sizeof(PhaseRec) % 16 == 0, "phase records travel as bulk copies");
 constexpr uint32_t TK_BAR_LIMIT = 1u << 22;   // polls of the grid barrier before giving up (about a second)
@@ -196,7 +202,7 @@ __device__ __forceinline__ void warm_operands(const SkParams& P, int NSEG) {
 // runs each phase's code once per layer, so what is not shared is fetched from the L2 every time:
 // the instruction cache of an SM holds far less than an unrolled copy per phase type would need).
 template <int W>
-__device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P, const int nseg, uint8_t* smem, const Ring& R, float* red, float* oscale,
+__device__ L2_TK_PHASE_INLINE bool gemv_phase(const TokenParams& tk, const SkParams& P, const int nseg, uint8_t* smem, const Ring& R, float* red, float* oscale,
                                         uint32_t& kbase, unsigned long long* stamp, uint32_t tagbase, int phase) {
     constexpr int GS = 32 * W;
     constexpr uint32_t UB = 256u * W + 80u;
@@ -369,9 +375,7 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
     for (int k = 0; k < nslots; k++) {
         const uint32_t slot = fslot;
         const int m = n - k * SU;  // units of this fill (all of them valid if >= SU)
-        const unsigned long long cw0 = stamp ? clock64() : 0;
         bool got = mbar_try_wait_u32(full_a + 8u * slot, fpar);
-        if (stamp && threadIdx.x == 0 && !got) stamp[15] += 1;
         if (!__all_sync(0xffffffffu, got)) {  // not there yet: the bounded wait
             got = !aborted() && mbar_wait_u32(full_a + 8u * slot, fpar);
             if (!__all_sync(0xffffffffu, got)) {
@@ -380,7 +384,6 @@ __device__ __noinline__ bool gemv_phase(const TokenParams& tk, const SkParams& P
                 break;
             }
         }
-        if (stamp && threadIdx.x == 0) stamp[14] += clock64() - cw0;
         if (!(skip & 1)) {
             const uint32_t rec0 = ring_a + slot * SLOT_BYTES;
             int tl1 = tl0, gg1 = gg0 + 1;
@@ -499,16 +502,16 @@ __device__ __noinline__ void warm_attention(const AttnParams& p, int pos_now, in
         const float4* vc4 = reinterpret_cast<const float4*>(p.vc) + (size_t)kvh * (HS / 4) + lane;
         const size_t rs = (size_t)KV / 4;
 #pragma unroll 1
-        for (int tb = t0; tb < t1; tb += 8) {
-            float4 a[8], b[8];
+        for (int tb = t0; tb < t1; tb += 8) {  // only one word of every 512-byte row is needed to bring the row's lines in
+            float a[8], b[8];
 #pragma unroll
             for (int u = 0; u < 8; u++) {
                 const int tt = min(tb + u, t1 - 1);
-                a[u] = __ldcg(kc4 + (size_t)tt * rs);
-                b[u] = __ldcg(vc4 + (size_t)tt * rs);
+                a[u] = __ldcg(reinterpret_cast<const float*>(kc4 + (size_t)tt * rs));
+                b[u] = __ldcg(reinterpret_cast<const float*>(vc4 + (size_t)tt * rs));
             }
 #pragma unroll
-            for (int u = 0; u < 8; u++) fold += a[u].x + b[u].x;
+            for (int u = 0; u < 8; u++) fold += a[u] + b[u];
         }
     }
     if (fold == 1.2345678e38f && sink) *sink = 1;  // never true in practice; keeps the loads alive
@@ -534,7 +537,7 @@ __device__ __forceinline__ bool load_tagged3(const unsigned long long* pa, const
 }
 
 template <int AG>
-__device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp, uint32_t in_tag,
+__device__ L2_TK_PHASE_INLINE bool attn_phase(const TokenParams& tk, const AttnParams& p, uint8_t* scratch, int pos, unsigned long long* stamp, uint32_t in_tag,
                                         uint32_t out_tag) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* base = reinterpret_cast<float*>(scratch);
@@ -554,7 +557,7 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
     const int nsplit = sp.nsplit, chunk = sp.chunk;
     const int nitems = nkv * nsplit;
     const int KV = p.n_kv_heads * HS;
-    const float inv_div = sqrtf((float)HS);
+    const float rdiv = 1.0f / sqrtf((float)HS);  // the reference divides by sqrt(head_size) (src/models.rs:158); the product differs by at most one ulp
     bool fine = true;  // false when a poll for a tagged input gave up
     constexpr int U = AG >= 4 ? 2 : 4;
     // combine: thread (j0, i) owns element i of heads j0, j0 + 4, ...
@@ -666,14 +669,14 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
                 float mr = -INFINITY;
 #pragma unroll
                 for (int u = 0; u < U; u++) {
-                    sc[u][g] = __fdiv_rn(sc[u][g], inv_div);  // src/models.rs:158
+                    sc[u][g] *= rdiv;
                     if (tb + u < t1) mr = fmaxf(mr, sc[u][g]);
                 }
                 const float mn = fmaxf(m[g], mr);
-                const float corr = expf(m[g] - mn);  // exp(-inf) = 0 on the first round
+                const float corr = __expf(m[g] - mn);  // exp(-inf) = 0 on the first round
                 float pr[U];
 #pragma unroll
-                for (int u = 0; u < U; u++) pr[u] = tb + u < t1 ? expf(sc[u][g] - mn) : 0.f;
+                for (int u = 0; u < U; u++) pr[u] = tb + u < t1 ? __expf(sc[u][g] - mn) : 0.f;
                 float ls = 0.f;
                 float4 as = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -715,7 +718,7 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
             const int w = tid / AG, g = tid % AG;
             if (w < nwarps) {
                 const float mw = sm_m[w][g];
-                sm_m[w][g] = mw == -INFINITY ? 0.f : expf(mw - fmax_g);
+                sm_m[w][g] = mw == -INFINITY ? 0.f : __expf(mw - fmax_g);
             }
             if (w == 0) sm_mx[g] = fmax_g;
         }
@@ -763,7 +766,7 @@ __device__ __noinline__ bool attn_phase(const TokenParams& tk, const AttnParams&
                 for (int s = 0; s < nsplit; s++) mm = fmaxf(mm, mg_m[s]);
                 float ll = 0.f, aa = 0.f;
                 for (int s = 0; s < nsplit; s++) {
-                    const float e = expf(mg_m[s] - mm);
+                    const float e = __expf(mg_m[s] - mm);
                     ll += mg_l[s] * e;
                     aa += mg_a[s * HS + i] * e;
                 }
@@ -942,7 +945,7 @@ __device__ __forceinline__ void select_phase(const SelectParams& p, float* scrat
 // ---- the kernel ------------------------------------------------------------------------------------
 
 template <int W, int AG>
-__global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_constant__ TokenParams tk) {
+__global__ void __launch_bounds__(TK_BLOCK, 1) token_kernel(const __grid_constant__ TokenParams tk) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(16) PhaseRec recs[TK_NREC];
     __shared__ __align__(8) uint64_t full[SK_MAX_SLOTS], empty[SK_MAX_SLOTS], rec_full[TK_NREC];
@@ -1058,8 +1061,8 @@ __global__ void __launch_bounds__(SK_THREADS + 32, 1) token_kernel(const __grid_
         bool fine = true;
         switch (rec.type) {
             case PH_EMBED: embed_phase(rec.u.em, out_tag); break;
-            case PH_GEMV1: ok = gemv_phase<W>(tk, rec.u.sk, 1, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
-            case PH_GEMV2: ok = gemv_phase<W>(tk, rec.u.sk, 2, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
+            case PH_GEMV1:
+            case PH_GEMV2: ok = gemv_phase<W>(tk, rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
             case PH_ATTN: fine = attn_phase<AG>(tk, rec.u.at, smem, tok_pos, stamp, tagbase | (uint32_t)rec.u.at.in_phase, out_tag); break;
             case PH_CLS: fine = cls_phase(rec.u.cl, reinterpret_cast<float*>(smem), red, tagbase | (uint32_t)rec.u.cl.in_phase); break;
             case PH_SELECT: if (blockIdx.x == 0) select_phase(rec.u.se, red); break;
@@ -1120,7 +1123,7 @@ static cudaError_t launch_token_t(const TokenParams& tk, int grid, size_t smem, 
     cudaLaunchConfig_t cfg{};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(SK_THREADS + 32);  // 16 consumer warps + the producer warp
+    cfg.blockDim = dim3(TK_BLOCK);  // 16 consumer warps + the producer warp
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident together: the grid barrier relies on it
