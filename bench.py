@@ -3,9 +3,11 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 7b|13b|70b] [--impl ours|reference]
 
-With N > 1 (launched by torch.distributed.run, one rank per GPU) the default workload stays the 7B one: every rank
-decodes its own token stream (batch-1 decode has nothing to exchange; `scaling` is "weak", `value` the sum over the
-ranks).  `--workload 70b` on N > 1 GPUs shards the 70B model over the ranks (tensor parallel, NCCL all-gathers).
+With one GPU visible the default workload is the 7B configuration the metric is quoted on.  Inside a scaling run (several
+GPUs visible, or launched by torch.distributed.run with one rank per GPU) the default is the 70B configuration, the one
+that shards: tensor parallel over all N ranks (the token kernel stores into every rank's memory over NVLink), at every N
+including 1, so that the per-N values form the strong-scaling curve.  `--workload 7b|13b` on N > 1 GPUs runs independent
+replicas (batch-1 decode of a model that fits one GPU has nothing to exchange; `scaling` is "weak").
 
 A step is one pass of the workload: a seeded random prompt through prefill, then the decode
 loop (the headline configuration for 7B: 32 prompt tokens, 256 greedy tokens).  `value` is decode tok/s with
@@ -40,13 +42,15 @@ TOKEN_KERNEL_TRAFFIC_RATIO = 1.024  # DRAM bytes / algorithmic bytes of the toke
 
 
 def measured_peaks():
+    """(HBM GB/s, dense bf16 TFLOP/s burst, which): the driver-written measurement of this pool's B200s, else the fallback."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
-            return float(json.load(open(path))["hbm_gbs"]), "measured"
+            d = json.load(open(path))
+            return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -103,6 +107,25 @@ def visible_gpus():
     if vis is not None and vis.strip() != "":
         n = min(n, len([v for v in vis.split(",") if v.strip()])) if n else len([v for v in vis.split(",") if v.strip()])
     return n
+
+
+def prefill_report(model, cfg, positions, ms, tp, hbm_peak, tensor_peak, peak_kind):
+    """Batched prefill (the tcgen05 GEMM path) against both rooflines.  Algorithmic flops: 2 * K * N per position and
+    QLinear (the classifier is not run in prefill); algorithmic bytes: the QLinear bytes of one pass over the weights per
+    chunk of up to 64 positions.  The integer GEMM executes 4 digit columns per position (balanced base-128 digits of the
+    activations), i.e. 4x the algorithmic multiply-adds on the int8 pipe."""
+    if positions <= 0 or ms <= 0:
+        return None
+    d, h, L = cfg.dim, cfg.hidden_dim, cfg.n_layers
+    kv = d * cfg.n_kv_heads // cfg.n_heads
+    flops_per_pos = 2.0 * L * (2 * d * d + 2 * d * kv + 3 * d * h)
+    qbytes = float(model.decode_bytes) - 4.0 * cfg.vocab_size * d - 4.0 * (2 * L + 1) * d  # qweight + qzeros + scales of this process's rows
+    passes = positions if tp else (positions + 63) // 64  # tensor-parallel models take the prompt one position at a time
+    tflops = flops_per_pos * positions / (ms * 1e-3) / 1e12
+    gbs = qbytes * passes / (ms * 1e-3) / 1e9
+    return {"positions": positions, "ms": ms, "weight_passes": passes, "tflops": tflops, "tensor_peak_tflops": tensor_peak,
+            "tensor_frac": tflops / tensor_peak, "weight_gbs": gbs, "hbm_frac": gbs / hbm_peak, "peak_kind": peak_kind,
+            "executed_mma_inflation": 1 if tp else 4}
 
 
 def make_prompt(np, n, vocab):
@@ -166,7 +189,8 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(WORKLOADS),
-                    help="auto: 7b (N > 1: independent replicas, weak scaling); 70b on N > 1 GPUs is tensor-parallel over all ranks")
+                    help="auto: 7b when one GPU is visible; 70b inside a scaling run (several GPUs visible or launched by torch.distributed.run), "
+                         "tensor-parallel over all ranks when N > 1.  7b/13b on N > 1 GPUs run as independent replicas")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-warmup", type=int, default=3, help="profiling runs may lower the warm-up floor")
@@ -319,7 +343,7 @@ def main():
         dist.destroy_process_group()
     if rank != 0:
         return
-    peak, peak_kind = measured_peaks()
+    peak, tensor_peak, peak_kind = measured_peaks()
     tok_s = value / streams
     if token_kernel:
         # One persistent kernel per token: it is the dominant (only) kernel.  Algorithmic bytes per launch
@@ -342,6 +366,7 @@ def main():
         "warmup": max(args.min_warmup, args.warmup), "ms_per_step": (decode_ms + prefill_ms) / args.steps, "higher_is_better": True,
         "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32 activations / int4 weights", "data": "synthetic", "config": config,
         "prefill_tok_s": streams * pos0 * args.steps / max(prefill_ms, 1e-9) * 1e3,
+        "prefill": prefill_report(model, cfg, pos0, prefill_ms / args.steps, tp, peak, tensor_peak, peak_kind),
         "decode_ms_per_token": decode_ms / (n_loop * args.steps),
         "roofline": roofline,
         "token_roofline": {"bytes_per_token": model.decode_bytes, "achieved_gbs": model.decode_bytes * tok_s / 1e9,

@@ -392,139 +392,15 @@ __device__ float stage_digits_pair(const SkSeg& sa, const SkSeg& sb, int in, flo
 // Digits: X is written in balanced base 256, X = sum_j d_j 256^j with -128 <= d_j <= 127, which is two
 // integer operations per value: the bytes of (X + 0x80808080) ^ 0x80808080.  All four are legal s8
 // operands of the integer MMA.
-// digits: [4][in + 16], plane 0 the most significant digit; ss: [G][2] digit sums (256 * S0 + S1,
-// 256 * S2 + S3); pg: [G] the factors.
-struct StageLoad { uint4 q[4]; float4 w0, w1; };
+//
+// Layout in shared memory: digits [4 planes][pstride], plane 0 the most significant digit, a plane holding
+// the K orders of the phase's matrices one after the other; sp [groups] records of four words
+// {256 * S0 + S1, f * 2^16, 256 * S2 + S3, f}: the digit sums of the upper and of the lower digit pair, each
+// followed by the factor its MMA columns are scaled with (f = 2^-(26 - E_g); the upper pair weighs 2^16 more).
 
-__device__ __forceinline__ void stage_issue(const SkSeg& sg, int blk, StageLoad& L) {
-    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned long long*>(sg.x) + (size_t)blk * 8);
-#pragma unroll
-    for (int i = 0; i < 4; i++)
-        asm volatile(L2_POLL_LD ".v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(L.q[i].x), "=r"(L.q[i].y), "=r"(L.q[i].z), "=r"(L.q[i].w) : "l"(p + i) : "memory");
-    if (sg.nw) {
-        const float4* n4 = reinterpret_cast<const float4*>(sg.nw);
-        L.w0 = __ldg(n4 + 2 * blk);
-        L.w1 = __ldg(n4 + 2 * blk + 1);
-    }
-}
-__device__ __forceinline__ bool stage_tags_ok(const StageLoad& L, uint32_t tag) {
-    return L.q[0].y == tag && L.q[0].w == tag && L.q[1].y == tag && L.q[1].w == tag && L.q[2].y == tag && L.q[2].w == tag && L.q[3].y == tag && L.q[3].w == tag;
-}
-
+// Turns 8 values of K-order block `blk` into digits and finishes the group's record.
 template <int W>
-__device__ __forceinline__ void stage_groups(const SkSeg& sg, int in, uint8_t* digits, int* ss, float* pg, uint32_t tag, bool want_sq, float* sq_out,
-                                          bool* fail, unsigned long long* stamp = nullptr) {
-    const int nblk = in / 8, stride = in + 16;
-    float sq = 0.f;
-    int blk = threadIdx.x;
-    StageLoad cur, nxt;
-    cur.w0 = cur.w1 = nxt.w0 = nxt.w1 = make_float4(1.f, 1.f, 1.f, 1.f);
-    if (blk < nblk) stage_issue(sg, blk, cur);  // the first block's values and norm weights are on their way together
-#pragma unroll 1
-    for (; (blk & ~31) < nblk; blk += SK_THREADS) {
-        const bool valid = blk < nblk;
-        if (valid && !stage_tags_ok(cur, tag)) {  // not there yet: poll (bounded)
-            uint32_t it = 0;
-#pragma unroll 1
-            do {
-                const float4 w0 = cur.w0, w1 = cur.w1;
-                stage_issue(sg, blk, cur);
-                cur.w0 = w0; cur.w1 = w1;
-            } while (!stage_tags_ok(cur, tag) && ++it < TAG_POLL_LIMIT);
-            if (it >= TAG_POLL_LIMIT) *fail = true;
-        }
-        if (stamp && threadIdx.x == 0 && blk == 0) stamp[21] = clock64();
-        if (blk + SK_THREADS < nblk) stage_issue(sg, blk + SK_THREADS, nxt);  // in flight while this block is turned into digits
-        float v[8] = {__uint_as_float(cur.q[0].x), __uint_as_float(cur.q[0].z), __uint_as_float(cur.q[1].x), __uint_as_float(cur.q[1].z),
-                      __uint_as_float(cur.q[2].x), __uint_as_float(cur.q[2].z), __uint_as_float(cur.q[3].x), __uint_as_float(cur.q[3].z)};
-        if (!valid) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[j] = 0.f;
-        }
-        if (want_sq) sq += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3] + v[4] * v[4] + v[5] * v[5] + v[6] * v[6] + v[7] * v[7];
-        v[0] *= cur.w0.x; v[1] *= cur.w0.y; v[2] *= cur.w0.z; v[3] *= cur.w0.w;
-        v[4] *= cur.w1.x; v[5] *= cur.w1.y; v[6] *= cur.w1.z; v[7] *= cur.w1.w;
-        float mx = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
-                         fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
-#pragma unroll
-        for (int o = 1; o < 4 * W; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        const float P = stage_scale(mx);
-        if (stamp && threadIdx.x == 0 && blk == 0) stamp[22] = clock64() + (P == 1.2345f ? 1 : 0);
-        uint32_t E[8];  // per element: bytes d3, d2, d1, d0 (least significant digit first)
-#pragma unroll
-        for (int j = 0; j < 8; j++) E[j] = ((uint32_t)__float2int_rn(v[j] * P) + 0x80808080u) ^ 0x80808080u;
-        // 4x4 byte transposes: words of one digit for inputs (0,2,4,6) and (1,3,5,7), the order in
-        // which the nibbles of a weight word separate into its low and high halves
-        uint32_t lo[4], hi[4];
-        {
-            const uint32_t a = __byte_perm(E[0], E[2], 0x5140), b2 = __byte_perm(E[0], E[2], 0x7362);
-            const uint32_t c = __byte_perm(E[4], E[6], 0x5140), d = __byte_perm(E[4], E[6], 0x7362);
-            lo[3] = __byte_perm(a, c, 0x5410); lo[2] = __byte_perm(a, c, 0x7632);
-            lo[1] = __byte_perm(b2, d, 0x5410); lo[0] = __byte_perm(b2, d, 0x7632);
-        }
-        {
-            const uint32_t a = __byte_perm(E[1], E[3], 0x5140), b2 = __byte_perm(E[1], E[3], 0x7362);
-            const uint32_t c = __byte_perm(E[5], E[7], 0x5140), d = __byte_perm(E[5], E[7], 0x7362);
-            hi[3] = __byte_perm(a, c, 0x5410); hi[2] = __byte_perm(a, c, 0x7632);
-            hi[1] = __byte_perm(b2, d, 0x5410); hi[0] = __byte_perm(b2, d, 0x7632);
-        }
-        int sum[4];
-#pragma unroll
-        for (int p = 0; p < 4; p++) {
-            if (valid) *reinterpret_cast<uint2*>(digits + (size_t)p * stride + (size_t)blk * 8) = make_uint2(lo[p], hi[p]);
-            sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
-        }
-        // a group is 4*W consecutive blocks = 4*W consecutive lanes: sum them with shuffles
-        int s01 = 256 * sum[0] + sum[1], s23 = 256 * sum[2] + sum[3];
-#pragma unroll
-        for (int o = 1; o < 4 * W; o <<= 1) {
-            s01 += __shfl_xor_sync(0xffffffffu, s01, o);
-            s23 += __shfl_xor_sync(0xffffffffu, s23, o);
-        }
-        if (valid && (threadIdx.x & (4 * W - 1)) == 0) {
-            const int g = blk / (4 * W);
-            *reinterpret_cast<int2*>(ss + 2 * g) = make_int2(s01, s23);
-            pg[g] = __uint_as_float((254u << 23) - __float_as_uint(P));  // 1 / P, exact
-        }
-        if (stamp && threadIdx.x == 0 && blk == 0) stamp[23] = clock64();
-        cur = nxt;
-    }
-    if (want_sq) *sq_out = sq;
-}
-
-// ---- staging of a vector that arrives in natural order and is consumed in a matrix's K order -------
-// Values cross CTAs fastest when every 128-byte line has one writer: a vector whose elements are scattered
-// by their producers into a consumer's K order (eight writers per line polled) takes about three times as
-// long to arrive as the same vector written tile by tile.  So producers store in natural order, and the
-// consumer (1) polls the natural vector into shared memory as plain floats, taking the sum of squares on the
-// way, and (2) gathers its K order from there through the matrix's g_index while it writes the digits.
-
-// (1) n / 8 blocks of 8 tagged values, times the norm weight (natural order, or null) -> xs[n]; returns this
-// thread's share of the sum of squares of the raw values.
-__device__ __forceinline__ float stage_poll_natural(const void* x_tagged, const float* nw_natural, int n, float* xs, uint32_t tag, bool* fail) {
-    const int nblk = n / 8;
-    float sq = 0.f;
-#pragma unroll 1
-    for (int blk = threadIdx.x; blk < nblk; blk += SK_THREADS) {
-        float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
-        if (nw_natural) {  // requested before the poll: it does not depend on the awaited values
-            w0 = __ldg(reinterpret_cast<const float4*>(nw_natural) + 2 * blk);
-            w1 = __ldg(reinterpret_cast<const float4*>(nw_natural) + 2 * blk + 1);
-        }
-        float4 v0, v1;
-        if (!load_tagged8(x_tagged, (size_t)blk * 8, tag, v0, v1)) *fail = true;
-        sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
-        v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
-        v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
-        reinterpret_cast<float4*>(xs)[2 * blk] = v0;
-        reinterpret_cast<float4*>(xs)[2 * blk + 1] = v1;
-    }
-    return sq;
-}
-
-// Turns 8 values of K-order block `blk` into balanced base-256 digits (see stage_groups) and finishes the group.
-template <int W>
-__device__ __forceinline__ void stage_emit8(float (&v)[8], bool valid, int blk, uint8_t* digits, int stride, int* ss, float* pg) {
+__device__ __forceinline__ void stage_emit8(float (&v)[8], bool valid, int blk, uint8_t* digits, int pstride, uint4* sp) {
     float mx = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
                      fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
 #pragma unroll
@@ -551,7 +427,7 @@ __device__ __forceinline__ void stage_emit8(float (&v)[8], bool valid, int blk, 
     int sum[4];
 #pragma unroll
     for (int p = 0; p < 4; p++) {
-        if (valid) *reinterpret_cast<uint2*>(digits + (size_t)p * stride + (size_t)blk * 8) = make_uint2(lo[p], hi[p]);
+        if (valid) *reinterpret_cast<uint2*>(digits + (size_t)p * pstride + (size_t)blk * 8) = make_uint2(lo[p], hi[p]);
         sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
     }
     // a group is 4*W consecutive blocks = 4*W consecutive lanes: sum them with shuffles
@@ -562,30 +438,82 @@ __device__ __forceinline__ void stage_emit8(float (&v)[8], bool valid, int blk, 
         s23 += __shfl_xor_sync(0xffffffffu, s23, o);
     }
     if (valid && (threadIdx.x & (4 * W - 1)) == 0) {
-        const int g = blk / (4 * W);
-        *reinterpret_cast<int2*>(ss + 2 * g) = make_int2(s01, s23);
-        pg[g] = __uint_as_float((254u << 23) - __float_as_uint(P));  // 1 / P, exact
+        const uint32_t f = (254u << 23) - __float_as_uint(P);  // 1 / P, exact (P is a power of two)
+        sp[blk / (4 * W)] = make_uint4((uint32_t)s01, f + (16u << 23), (uint32_t)s23, f);
     }
+}
+
+// A vector that its producers already write in this matrix's K order (w2 after w1/w3): polled block by block and
+// turned into digits at once.  Returns this thread's share of the sum of squares.
+template <int W>
+__device__ __forceinline__ float stage_direct(const void* x_tagged, int in, uint8_t* digits, int pstride, uint4* sp, uint32_t tag, bool* fail,
+                                              unsigned long long* stamp = nullptr) {
+    const int nblk = in / 8;
+    float sq = 0.f;
+#pragma unroll 1
+    for (int blk = threadIdx.x; (blk & ~31) < nblk; blk += SK_THREADS) {
+        const bool valid = blk < nblk;
+        float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+        if (valid && !load_tagged8(x_tagged, (size_t)blk * 8, tag, v0, v1)) *fail = true;
+        if (stamp && threadIdx.x == 0 && blk == 0) stamp[21] = clock64();
+        float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        sq += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3] + v[4] * v[4] + v[5] * v[5] + v[6] * v[6] + v[7] * v[7];
+        stage_emit8<W>(v, valid, blk, digits, pstride, sp);
+    }
+    if (stamp && threadIdx.x == 0) stamp[23] = clock64();
+    return sq;
+}
+
+// ---- staging of a vector that arrives in natural order and is consumed in a matrix's K order -------
+// Values cross CTAs fastest when every 128-byte line has one writer: a vector whose elements are scattered
+// by their producers into a consumer's K order (eight writers per line polled) takes about three times as
+// long to arrive as the same vector written tile by tile.  So producers store in natural order, and the
+// consumer (1) polls the natural vector into shared memory as plain floats, applying the norm weight and
+// taking the sum of squares on the way, and (2) gathers its K order from there through the matrix's g_index
+// while it writes the digits.
+
+// (1) n / 8 blocks of 8 tagged values, times the norm weight (natural order, or null) -> xs[n]; returns this
+// thread's share of the sum of squares of the raw values.
+__device__ __forceinline__ float stage_poll_natural(const void* x_tagged, const float* nw_natural, int n, float* xs, uint32_t tag, bool* fail) {
+    const int nblk = n / 8;
+    float sq = 0.f;
+#pragma unroll 1
+    for (int blk = threadIdx.x; blk < nblk; blk += SK_THREADS) {
+        float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
+        if (nw_natural) {  // requested before the poll: it does not depend on the awaited values
+            w0 = __ldg(reinterpret_cast<const float4*>(nw_natural) + 2 * blk);
+            w1 = __ldg(reinterpret_cast<const float4*>(nw_natural) + 2 * blk + 1);
+        }
+        float4 v0, v1;
+        if (!load_tagged8(x_tagged, (size_t)blk * 8, tag, v0, v1)) *fail = true;
+        sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+        v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
+        v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
+        reinterpret_cast<float4*>(xs)[2 * blk] = v0;
+        reinterpret_cast<float4*>(xs)[2 * blk + 1] = v1;
+    }
+    return sq;
 }
 
 // (2) K-order block b of a matrix: positions perm[8b .. 8b+7] of xs (16-bit indices: IN < 65536).
 template <int W>
-__device__ __forceinline__ void gather_emit(const uint4& idx, const float* xs, bool valid, int blk, uint8_t* digits, int stride, int* ss, float* pg) {
+__device__ __forceinline__ void gather_emit(const uint4& idx, const float* xs, bool valid, int blk, uint8_t* digits, int pstride, uint4* sp) {
     float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (valid) {
         v[0] = xs[idx.x & 0xFFFFu]; v[1] = xs[idx.x >> 16]; v[2] = xs[idx.y & 0xFFFFu]; v[3] = xs[idx.y >> 16];
         v[4] = xs[idx.z & 0xFFFFu]; v[5] = xs[idx.z >> 16]; v[6] = xs[idx.w & 0xFFFFu]; v[7] = xs[idx.w >> 16];
     }
-    stage_emit8<W>(v, valid, blk, digits, stride, ss, pg);
+    stage_emit8<W>(v, valid, blk, digits, pstride, sp);
 }
 
 // The whole staging of a GEMV phase whose input arrives in natural order: nseg matrices (w1 with w3) read the
 // same vector, each through its own g_index (seg[s].perm: 16-bit indices here); seg[0].nw is the norm weight
-// in natural order.  Returns this thread's share of the sum of squares.
+// in natural order.  Matrix s occupies positions [s * in, (s + 1) * in) of a digit plane and groups
+// [s * G, (s + 1) * G) of sp.  Returns this thread's share of the sum of squares.
 template <int W>
-__device__ __forceinline__ float stage_natural(const SkSeg* seg, int nseg, int in, int G, uint8_t* digits, int* ss, float* pg, float* xs, uint32_t tag, bool* fail,
-                                               unsigned long long* stamp = nullptr) {
-    const int nblk = in / 8, stride = in + 16;
+__device__ __forceinline__ float stage_natural(const SkSeg* seg, int nseg, int in, int G, uint8_t* digits, int pstride, uint4* sp, float* xs, uint32_t tag,
+                                               bool* fail, unsigned long long* stamp = nullptr) {
+    const int nblk = in / 8;
     // the indices of this thread's first K-order block of each matrix: requested before the vector is awaited
     uint4 first0 = make_uint4(0, 0, 0, 0), first1 = first0;
     const int blk0 = threadIdx.x;
@@ -600,12 +528,11 @@ __device__ __forceinline__ float stage_natural(const SkSeg* seg, int nseg, int i
 #pragma unroll
     for (int s = 0; s < 2; s++) {
         if (s >= nseg) break;
-        uint8_t* dg = digits + (size_t)s * 4 * stride;
 #pragma unroll 1
         for (int blk = blk0; (blk & ~31) < nblk; blk += SK_THREADS) {
             uint4 idx = s ? first1 : first0;
             if (blk != blk0 && blk < nblk) idx = __ldg(reinterpret_cast<const uint4*>(seg[s].perm) + blk);
-            gather_emit<W>(idx, xs, blk < nblk, blk, dg, stride, ss + s * G * 2, pg + s * G);
+            gather_emit<W>(idx, xs, blk < nblk, blk, digits + (size_t)s * in, pstride, sp + s * G);
         }
     }
     if (stamp && threadIdx.x == 0) stamp[23] = clock64();

@@ -197,6 +197,7 @@ cudaError_t launch_token(const TokenParams& tk, int group_size, int attn_groups,
 cudaError_t token_set_poll_limit(unsigned polls);  // polls of a tagged input before giving up; 0 = default
 cudaError_t token_init(int max_optin);     // max_optin: opt-in shared memory per block of the device
 size_t token_attn_scratch_bytes(int ag);   // shared memory the attention phase needs
+size_t token_gemv_smem(int in, int G, int nseg, int ptiles, bool natural);  // shared memory a GEMV phase of the token kernel needs in front of the ring
 
 void launch_embed(const EmbedParams& p, cudaStream_t st, bool pdl);
 // `p` points to device memory: the kernel copies the record into shared memory with one cooperative load

@@ -478,8 +478,7 @@ static int plan_token(l2_state* s) {
         const SkLaunch& L = s->plans[which];  // every layer has the same shapes
         int max_g = 0;
         for (int i = 0; i < L.p.njobs; i++) max_g = std::max(max_g, L.p.job[i].G);
-        // + one scaling factor per group; + the input vector as plain floats where it arrives in natural order (all but w2)
-        fixed = std::max(fixed, sk_smem_fixed(L.p.job[0].in, max_g, L.nseg, L.p.ptiles) + (((size_t)L.nseg * max_g * 4 + 15) & ~(size_t)15) + (which != 3 ? (size_t)L.p.job[0].in * 4 : 0));
+        fixed = std::max(fixed, token_gemv_smem(L.p.job[0].in, max_g, L.nseg, L.p.ptiles, which != 3));  // all inputs but w2's arrive in natural order
     }
     fixed = (fixed + 127) & ~(size_t)127;
     const int su = 2 * SK_WARPS;  // unit records per slot fill: every consumer warp takes one pair
@@ -489,6 +488,7 @@ static int plan_token(l2_state* s) {
     // otherwise be shorter than three slots.
     int slots = 0;
     size_t budget = 190 * 1024;
+    if (const char* e = getenv("L2_TK_SMEM_KB")) budget = (size_t)std::max(64, std::min(222, atoi(e))) * 1024;  // tuning knob
     for (int attempt = 0; attempt < 2; attempt++, budget = 222 * 1024) {
         slots = fixed < budget ? (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(c.group_size, su)) : 0;
         if (slots >= 3) break;

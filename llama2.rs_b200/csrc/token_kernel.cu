@@ -201,50 +201,57 @@ __device__ __forceinline__ void warm_operands(const SkParams& P, int NSEG) {
 // pairs w1 with w3 (SwiGLU).  One copy of this code serves every GEMV phase of the token (the kernel
 // runs each phase's code once per layer, so what is not shared is fetched from the L2 every time:
 // the instruction cache of an SM holds far less than an unrolled copy per phase type would need).
+// Shared memory in front of the weight ring that a GEMV phase needs (host side of the carve-up in gemv_phase).
+size_t token_gemv_smem(int in, int G, int nseg, int ptiles, bool natural) {
+    size_t b = (size_t)4 * ((size_t)nseg * in + 16);       // digit planes
+    b += (size_t)nseg * G * 16;                            // group records
+    if (natural) b += (size_t)in * 4;                      // the natural-order vector as plain floats
+    b += (size_t)ptiles * SK_WARPS * 32 * 4;               // tile sums per warp
+    return b;
+}
+
 template <int W>
 __device__ L2_TK_PHASE_INLINE bool gemv_phase(const TokenParams& tk, const SkParams& P, const int nseg, uint8_t* smem, const Ring& R, float* red, float* oscale,
-                                        uint32_t& kbase, unsigned long long* stamp, uint32_t tagbase, int phase) {
+                                              uint32_t& kbase, unsigned long long* stamp, uint32_t tagbase, int phase) {
     constexpr int GS = 32 * W;
     constexpr uint32_t UB = 256u * W + 80u;
-    const int ROWS = 16 * nseg;
+    constexpr int SU = 2 * SK_WARPS;  // units per slot fill: a pair per warp
+    constexpr uint32_t SLOT_BYTES = (uint32_t)SU * UB;
+    constexpr int PROWS = 32;         // tile sums per (tile, warp): 16 rows of up to two matrices
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const CtaRange cr = sk_cta_range(P);
     const SkJob& J = P.job[cr.ji];
     const int G = J.G, Gs = nseg * G, nt = cr.nt, tau_first = cr.tau_first;
     const int n = nt * Gs;
-    constexpr int SU = 2 * SK_WARPS;  // units per slot fill: a pair per warp
-    constexpr uint32_t SLOT_BYTES = (uint32_t)SU * UB;
-    // the ring's constants as plain values: the record itself lives in the caller's local memory, and a load from it
-    // inside the main loop would cost a trip to the L2 whenever the small L1 has dropped the line
+    const int nslots = (n + SU - 1) / SU;
+    // the ring's constants as plain values: the record itself may live in local memory, and a load from it inside the
+    // main loop would cost a trip to the L2 whenever the small L1 has dropped the line
     const uint32_t r_base = R.base, r_full = R.full, r_empty = R.empty, r_zeros = R.zeros, r_abort = R.abort_flag;
     const int NS = R.NS, skip = R.skip;
     auto aborted = [&]() { return lds_volatile_i32(r_abort) != 0; };
-    uint32_t kb = kbase;
-    const int nslots = (n + SU - 1) / SU;
 
-    const int dstride = J.in + 16;
-    uint8_t* digits = smem;                                              // [nseg][4][in + 16]
-    int* ss = reinterpret_cast<int*>(smem + (size_t)nseg * 4 * dstride);  // [nseg][G][2]
-    float* pg = reinterpret_cast<float*>(ss + Gs * 2);                   // [nseg][G] 2^-(26 - E_g)
+    const int pstride = nseg * J.in + 16;
+    uint8_t* digits = smem;                                              // [4][nseg * in + 16]
+    uint4* sp = reinterpret_cast<uint4*>(smem + (size_t)4 * pstride);    // [nseg * G] group records
     const bool natural = J.seg[0].perm != nullptr;                       // the input arrives in natural order and is gathered into the K order
-    float* xs = pg + ((Gs + 3) & ~3);                                    // [in] the natural-order vector as plain floats (only then); 16-byte aligned
-    float* partial = xs + (natural ? J.in : 0);                          // [nt][SK_WARPS][ROWS]
+    float* xs = reinterpret_cast<float*>(sp + Gs);                       // [in] the natural-order vector as plain floats (only then)
+    float* partial = xs + (natural ? J.in : 0);                          // [nt][SK_WARPS][PROWS]
 
-    for (int i = threadIdx.x; i < nt * SK_WARPS * ROWS; i += SK_THREADS) partial[i] = 0.f;
+    for (int i = threadIdx.x; i < nt * SK_WARPS * PROWS; i += SK_THREADS) partial[i] = 0.f;
     bool stage_failed = false;  // a poll for a tagged input gave up
-    float sq = 0.f;
     if (stamp && threadIdx.x == 0) stamp[16] = clock64();
     if (n > 0) {
+        float sq;
         if (natural)  // w1 and w3 read the same x, each through its own g_index
-            sq = stage_natural<W>(J.seg, nseg, J.in, G, digits, ss, pg, xs, tagbase | (uint32_t)J.in_phase[0], &stage_failed, stamp);
+            sq = stage_natural<W>(J.seg, nseg, J.in, G, digits, pstride, sp, xs, tagbase | (uint32_t)J.in_phase[0], &stage_failed, stamp);
         else          // the producer's row order is this matrix's K order (w2 after w1/w3)
-            stage_groups<W>(J.seg[0], J.in, digits, ss, pg, tagbase | (uint32_t)J.in_phase[0], true, &sq, &stage_failed, stamp);
+            sq = stage_direct<W>(J.seg[0].x, J.in, digits, pstride, sp, tagbase | (uint32_t)J.in_phase[0], &stage_failed, stamp);
         if (stamp && threadIdx.x == 0) stamp[17] = clock64();
         sq = tk_warp_sum(sq);
         if (lane == 0) red[warp] = sq;
     }
     if (stage_failed) ring_abort(R, 1010);
-    consumer_sync();  // digits, sums and factors are in place; so are the zeroed tile sums
+    consumer_sync();  // digits and group records are in place; so are the zeroed tile sums
     if (warp == 0) {  // rmsnorm factor of the input (src/models.rs:58-60), read by the epilogue; the digit scaling is already in the sums
         float total = tk_warp_sum(lane < SK_WARPS ? red[lane] : 0.f);
         if (lane == 0) oscale[0] = J.seg[0].nw ? 1.0f / sqrtf(total / (float)J.in + P.eps) : 1.0f;
@@ -260,124 +267,44 @@ __device__ L2_TK_PHASE_INLINE bool gemv_phase(const TokenParams& tk, const SkPar
         asm volatile(L2_POLL_LD ".u64 %0, [%1];" : "=l"(e_res) : "l"(reinterpret_cast<const unsigned long long*>(J.out) + e_row) : "memory");
     }
 
-    // ---- main loop.  In every slot fill this warp owns units 2*warp and 2*warp + 1.  With four warps
-    // per scheduler the loop lives on instruction count and on the length of its dependent chain, so
-    //  * it is straight-line code without data-dependent branches: all lanes run the scale / zero-point
-    //    step (lanes t >= 2 hold the unused MMA columns and are ignored when the sums are flushed), lanes
-    //    r >= 4 read their digits from a block of zeros instead of skipping the load; in the last,
-    //    partial fill of a phase the units beyond the end are multiplied all the same (the slot holds
-    //    older records there) and only their sums are left out;
-    //  * tile and group are carried from fill to fill instead of being recomputed.
+    // ---- main loop.  In every slot fill this warp owns units 2*warp and 2*warp + 1; unit u of the CTA is group
+    // u % Gs of tile u / Gs (the groups of w1 and of w3 of a tile follow one another).  The loop is bound by
+    // instruction issue (16 warps run it on 4 schedulers), so it is straight-line code on 32-bit shared-space
+    // addresses: all lanes run the scale / zero-point step (lanes t >= 2 hold the unused MMA columns and are ignored
+    // when the sums are written), lanes r >= 4 read their digits from a block of zeros instead of skipping the load;
+    // in the last, partial fill of a phase the units beyond the end are multiplied all the same (the slot holds older
+    // records there) and only their sums are left out.  Row sums stay in registers while consecutive units belong to
+    // the same (tile, matrix) and go to shared memory when that changes.
     const int r = lane >> 2, t = lane & 3;
+    const uint32_t zshift = 4u * (uint32_t)r;
+    const uint32_t w_lane = r_base + (uint32_t)(2 * warp) * UB + (uint32_t)lane * 16u;            // this lane's weights of unit 0 in slot 0
+    const uint32_t m_lane = r_base + (uint32_t)(2 * warp) * UB + 256u * W + 4u * (uint32_t)r;     // its two scales (and, + 64 - 4r, the zero-point words)
+    const uint32_t z_warp = r_base + (uint32_t)(2 * warp) * UB + 256u * W + 64u;
+    const uint32_t dg_lane = r < 4 ? smem_u32(digits) + (uint32_t)(r * pstride + t * (8 * W)) : r_zeros;
+    const uint32_t dstep = r < 4 ? (uint32_t)GS : 0u;
+    const uint32_t sp_lane = smem_u32(sp) + 8u * (uint32_t)(t & 1);
+    const uint32_t part_lane = smem_u32(partial) + 4u * (uint32_t)(warp * PROWS + r);
     float tot0 = 0.f, tot1 = 0.f;
-    int cur_key = -1;  // nseg * tile + segment the row sums belong to
-    bool ok = true;
-    auto flush = [&]() {
-        if (cur_key >= 0) {
-            // lanes t = 0 hold digits 0,1 (weight 2^16 relative to digits 2,3 held by lanes t = 1)
-            float a = t == 0 ? tot0 * 65536.0f : tot0, b = t == 0 ? tot1 * 65536.0f : tot1;
-            a += __shfl_xor_sync(0xffffffffu, a, 1);
-            b += __shfl_xor_sync(0xffffffffu, b, 1);
-            if (t == 0) {
-                const int tl = nseg == 2 ? cur_key >> 1 : cur_key, sg = nseg == 2 ? cur_key & 1 : 0;
-                float* dst = partial + ((size_t)tl * SK_WARPS + warp) * ROWS + sg * 16;
-                dst[r] = a;
-                dst[r + 8] = b;
-            }
-        }
-        tot0 = tot1 = 0.f;
-    };
-    const int zshift = 4 * r;
-    // 32-bit shared-space addresses of everything the loop touches
-    const uint32_t ring_a = r_base + (uint32_t)(2 * warp) * UB;   // this warp's pair inside slot 0
-    const uint32_t full_a = r_full, empty_a = r_empty;
-    const uint32_t ss_a = smem_u32(ss) + 4u * (uint32_t)(t & 1);
-    const uint32_t pg_a = smem_u32(pg);
-    // this lane's digits of the group at position gg; lanes r >= 4 (MMA columns 4..7) read zeros
-    const uint32_t dg_a = r < 4 ? smem_u32(digits) + (uint32_t)(r * dstride + t * (8 * W)) : r_zeros;
-    const uint32_t dmul = r < 4 ? 1u : 0u;
-    constexpr uint32_t META = 256u * W;  // scales, then the two zero-point words
-    auto digits_of = [&](int gg) {
-        const int seg = gg >= G ? 1 : 0;
-        return dg_a + (uint32_t)(seg * 4 * dstride + (gg - seg * G) * GS) * dmul;
-    };
-    auto key_of = [&](int tl, int gg) { return nseg == 2 ? 2 * tl + (gg >= G ? 1 : 0) : tl; };
-    struct Unit { uint32_t a[W], b[W], d[2 * W]; };
-    auto unit_load = [&](uint32_t rec, uint32_t dg, Unit& u) {
-        if constexpr (W == 4) {
-            const uint4 a = lds128(rec + lane * 16), b = lds128(rec + 512 + lane * 16), d0 = lds128(dg), d1 = lds128(dg + 16);
-            u.a[0] = a.x; u.a[1] = a.y; u.a[2] = a.z; u.a[3] = a.w;
-            u.b[0] = b.x; u.b[1] = b.y; u.b[2] = b.z; u.b[3] = b.w;
-            u.d[0] = d0.x; u.d[1] = d0.y; u.d[2] = d0.z; u.d[3] = d0.w; u.d[4] = d1.x; u.d[5] = d1.y; u.d[6] = d1.z; u.d[7] = d1.w;
-        } else if constexpr (W == 2) {
-            const uint2 a = lds64(rec + lane * 8), b = lds64(rec + 256 + lane * 8);
-            const uint4 d0 = lds128(dg);
-            u.a[0] = a.x; u.a[1] = a.y; u.b[0] = b.x; u.b[1] = b.y;
-            u.d[0] = d0.x; u.d[1] = d0.y; u.d[2] = d0.z; u.d[3] = d0.w;
-        } else {
-            u.a[0] = lds32(rec + lane * 4); u.b[0] = lds32(rec + 128 + lane * 4);
-            const uint2 d0 = lds64(dg);
-            u.d[0] = d0.x; u.d[1] = d0.y;
+    uint32_t cur_dst = 0;  // where the running row sums belong (0: nothing accumulated yet)
+    auto flush = [&]() {   // lanes t = 0 hold digits 0,1 (already scaled by 2^16), lanes t = 1 digits 2,3
+        const float a = tot0 + __shfl_xor_sync(0xffffffffu, tot0, 1), b = tot1 + __shfl_xor_sync(0xffffffffu, tot1, 1);
+        if (t == 0) {
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(cur_dst), "f"(a) : "memory");
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(cur_dst + 32u), "f"(b) : "memory");
         }
     };
     constexpr uint32_t M = 0x0F0F0F0Fu;
-    // The MMAs of the two units of a pair are issued as independent instructions, back to back: on this
-    // part an integer mma.sync that depends on the previous one of its warp (or that follows another
-    // warp's) occupies the tensor pipe about four times as long as one that follows an independent one
-    // of the same warp.  Even and odd K steps of a unit therefore have their own accumulators.
-    auto mma_step = [&](const Unit& u, int i, int (&c)[4], bool first) {
-        if (first) mma_u8s8_first(c, u.a[i] & M, u.b[i] & M, (u.a[i] >> 4) & M, (u.b[i] >> 4) & M, u.d[2 * i], u.d[2 * i + 1]);
-        else mma_u8s8(c, u.a[i] & M, u.b[i] & M, (u.a[i] >> 4) & M, (u.b[i] >> 4) & M, u.d[2 * i], u.d[2 * i + 1]);
-    };
-    auto pair_mma = [&](const Unit& u0, const Unit& u1, int (&c0)[4], int (&c1)[4]) {
-        if constexpr (W == 1) {
-            mma_step(u0, 0, c0, true);
-            mma_step(u1, 0, c1, true);
-        } else {
-            int e0[4], e1[4];  // odd steps
-            mma_step(u0, 0, c0, true);
-            mma_step(u0, 1, e0, true);
-            mma_step(u1, 0, c1, true);
-            mma_step(u1, 1, e1, true);
-#pragma unroll
-            for (int i = 2; i < W; i += 2) {
-                mma_step(u0, i, c0, false);
-                mma_step(u0, i + 1, e0, false);
-                mma_step(u1, i, c1, false);
-                mma_step(u1, i + 1, e1, false);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) { c0[j] += e0[j]; c1[j] += e1[j]; }
-        }
-    };
-    struct Meta { uint32_t s0, s1, sv, pf; uint2 zz; };
-    auto meta_load = [&](uint32_t rec, int gg, Meta& mt) {
-        mt.s0 = lds32(rec + META + 4 * r);
-        mt.s1 = lds32(rec + META + 32 + 4 * r);
-        mt.zz = lds64(rec + META + 64);
-        mt.sv = lds32(ss_a + 8u * (uint32_t)gg);
-        mt.pf = lds32(pg_a + 4u * (uint32_t)gg);
-    };
-    // scale, zero point and digit sums of one finished unit (exact integers up to the final FMA)
-    auto unit_finish = [&](const Meta& mt, int key, const int (&c)[4]) {
-        if (key != cur_key) { flush(); cur_key = key; }  // warp-uniform
-        const int z0 = (int)((mt.zz.x >> zshift) & 15u) + 1, z1 = (int)((mt.zz.y >> zshift) & 15u) + 1;  // src/gptq.rs:148
-        const int sv = (int)mt.sv;
-        const float pf = __uint_as_float(mt.pf);  // a power of two: the products below are exact scalings
-        tot0 = fmaf(__uint_as_float(mt.s0) * pf, (float)(c[0] * 256 + c[1] - z0 * sv), tot0);
-        tot1 = fmaf(__uint_as_float(mt.s1) * pf, (float)(c[2] * 256 + c[3] - z1 * sv), tot1);
-    };
-    // position of this warp's first unit of the current fill; advanced by SU units per fill
-    int tl0 = 0, gg0 = 2 * warp;
-    while (gg0 >= Gs) { gg0 -= Gs; tl0++; }
-    uint32_t fslot = kb & 0xFFFFu, fpar = kb >> 16;  // slot and parity of the next fill, carried from phase to phase
+    // position of this warp's first unit of the current fill: group f0 of the tile's Gs, tile tile0
+    int f0 = 2 * warp, tile0 = 0;
+    while (f0 >= Gs) { f0 -= Gs; tile0++; }
+    int rem = n - 2 * warp;  // units of this warp's stride that are left, counted from its first of the current fill
+    uint32_t fslot = kbase & 0xFFFFu, fpar = kbase >> 16;  // slot and parity of the next fill, carried from phase to phase
+    bool ok = true;
 #pragma unroll 1
     for (int k = 0; k < nslots; k++) {
-        const uint32_t slot = fslot;
-        const int m = n - k * SU;  // units of this fill (all of them valid if >= SU)
-        bool got = mbar_try_wait_u32(full_a + 8u * slot, fpar);
+        bool got = mbar_try_wait_u32(r_full + 8u * fslot, fpar);
         if (!__all_sync(0xffffffffu, got)) {  // not there yet: the bounded wait
-            got = !aborted() && mbar_wait_u32(full_a + 8u * slot, fpar);
+            got = !aborted() && mbar_wait_u32(r_full + 8u * fslot, fpar);
             if (!__all_sync(0xffffffffu, got)) {
                 if (!aborted()) ring_abort(R, 1001);
                 ok = false;
@@ -385,32 +312,96 @@ __device__ L2_TK_PHASE_INLINE bool gemv_phase(const TokenParams& tk, const SkPar
             }
         }
         if (!(skip & 1)) {
-            const uint32_t rec0 = ring_a + slot * SLOT_BYTES;
-            int tl1 = tl0, gg1 = gg0 + 1;
-            if (gg1 == Gs) { gg1 = 0; tl1++; }
+            const uint32_t so = fslot * SLOT_BYTES;
+            int f1 = f0 + 1, tile1 = tile0;
+            if (f1 == Gs) { f1 = 0; tile1++; }
+            // operands of both units: weights (two 16-row halves), digits, scales, zero points, group record
+            uint32_t a0[W], b0[W], a1[W], b1[W], d0[2 * W], d1[2 * W];
+            const uint32_t dg0 = dg_lane + (uint32_t)f0 * dstep, dg1 = dg_lane + (uint32_t)f1 * dstep;
+            if constexpr (W == 4) {
+                const uint4 x0 = lds128(w_lane + so), y0 = lds128(w_lane + so + 512), x1 = lds128(w_lane + so + UB), y1 = lds128(w_lane + so + UB + 512);
+                const uint4 p0 = lds128(dg0), q0 = lds128(dg0 + 16), p1 = lds128(dg1), q1 = lds128(dg1 + 16);
+                a0[0] = x0.x; a0[1] = x0.y; a0[2] = x0.z; a0[3] = x0.w; b0[0] = y0.x; b0[1] = y0.y; b0[2] = y0.z; b0[3] = y0.w;
+                a1[0] = x1.x; a1[1] = x1.y; a1[2] = x1.z; a1[3] = x1.w; b1[0] = y1.x; b1[1] = y1.y; b1[2] = y1.z; b1[3] = y1.w;
+                d0[0] = p0.x; d0[1] = p0.y; d0[2] = p0.z; d0[3] = p0.w; d0[4] = q0.x; d0[5] = q0.y; d0[6] = q0.z; d0[7] = q0.w;
+                d1[0] = p1.x; d1[1] = p1.y; d1[2] = p1.z; d1[3] = p1.w; d1[4] = q1.x; d1[5] = q1.y; d1[6] = q1.z; d1[7] = q1.w;
+            } else if constexpr (W == 2) {
+                const uint32_t wl = w_lane - (uint32_t)lane * 8u;  // 8 bytes per lane and half
+                const uint2 x0 = lds64(wl + so), y0 = lds64(wl + so + 256), x1 = lds64(wl + so + UB), y1 = lds64(wl + so + UB + 256);
+                const uint4 p0 = lds128(dg0), p1 = lds128(dg1);
+                a0[0] = x0.x; a0[1] = x0.y; b0[0] = y0.x; b0[1] = y0.y; a1[0] = x1.x; a1[1] = x1.y; b1[0] = y1.x; b1[1] = y1.y;
+                d0[0] = p0.x; d0[1] = p0.y; d0[2] = p0.z; d0[3] = p0.w; d1[0] = p1.x; d1[1] = p1.y; d1[2] = p1.z; d1[3] = p1.w;
+            } else {
+                const uint32_t wl = w_lane - (uint32_t)lane * 12u;  // 4 bytes per lane and half
+                a0[0] = lds32(wl + so); b0[0] = lds32(wl + so + 128); a1[0] = lds32(wl + so + UB); b1[0] = lds32(wl + so + UB + 128);
+                const uint2 p0 = lds64(dg0), p1 = lds64(dg1);
+                d0[0] = p0.x; d0[1] = p0.y; d1[0] = p1.x; d1[1] = p1.y;
+            }
+            const uint32_t s00 = lds32(m_lane + so), s01 = lds32(m_lane + so + 32), s10 = lds32(m_lane + so + UB), s11 = lds32(m_lane + so + UB + 32);
+            const uint2 zz0 = lds64(z_warp + so), zz1 = lds64(z_warp + so + UB);
+            const uint2 g0 = lds64(sp_lane + 16u * (uint32_t)f0), g1 = lds64(sp_lane + 16u * (uint32_t)f1);  // {digit sums of this lane's columns, their factor}
+            // The MMAs of the pair are independent instructions issued back to back (even and odd K steps of a unit have
+            // their own accumulators): an integer mma.sync that depends on the previous one of its warp occupies the
+            // tensor pipe about four times as long as one that follows an independent one.
             int c0[4], c1[4];
-            Unit u0, u1;
-            Meta m0, m1;
-            unit_load(rec0, digits_of(gg0), u0);
-            unit_load(rec0 + UB, digits_of(gg1), u1);
-            meta_load(rec0, gg0, m0);
-            meta_load(rec0 + UB, gg1, m1);
-            pair_mma(u0, u1, c0, c1);
-            if (2 * warp < m) unit_finish(m0, key_of(tl0, gg0), c0);
-            if (2 * warp + 1 < m) unit_finish(m1, key_of(tl1, gg1), c1);
+            if constexpr (W == 1) {
+                mma_u8s8_first(c0, a0[0] & M, b0[0] & M, (a0[0] >> 4) & M, (b0[0] >> 4) & M, d0[0], d0[1]);
+                mma_u8s8_first(c1, a1[0] & M, b1[0] & M, (a1[0] >> 4) & M, (b1[0] >> 4) & M, d1[0], d1[1]);
+            } else {
+                int e0[4], e1[4];
+                mma_u8s8_first(c0, a0[0] & M, b0[0] & M, (a0[0] >> 4) & M, (b0[0] >> 4) & M, d0[0], d0[1]);
+                mma_u8s8_first(e0, a0[1] & M, b0[1] & M, (a0[1] >> 4) & M, (b0[1] >> 4) & M, d0[2], d0[3]);
+                mma_u8s8_first(c1, a1[0] & M, b1[0] & M, (a1[0] >> 4) & M, (b1[0] >> 4) & M, d1[0], d1[1]);
+                mma_u8s8_first(e1, a1[1] & M, b1[1] & M, (a1[1] >> 4) & M, (b1[1] >> 4) & M, d1[2], d1[3]);
+#pragma unroll
+                for (int i = 2; i < W; i += 2) {
+                    mma_u8s8(c0, a0[i] & M, b0[i] & M, (a0[i] >> 4) & M, (b0[i] >> 4) & M, d0[2 * i], d0[2 * i + 1]);
+                    mma_u8s8(e0, a0[i + 1] & M, b0[i + 1] & M, (a0[i + 1] >> 4) & M, (b0[i + 1] >> 4) & M, d0[2 * i + 2], d0[2 * i + 3]);
+                    mma_u8s8(c1, a1[i] & M, b1[i] & M, (a1[i] >> 4) & M, (b1[i] >> 4) & M, d1[2 * i], d1[2 * i + 1]);
+                    mma_u8s8(e1, a1[i + 1] & M, b1[i + 1] & M, (a1[i + 1] >> 4) & M, (b1[i + 1] >> 4) & M, d1[2 * i + 2], d1[2 * i + 3]);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) { c0[j] += e0[j]; c1[j] += e1[j]; }
+            }
+            // scale, zero point and digit sums of the finished units (exact integers up to the final FMA)
+            if (rem > 0) {
+                const uint32_t dst = part_lane + (uint32_t)tile0 * (SK_WARPS * PROWS * 4u) + (f0 >= G ? 64u : 0u);
+                if (dst != cur_dst) {  // warp-uniform
+                    if (cur_dst) flush();
+                    cur_dst = dst;
+                    tot0 = tot1 = 0.f;
+                }
+                const int za = (int)((zz0.x >> zshift) & 15u) + 1, zb = (int)((zz0.y >> zshift) & 15u) + 1;  // src/gptq.rs:148
+                const float pf = __uint_as_float(g0.y);  // a power of two: the products below are exact scalings
+                tot0 = fmaf(__uint_as_float(s00) * pf, (float)(c0[0] * 256 + c0[1] - za * (int)g0.x), tot0);
+                tot1 = fmaf(__uint_as_float(s01) * pf, (float)(c0[2] * 256 + c0[3] - zb * (int)g0.x), tot1);
+            }
+            if (rem > 1) {
+                const uint32_t dst = part_lane + (uint32_t)tile1 * (SK_WARPS * PROWS * 4u) + (f1 >= G ? 64u : 0u);
+                if (dst != cur_dst) {
+                    if (cur_dst) flush();
+                    cur_dst = dst;
+                    tot0 = tot1 = 0.f;
+                }
+                const int za = (int)((zz1.x >> zshift) & 15u) + 1, zb = (int)((zz1.y >> zshift) & 15u) + 1;
+                const float pf = __uint_as_float(g1.y);
+                tot0 = fmaf(__uint_as_float(s10) * pf, (float)(c1[0] * 256 + c1[1] - za * (int)g1.x), tot0);
+                tot1 = fmaf(__uint_as_float(s11) * pf, (float)(c1[2] * 256 + c1[3] - zb * (int)g1.x), tot1);
+            }
         }
         __syncwarp();  // every lane has read the slot
-        if (lane == 0) mbar_arrive_u32(empty_a + 8u * slot);
-        gg0 += SU;
-        while (gg0 >= Gs) { gg0 -= Gs; tl0++; }
+        if (lane == 0) mbar_arrive_u32(r_empty + 8u * fslot);
+        rem -= SU;
+        f0 += SU;
+        while (f0 >= Gs) { f0 -= Gs; tile0++; }
         if (++fslot == (uint32_t)NS) { fslot = 0; fpar ^= 1u; }
     }
     kbase = fslot | (fpar << 16);
-    flush();
+    if (cur_dst) flush();
     if (stamp && threadIdx.x == 0) { stamp[2] = clock64(); stamp[9] = (unsigned long long)nslots; }
     consumer_sync();
     if (stamp && threadIdx.x == 0) stamp[18] = clock64();
-    if (aborted()) return false;
+    if (!ok || aborted()) return false;
 
     const float rs = oscale[0];
     // Results leave as (value, tag) pairs: whoever needs them polls for the tag of this phase.
@@ -419,8 +410,7 @@ __device__ L2_TK_PHASE_INLINE bool gemv_phase(const TokenParams& tk, const SkPar
 #pragma unroll 1
     for (int tl = warp; tl < nt; tl += SK_WARPS) {
         float v = 0.f;
-        if (lane < ROWS)
-            for (int w = 0; w < SK_WARPS; w++) v += partial[((size_t)tl * SK_WARPS + w) * ROWS + lane];
+        for (int w = 0; w < SK_WARPS; w++) v += partial[(tl * SK_WARPS + w) * PROWS + lane];
         float y = v * rs;
         if (stamp && threadIdx.x == 0) stamp[19] = clock64() + (y == 1.2345f ? 1 : 0);
         const int row = (tau_first + tl) * 16 + (lane & 15);
