@@ -403,6 +403,7 @@ template <int W>
 __device__ __forceinline__ void stage_emit8(float (&v)[8], bool valid, int blk, uint8_t* digits, int pstride, uint4* sp) {
     float mx = fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
                      fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
+    // (a group's 4 * W lanes reduce with shuffles: redux.sync on a part of the warp was measured slower here)
 #pragma unroll
     for (int o = 1; o < 4 * W; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     const float P = stage_scale(mx);
@@ -468,71 +469,54 @@ __device__ __forceinline__ float stage_direct(const void* x_tagged, int in, uint
 // Values cross CTAs fastest when every 128-byte line has one writer: a vector whose elements are scattered
 // by their producers into a consumer's K order (eight writers per line polled) takes about three times as
 // long to arrive as the same vector written tile by tile.  So producers store in natural order, and the
-// consumer (1) polls the natural vector into shared memory as plain floats, applying the norm weight and
-// taking the sum of squares on the way, and (2) gathers its K order from there through the matrix's g_index
-// while it writes the digits.
+// consumer (1) polls the natural vector, applies the norm weight, takes the sum of squares and scatters the
+// values into the matrix's K order in shared memory (plain floats; the bank conflicts of the scattered stores
+// are paid while other values are still awaited), and (2) turns the K-order floats into digits block by block.
+// seg[s].perm holds 16-bit indices: natural element i belongs at position perm[i] of matrix s's K order.
 
-// (1) n / 8 blocks of 8 tagged values, times the norm weight (natural order, or null) -> xs[n]; returns this
-// thread's share of the sum of squares of the raw values.
-__device__ __forceinline__ float stage_poll_natural(const void* x_tagged, const float* nw_natural, int n, float* xs, uint32_t tag, bool* fail) {
-    const int nblk = n / 8;
-    float sq = 0.f;
-#pragma unroll 1
-    for (int blk = threadIdx.x; blk < nblk; blk += SK_THREADS) {
-        float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
-        if (nw_natural) {  // requested before the poll: it does not depend on the awaited values
-            w0 = __ldg(reinterpret_cast<const float4*>(nw_natural) + 2 * blk);
-            w1 = __ldg(reinterpret_cast<const float4*>(nw_natural) + 2 * blk + 1);
-        }
-        float4 v0, v1;
-        if (!load_tagged8(x_tagged, (size_t)blk * 8, tag, v0, v1)) *fail = true;
-        sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
-        v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
-        v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
-        reinterpret_cast<float4*>(xs)[2 * blk] = v0;
-        reinterpret_cast<float4*>(xs)[2 * blk + 1] = v1;
-    }
-    return sq;
-}
-
-// (2) K-order block b of a matrix: positions perm[8b .. 8b+7] of xs (16-bit indices: IN < 65536).
-template <int W>
-__device__ __forceinline__ void gather_emit(const uint4& idx, const float* xs, bool valid, int blk, uint8_t* digits, int pstride, uint4* sp) {
-    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (valid) {
-        v[0] = xs[idx.x & 0xFFFFu]; v[1] = xs[idx.x >> 16]; v[2] = xs[idx.y & 0xFFFFu]; v[3] = xs[idx.y >> 16];
-        v[4] = xs[idx.z & 0xFFFFu]; v[5] = xs[idx.z >> 16]; v[6] = xs[idx.w & 0xFFFFu]; v[7] = xs[idx.w >> 16];
-    }
-    stage_emit8<W>(v, valid, blk, digits, pstride, sp);
-}
-
-// The whole staging of a GEMV phase whose input arrives in natural order: nseg matrices (w1 with w3) read the
-// same vector, each through its own g_index (seg[s].perm: 16-bit indices here); seg[0].nw is the norm weight
-// in natural order.  Matrix s occupies positions [s * in, (s + 1) * in) of a digit plane and groups
-// [s * G, (s + 1) * G) of sp.  Returns this thread's share of the sum of squares.
 template <int W>
 __device__ __forceinline__ float stage_natural(const SkSeg* seg, int nseg, int in, int G, uint8_t* digits, int pstride, uint4* sp, float* xs, uint32_t tag,
                                                bool* fail, unsigned long long* stamp = nullptr) {
     const int nblk = in / 8;
-    // the indices of this thread's first K-order block of each matrix: requested before the vector is awaited
-    uint4 first0 = make_uint4(0, 0, 0, 0), first1 = first0;
-    const int blk0 = threadIdx.x;
-    if (blk0 < nblk) {
-        first0 = __ldg(reinterpret_cast<const uint4*>(seg[0].perm) + blk0);
-        if (nseg == 2) first1 = __ldg(reinterpret_cast<const uint4*>(seg[1].perm) + blk0);
+    float* xs1 = xs + in;  // the second matrix's K order (w3 beside w1)
+    float sq = 0.f;
+    // (1) everything that does not depend on the awaited values is requested first: positions and norm weights
+#pragma unroll 1
+    for (int blk = threadIdx.x; blk < nblk; blk += SK_THREADS) {
+        const uint4 i0 = __ldg(reinterpret_cast<const uint4*>(seg[0].perm) + blk);
+        uint4 i1 = make_uint4(0, 0, 0, 0);
+        if (nseg == 2) i1 = __ldg(reinterpret_cast<const uint4*>(seg[1].perm) + blk);
+        float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
+        if (seg[0].nw) {
+            w0 = __ldg(reinterpret_cast<const float4*>(seg[0].nw) + 2 * blk);
+            w1 = __ldg(reinterpret_cast<const float4*>(seg[0].nw) + 2 * blk + 1);
+        }
+        float4 v0, v1;
+        if (!load_tagged8(seg[0].x, (size_t)blk * 8, tag, v0, v1)) *fail = true;
+        sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+        v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
+        v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
+        xs[i0.x & 0xFFFFu] = v0.x; xs[i0.x >> 16] = v0.y; xs[i0.y & 0xFFFFu] = v0.z; xs[i0.y >> 16] = v0.w;
+        xs[i0.z & 0xFFFFu] = v1.x; xs[i0.z >> 16] = v1.y; xs[i0.w & 0xFFFFu] = v1.z; xs[i0.w >> 16] = v1.w;
+        if (nseg == 2) {
+            xs1[i1.x & 0xFFFFu] = v0.x; xs1[i1.x >> 16] = v0.y; xs1[i1.y & 0xFFFFu] = v0.z; xs1[i1.y >> 16] = v0.w;
+            xs1[i1.z & 0xFFFFu] = v1.x; xs1[i1.z >> 16] = v1.y; xs1[i1.w & 0xFFFFu] = v1.z; xs1[i1.w >> 16] = v1.w;
+        }
     }
-    const float sq = stage_poll_natural(seg[0].x, seg[0].nw, in, xs, tag, fail);
     if (stamp && threadIdx.x == 0) stamp[21] = clock64();
     consumer_sync();
     if (stamp && threadIdx.x == 0) stamp[22] = clock64();
-#pragma unroll
-    for (int s = 0; s < 2; s++) {
-        if (s >= nseg) break;
+    // (2) digits, block by block of each matrix's K order
 #pragma unroll 1
-        for (int blk = blk0; (blk & ~31) < nblk; blk += SK_THREADS) {
-            uint4 idx = s ? first1 : first0;
-            if (blk != blk0 && blk < nblk) idx = __ldg(reinterpret_cast<const uint4*>(seg[s].perm) + blk);
-            gather_emit<W>(idx, xs, blk < nblk, blk, digits + (size_t)s * in, pstride, sp + s * G);
+    for (int s = 0; s < nseg; s++) {
+        const float4* src = reinterpret_cast<const float4*>(xs + (size_t)s * in);
+#pragma unroll 1
+        for (int blk = threadIdx.x; (blk & ~31) < nblk; blk += SK_THREADS) {
+            const bool valid = blk < nblk;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+            if (valid) { a = src[2 * blk]; b = src[2 * blk + 1]; }
+            float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            stage_emit8<W>(v, valid, blk, digits + (size_t)s * in, pstride, sp + s * G);
         }
     }
     if (stamp && threadIdx.x == 0) stamp[23] = clock64();

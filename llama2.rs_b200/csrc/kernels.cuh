@@ -33,8 +33,8 @@ struct SkSeg {
     const uint32_t* rec;  // [tile][group] unit records of 64*W + 20 words (see repack.cpp)
     const float* x;       // input in this matrix's K order (the producer scatters it); token kernel: tagged, see perm
     const float* nw;      // rmsnorm weight in the matrix's K order, or null
-    const int* perm;      // token kernel: x is in natural order and position p of the K order reads x[perm[p]], perm as packed 16-bit
-                          // indices, and nw is in natural order too (null: x is in K order already)
+    const int* perm;      // token kernel: x is in natural order, element i of it belongs at position perm[i] of the K order (perm as packed
+                          // 16-bit indices), and nw is in natural order too (null: x is in K order already)
 };
 
 // One fused dequant+GEMV problem of a launch.  nseg == 2 pairs w1 with w3 for SwiGLU.

@@ -94,8 +94,8 @@ int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vecto
         std::vector<int32_t> inv = inverse_permutation(g_index, p.in);
         if (int rc = dev_upload(&d.inv, inv.data(), (size_t)p.in, allocs, bytes)) return rc;
         if (p.in < 65536) {
-            std::vector<uint16_t> p16(g_index, g_index + p.in);
-            if (int rc = dev_upload(&d.perm16, p16.data(), (size_t)p.in, allocs, bytes)) return rc;
+            std::vector<uint16_t> i16(inv.begin(), inv.end());
+            if (int rc = dev_upload(&d.inv16, i16.data(), (size_t)p.in, allocs, bytes)) return rc;
         }
     }
     return L2_OK;
@@ -579,7 +579,7 @@ static int build_phase_table(l2_state* s, int kind) {
             // the consumer through its g_index; only w2 reads a vector that its producers (w1/w3, whose rows are stored in
             // w2's K order) already write in the right order.
             const DevLayer& y = m->layers[l];
-            auto p16 = [](const DevQ& q) { return reinterpret_cast<const int*>(q.perm16); };
+            auto p16 = [](const DevQ& q) { return reinterpret_cast<const int*>(q.inv16); };
             const int* perms[4][3] = {{p16(y.wq), p16(y.wk), p16(y.wv)}, {p16(y.wo), nullptr, nullptr}, {p16(y.w1), p16(y.w3), nullptr}, {nullptr, nullptr, nullptr}};
             const float* norms[4] = {y.rms_att, nullptr, y.rms_ffn, nullptr};
             if (c.dim >= 65536) return fail(L2_EINVAL, "token kernel: DIM %d does not fit 16-bit gather indices", c.dim);

@@ -111,10 +111,11 @@ __device__ __forceinline__ void prefetch_line_l2(const void* p) { asm volatile("
 
 // Producer side of one GEMV phase (called by the whole producer warp, lane 0 issues): streams this
 // CTA's unit records through the ring.  `kfill` counts slot fills since the start of the kernel.
-// Nothing beyond the ring is requested ahead of time: prefetches into the L2 (bulk or per line) were
-// measured to cost more than they gain here, because every request of an SM shares one path to
-// the L2 and the latency-critical loads of a phase (its input vector, the K/V rows) queue behind
-// whatever has been requested ahead.
+// Nothing beyond the ring is requested ahead of time.  Asking the L2 for the next phase's weights
+// (cp.async.bulk.prefetch.L2, issued one GEMV phase ahead) does make slot fills faster in isolation
+// (32-42 against 25 bytes per clock and SM), but in the kernel it was measured to cost more than it
+// gains, twice: the exchanges between phases are trips to the L2, and they slow down when HBM
+// traffic is poured into the L2 in exactly the windows in which they happen.
 template <int W>
 __device__ __forceinline__ bool produce_units(const SkParams& P, int NSEG, const Ring& R, uint32_t& kfill, unsigned long long* pstamp = nullptr) {
     constexpr uint32_t UB = 256u * W + 80u;
@@ -205,7 +206,7 @@ __device__ __forceinline__ void warm_operands(const SkParams& P, int NSEG) {
 size_t token_gemv_smem(int in, int G, int nseg, int ptiles, bool natural) {
     size_t b = (size_t)4 * ((size_t)nseg * in + 16);       // digit planes
     b += (size_t)nseg * G * 16;                            // group records
-    if (natural) b += (size_t)in * 4;                      // the natural-order vector as plain floats
+    if (natural) b += (size_t)nseg * in * 4;               // the vector in each matrix's K order as plain floats
     b += (size_t)ptiles * SK_WARPS * 32 * 4;               // tile sums per warp
     return b;
 }
@@ -234,8 +235,8 @@ __device__ L2_TK_PHASE_INLINE bool gemv_phase(const TokenParams& tk, const SkPar
     uint8_t* digits = smem;                                              // [4][nseg * in + 16]
     uint4* sp = reinterpret_cast<uint4*>(smem + (size_t)4 * pstride);    // [nseg * G] group records
     const bool natural = J.seg[0].perm != nullptr;                       // the input arrives in natural order and is gathered into the K order
-    float* xs = reinterpret_cast<float*>(sp + Gs);                       // [in] the natural-order vector as plain floats (only then)
-    float* partial = xs + (natural ? J.in : 0);                          // [nt][SK_WARPS][PROWS]
+    float* xs = reinterpret_cast<float*>(sp + Gs);                       // [nseg][in] the vector in each matrix's K order as plain floats (only then)
+    float* partial = xs + (natural ? nseg * J.in : 0);                   // [nt][SK_WARPS][PROWS]
 
     for (int i = threadIdx.x; i < nt * SK_WARPS * PROWS; i += SK_THREADS) partial[i] = 0.f;
     bool stage_failed = false;  // a poll for a tagged input gave up
