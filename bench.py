@@ -338,7 +338,12 @@ def main():
     e2e = {"value": streams * n_loop / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 40 * n_loop, "d2h_bytes_per_step": 40 * n_loop,
            "note": "one l2_decode_step call per token: 40-byte loop record up, 40-byte record (chosen token) back"}
 
+    streams_identical = None
     if world > 1:
+        if tp:  # every rank of a tensor-parallel group must have produced the same token stream
+            all_toks = [None] * world
+            dist.all_gather_object(all_toks, [int(t) for t in toks_ref])
+            streams_identical = all(t == all_toks[0] for t in all_toks)
         dist.barrier()
         dist.destroy_process_group()
     if rank != 0:
@@ -373,6 +378,8 @@ def main():
                            "frac_of_8tbs": model.decode_bytes * tok_s / 8e12, "frac_of_measured": model.decode_bytes * tok_s / (peak * 1e9)},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
     }
+    if streams_identical is not None:
+        out["tp_streams_identical"] = streams_identical
     if not args.no_cpu_baseline and world == 1:  # the CPU leg belongs to the single-GPU line
         try:
             out["cpu_baseline"] = CpuArm(args.workload, payload=payload, cfg=cfg).run()

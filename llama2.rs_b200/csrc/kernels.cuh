@@ -73,24 +73,24 @@ struct alignas(16) SkParams {
 // Batched QLinear on tcgen05 (gemm_tc.cu): out[m][o] for m < M tokens, 128 output rows per CTA.
 struct TcParams {
     const uint32_t* rec;   // unit records of the matrix (see repack.cpp)
-    const uint8_t* bimg;   // [G][n][gs] signed digit bytes of the activations, swizzled (act_quant_kernel)
-    const int* sv;         // [G][mpad][2] digit sums per token and group: 128*S0+S1, 128*S2+S3
+    const uint8_t* bimg;   // [G] blocks of [n][gs] signed digit bytes of the activations, swizzled, followed by [mpad] digit sums
+                           // per token (f32): one contiguous block per group (act_quant_kernel)
     const float* oscale;   // [mpad] factor of the integer result per token
     float* out;            // [M][ldo]
     int* status;
     int tiles16, G, gs, rows;
-    int m, mpad, n;        // tokens, tokens padded to a multiple of 4, n = 4 * mpad
+    int m, mpad, n;        // tokens, tokens padded to a multiple of 16, n = 4 * mpad
     int ldo, epi;
-    int ksplit;            // > 1: the groups are split over gridDim.y CTAs, slice k writes out + k * kstride (plain stores)
+    int ksplit;            // > 1: the groups are split over gridDim.y CTAs; slice k stores part + k * kstride [m][rows]
     size_t kstride;
+    float* part;
 };
 
 struct QuantParams {
     const float* x;        // [M][ldx] activations, natural order
     const int* perm;       // consumer's K order (g_index) or null
     const float* nw;       // rmsnorm weight in the consumer's K order, or null (no norm)
-    uint8_t* bimg;         // [G][n][gs]
-    int* sv;               // [G][mpad][2]
+    uint8_t* bimg;         // [G] blocks of [n][gs] digit bytes + [mpad] digit sums (f32)
     float* oscale;         // [mpad]
     int in, gs, ldx, mpad, n;
     float eps;
@@ -211,10 +211,12 @@ void launch_rope_append(const RopeParams& p, int n_heads, int M, cudaStream_t st
 void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_t st);
 void launch_swiglu(const float* h1, const float* h3, float* hb, size_t n, cudaStream_t st);
 // out[m][o] (+)= sum over the K slices, in slice order: finishes a GEMM whose groups were split over several CTAs
-void launch_ksum(const float* part, size_t kstride, int ksplit, float* out, int ldo, int rows, int M, int epi, cudaStream_t st);
 cudaError_t launch_gemm_tc(const TcParams& p, cudaStream_t st);
 cudaError_t gemm_tc_init(int max_smem);
+void launch_ksum(const float* part, size_t kstride, int ksplit, float* out, int ldo, int rows, int M, int epi, cudaStream_t st);
 size_t gemm_tc_smem_bytes(int gs, int n);
+int gemm_tc_mpad(int tokens);  // tokens of a pass, padded to the granularity of the kernel's drain (16)
+size_t gemm_tc_image_bytes(int in, int gs, int tokens);  // digit image of `tokens` activations rows for a matrix with IN = in
 extern unsigned long long* g_sk_trace;  // device buffer for SkParams::trace when tracing is on
 void launch_attn(const AttnParams& p, cudaStream_t st, bool pdl);
 void launch_cls(const ClsParams& p, int grid, cudaStream_t st, bool pdl);

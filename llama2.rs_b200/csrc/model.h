@@ -51,8 +51,7 @@ constexpr int MAX_BATCH = 64;  // tokens of one batched forward (one tcgen05 til
 struct BatchBuffers {
     float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *h1 = nullptr, *h3 = nullptr, *hb = nullptr;
     float* kpart[3] = {nullptr, nullptr, nullptr};  // [4][tokens][rows] partial results of GEMMs whose groups are split over CTAs, one per stream
-    uint8_t* img[3] = {nullptr, nullptr, nullptr};  // digit images of up to three consumers
-    int* sv[3] = {nullptr, nullptr, nullptr};
+    uint8_t* img[3] = {nullptr, nullptr, nullptr};  // digit images (with the digit sums) of up to three consumers
     float* osc[3] = {nullptr, nullptr, nullptr};
     int *tok = nullptr, *pos = nullptr;             // device token ids / positions of the batch
     int* h_stage = nullptr;                         // pinned ring for their upload
@@ -138,8 +137,7 @@ struct l2_qlinear {
     int group_size = 128;
     float *x_dev = nullptr, *xp_dev = nullptr, *y_dev = nullptr;
     l2::SkParams* d_plan = nullptr;
-    uint8_t* img = nullptr;   // batched path: digit image, sums and factors
-    int* sv = nullptr;
+    uint8_t* img = nullptr;   // batched path: digit image with the digit sums, and the factors
     float* osc = nullptr;
     int* status = nullptr;
     int cap_b = 0;
@@ -162,7 +160,7 @@ struct NcclId { char bytes[128]; };  // ncclUniqueId
 int tp_all_gather(l2_model* m, float* buf, size_t count, cudaStream_t st);
 void tp_disconnect(l2_model* m);
 void tp_rows(int total_rows, int rank, int world, int* row0, int* nrows);
-int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const float* nw, float eps, int M, uint8_t* img, int* sv, float* osc,
+int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const float* nw, float eps, int M, uint8_t* img, float* osc,
                  float* out, int ldo, int epi, int* status, cudaStream_t st, float* kpart = nullptr, int sms = 148, int side_tiles = 0);
 int dev_alloc_bytes(void** p, size_t bytes, std::vector<void*>& allocs);
 void sk_set_matrix(SkJob& j, int seg, const DevQ& q, const float* x, const float* nw);

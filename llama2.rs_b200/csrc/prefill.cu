@@ -15,40 +15,38 @@ int dev_alloc_bytes(void** p, size_t bytes, std::vector<void*>& allocs) {
 
 // out[m][:] = QLinear(x[m][:]) for m < M.  gather: x is in natural order and is brought into the
 // matrix's K order through its g_index; nw (K order) folds an rmsnorm in.
-int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const float* nw, float eps, int M, uint8_t* img, int* sv,
+int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const float* nw, float eps, int M, uint8_t* img,
                  float* osc, float* out, int ldo, int epi, int* status, cudaStream_t st, float* kpart, int sms, int side_tiles) {
-    const int mpad = (M + 3) & ~3;
+    const int mpad = gemm_tc_mpad(M);
     QuantParams a{};
     a.x = x; a.perm = gather ? q.perm : nullptr; a.nw = nw;
-    a.bimg = img; a.sv = sv; a.oscale = osc;
+    a.bimg = img; a.oscale = osc;
     a.in = q.in; a.gs = q.gs; a.ldx = ldx; a.mpad = mpad; a.n = 4 * mpad; a.eps = eps;
     launch_act_quant(a, M, st);
     TcParams t{};
-    t.rec = q.rec; t.bimg = img; t.sv = sv; t.oscale = osc; t.out = out; t.status = status;
+    t.rec = q.rec; t.bimg = img; t.oscale = osc; t.out = out; t.status = status;
     t.tiles16 = q.tiles; t.G = q.G; t.gs = q.gs; t.rows = q.out;
     t.m = M; t.mpad = mpad; t.n = 4 * mpad; t.ldo = ldo; t.epi = epi;
     // A matrix with few 128-row tiles would leave most SMs idle: its groups are split over several CTAs
-    // per tile, which write partial results that a small kernel adds up in slice order.
+    // per tile, which store partial results that a small kernel adds up in slice order.
     // (side_tiles: 128-row tiles of the GEMMs that run side by side with this one on other streams)
     const int tiles128 = (q.tiles + 7) / 8;
     int ks = 1;
-    if (kpart) {  // fewest waves x groups per CTA, a little in favour of fewer slices
+    if (kpart) {  // cost in group times: waves x (groups per CTA + about four to fill the CTA's pipeline) + about five for the sum kernel
         long best = -1;
         for (int k = 1; k <= 4 && k * 4 <= q.G; k++) {
             const long waves = ((long)(tiles128 + side_tiles) * k + sms - 1) / sms;
-            const long cost = waves * ((q.G + k - 1) / k) * 16 + k;
+            const long cost = waves * ((q.G + k - 1) / k + 4) + (k > 1 ? 5 : 0);
             if (best < 0 || cost < best) { best = cost; ks = k; }
         }
     }
     if (ks > 1) {
         t.ksplit = ks;
         t.kstride = (size_t)M * q.out;
-        t.out = kpart; t.ldo = q.out; t.epi = EPI_STORE;
-        L2_CUDA(launch_gemm_tc(t, st));
-        launch_ksum(kpart, t.kstride, ks, out, ldo, q.out, M, epi, st);
-    } else {
-        L2_CUDA(launch_gemm_tc(t, st));
+        t.part = kpart;
     }
+    L2_CUDA(launch_gemm_tc(t, st));
+    if (ks > 1) launch_ksum(kpart, t.kstride, ks, out, ldo, q.out, M, epi, st);
     return L2_OK;
 }
 
@@ -57,7 +55,7 @@ static int ensure_batch(l2_state* s) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
     const size_t B = MAX_BATCH, D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
-    const size_t kmax = std::max(D, H), gmax = kmax / c.group_size;
+    const size_t kmax = std::max(D, H);
     BatchBuffers* b = new BatchBuffers;
     int rc = 0;
     auto F = [&](float** p, size_t n) { return dev_alloc_bytes(reinterpret_cast<void**>(p), n * sizeof(float), s->allocs); };
@@ -65,11 +63,10 @@ static int ensure_batch(l2_state* s) {
         (rc = F(&b->att, B * D)) || (rc = F(&b->h1, B * H)) || (rc = F(&b->h3, B * H)) || (rc = F(&b->hb, B * H)) ||
         (rc = F(&b->kpart[0], 4 * B * kmax)) || (rc = F(&b->kpart[1], 4 * B * kmax)) || (rc = F(&b->kpart[2], 4 * B * kmax))) { delete b; return rc; }
     for (int i = 0; i < 3; i++) {
-        if ((rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->img[i]), 4 * B * kmax, s->allocs)) ||
-            (rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->sv[i]), gmax * B * 2 * sizeof(int), s->allocs)) ||
+        const size_t img_bytes = gemm_tc_image_bytes((int)kmax, c.group_size, (int)B);
+        if ((rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->img[i]), img_bytes, s->allocs)) ||
             (rc = F(&b->osc[i], B))) { delete b; return rc; }
-        L2_CUDA(cudaMemset(b->img[i], 0, 4 * B * kmax));
-        L2_CUDA(cudaMemset(b->sv[i], 0, gmax * B * 2 * sizeof(int)));
+        L2_CUDA(cudaMemset(b->img[i], 0, img_bytes));
     }
     if ((rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->tok), B * sizeof(int), s->allocs)) ||
         (rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->pos), B * sizeof(int), s->allocs))) { delete b; return rc; }
@@ -107,9 +104,9 @@ int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos)
         L2_CUDA(cudaEventRecord(b->fork, st));
         L2_CUDA(cudaStreamWaitEvent(b->aux[0], b->fork, 0));
         L2_CUDA(cudaStreamWaitEvent(b->aux[1], b->fork, 0));
-        if ((rc = gemm_batched(y.wq, b->x, D, true, y.nw_q, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->q, D, EPI_STORE, status, st, b->kpart[0], m->sms, (y.wk.tiles + 7) / 8 + (y.wv.tiles + 7) / 8))) return rc;
-        if ((rc = gemm_batched(y.wk, b->x, D, true, y.nw_k, m->eps, M, b->img[1], b->sv[1], b->osc[1], b->k, KV, EPI_STORE, status, b->aux[0], b->kpart[1], m->sms, (y.wq.tiles + 7) / 8 + (y.wv.tiles + 7) / 8))) return rc;
-        if ((rc = gemm_batched(y.wv, b->x, D, true, y.nw_v, m->eps, M, b->img[2], b->sv[2], b->osc[2], b->v, KV, EPI_STORE, status, b->aux[1], b->kpart[2], m->sms, (y.wq.tiles + 7) / 8 + (y.wk.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.wq, b->x, D, true, y.nw_q, m->eps, M, b->img[0], b->osc[0], b->q, D, EPI_STORE, status, st, b->kpart[0], m->sms, (y.wk.tiles + 7) / 8 + (y.wv.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.wk, b->x, D, true, y.nw_k, m->eps, M, b->img[1], b->osc[1], b->k, KV, EPI_STORE, status, b->aux[0], b->kpart[1], m->sms, (y.wq.tiles + 7) / 8 + (y.wv.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.wv, b->x, D, true, y.nw_v, m->eps, M, b->img[2], b->osc[2], b->v, KV, EPI_STORE, status, b->aux[1], b->kpart[2], m->sms, (y.wq.tiles + 7) / 8 + (y.wk.tiles + 7) / 8))) return rc;
         for (int i = 0; i < 2; i++) {
             L2_CUDA(cudaEventRecord(b->join[i], b->aux[i]));
             L2_CUDA(cudaStreamWaitEvent(st, b->join[i], 0));
@@ -125,17 +122,17 @@ int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos)
         a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups(); a.ldq = D; a.ldo = D;
         launch_attn_batch(a, c.n_heads, M, st);
         // wo + residual (:260-264)
-        if ((rc = gemm_batched(y.wo, b->att, D, true, nullptr, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->x, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
+        if ((rc = gemm_batched(y.wo, b->att, D, true, nullptr, m->eps, M, b->img[0], b->osc[0], b->x, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
         // rmsnorm + w1/w3 + SwiGLU (:266-276); their rows are stored in w2's K order
         L2_CUDA(cudaEventRecord(b->fork, st));
         L2_CUDA(cudaStreamWaitEvent(b->aux[0], b->fork, 0));
-        if ((rc = gemm_batched(y.w1, b->x, D, true, y.nw_1, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->h1, H, EPI_STORE, status, st, b->kpart[0], m->sms, (y.w3.tiles + 7) / 8))) return rc;
-        if ((rc = gemm_batched(y.w3, b->x, D, true, y.nw_3, m->eps, M, b->img[1], b->sv[1], b->osc[1], b->h3, H, EPI_STORE, status, b->aux[0], b->kpart[1], m->sms, (y.w1.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.w1, b->x, D, true, y.nw_1, m->eps, M, b->img[0], b->osc[0], b->h1, H, EPI_STORE, status, st, b->kpart[0], m->sms, (y.w3.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.w3, b->x, D, true, y.nw_3, m->eps, M, b->img[1], b->osc[1], b->h3, H, EPI_STORE, status, b->aux[0], b->kpart[1], m->sms, (y.w1.tiles + 7) / 8))) return rc;
         L2_CUDA(cudaEventRecord(b->join[0], b->aux[0]));
         L2_CUDA(cudaStreamWaitEvent(st, b->join[0], 0));
         launch_swiglu(b->h1, b->h3, b->hb, (size_t)M * H, st);
         // w2 + residual (:279-285)
-        if ((rc = gemm_batched(y.w2, b->hb, H, false, nullptr, m->eps, M, b->img[0], b->sv[0], b->osc[0], b->x, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
+        if ((rc = gemm_batched(y.w2, b->hb, H, false, nullptr, m->eps, M, b->img[0], b->osc[0], b->x, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
     }
     L2_CUDA(cudaGetLastError());
     return L2_OK;

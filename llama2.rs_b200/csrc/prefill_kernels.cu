@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_cons
     const float scale = __uint_as_float((uint32_t)(127 + e) << 23);
     if (tid == 0) P.oscale[m] = rs / scale;
 
-    const size_t img_group = (size_t)P.n * gs;  // bytes of one group's image
+    const size_t img_group = (size_t)P.n * gs + (size_t)P.mpad * 4;  // bytes of one group's block: the digit image, then the tokens' digit sums
     const int rounds = (nblk + AQ_THREADS - 1) / AQ_THREADS;
     for (int k = 0; k < rounds; k++) {
         const int blk = tid + k * AQ_THREADS;
@@ -126,8 +126,8 @@ __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_cons
             s23 += __shfl_xor_sync(0xffffffffu, s23, o);
         }
         if (valid && (tid & (lanes_per_group - 1)) == 0) {
-            P.sv[((size_t)g * P.mpad + m) * 2] = s01;
-            P.sv[((size_t)g * P.mpad + m) * 2 + 1] = s23;
+            // the digit sum of the token's 28-bit integers over the group, as the f32 nearest to it (|s01|, |s23| < 2^22 are exact)
+            *reinterpret_cast<float*>(P.bimg + (size_t)g * img_group + (size_t)P.n * gs + (size_t)m * 4) = fmaf((float)s01, 16384.0f, (float)s23);
         }
     }
 }
