@@ -38,7 +38,7 @@ WORKLOADS = {  # name: (model size, group size, prompt tokens, decode tokens)  -
     "70b": ("70B", 64, 64, 256),
 }
 WEIGHT_SEED, PROMPT_SEED = 20240, 7
-TOKEN_KERNEL_TRAFFIC_RATIO = 1.024  # DRAM bytes / algorithmic bytes of the token kernel, from its ncu capture
+TOKEN_KERNEL_TRAFFIC_RATIO = 1.022  # DRAM bytes / algorithmic bytes of the token kernel, from its ncu capture
 
 
 def measured_peaks():
@@ -195,6 +195,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-warmup", type=int, default=3, help="profiling runs may lower the warm-up floor")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model to this many layers (not a benchmark number)")
+    ap.add_argument("--prompt", type=int, default=0, help="profiling only: prompt tokens instead of the workload's (not a benchmark number)")
     ap.add_argument("--tp-nccl", action="store_true", help="70b on N > 1 GPUs: NCCL all-gathers between per-operator kernels instead of peer-memory stores")
     ap.add_argument("--flags", type=int, default=0, help="L2_FLAG_* bits for the model (8 = one launch per operator instead of one kernel per token)")
     args = ap.parse_args()
@@ -209,6 +210,8 @@ def main():
         args.workload = "70b" if ("WORLD_SIZE" in os.environ or visible_gpus() > 1) else "7b"
     tp = world > 1 and args.workload == "70b"  # 70B is sharded over the ranks (tensor parallel); smaller models run as replicas
     size, gs, n_prompt, n_decode = WORKLOADS[args.workload]
+    if args.prompt > 0:
+        n_prompt = args.prompt
     config = {"workload": "Llama2-%s GPTQ 4-bit g%d act-order, %d-token random prompt, %d greedy decode tokens, batch 1"
                           % (size, gs, n_prompt, n_decode) +
                           (" (default of a scaling run: more than one GPU visible or launched by torch.distributed.run; with one GPU visible the default is the 7B configuration)"
@@ -251,6 +254,8 @@ def main():
     if args.layers:
         cfg.n_layers = args.layers
         config["truncated_layers"] = args.layers
+    if args.prompt > 0:
+        config["profiling_prompt"] = args.prompt
     need_payload = rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "70b"
     payload = l2.synth_fill(cfg, WEIGHT_SEED) if need_payload else None
     if payload is not None:
@@ -357,7 +362,7 @@ def main():
                     "achieved": model.decode_bytes * tok_s / 1e9, "peak": peak, "unit": "GB/s",
                     "frac": model.decode_bytes * tok_s / 1e9 / peak, "peak_kind": peak_kind,
                     # DRAM bytes per launch: ncu capture of the same kernel on a 4-layer model (dram read+write =
-                    # 1.024 x its algorithmic bytes), scaled to a full launch by the bytes processed
+                    # 1.022 x its algorithmic bytes), scaled to a full launch by the bytes processed
                     "traffic": int(TOKEN_KERNEL_TRAFFIC_RATIO * model.decode_bytes),
                     "bytes_per_launch": int(model.decode_bytes), "us_per_launch": 1e6 / tok_s}
     else:

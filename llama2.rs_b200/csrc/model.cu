@@ -1421,6 +1421,7 @@ static int qlinear_reserve(l2_qlinear* h, int B) {
     if (!h->img) {  // buffers of the batched (tcgen05) path, one chunk of MAX_BATCH tokens
         if ((rc = dev_alloc(reinterpret_cast<void**>(&h->img), gemm_tc_image_bytes(h->q.in, h->q.gs, MAX_BATCH), h->allocs))) return rc;
         if ((rc = dev_alloc(reinterpret_cast<void**>(&h->osc), sizeof(float) * MAX_BATCH, h->allocs))) return rc;
+        if ((rc = dev_alloc(reinterpret_cast<void**>(&h->kpart), sizeof(float) * 4 * MAX_BATCH * h->q.out, h->allocs))) return rc;
         if ((rc = dev_alloc(reinterpret_cast<void**>(&h->status), sizeof(int), h->allocs))) return rc;
         L2_CUDA(cudaMemset(h->status, 0, sizeof(int)));
     }
@@ -1438,7 +1439,7 @@ extern "C" int l2_qlinear_matvec_dev(l2_qlinear* h, const float* x_dev, float* x
         for (int b0 = 0; b0 < B; b0 += MAX_BATCH) {
             const int M = std::min<int>(MAX_BATCH, B - b0);
             if (int rc = gemm_batched(h->q, x_dev + (size_t)b0 * h->q.in, h->q.in, true, nullptr, 0.f, M, h->img, h->osc,
-                                      xout_dev + (size_t)b0 * h->q.out, h->q.out, EPI_STORE, h->status, st)) return rc;
+                                      xout_dev + (size_t)b0 * h->q.out, h->q.out, EPI_STORE, h->status, st, h->kpart, h->sms)) return rc;
         }
         return L2_OK;
     }

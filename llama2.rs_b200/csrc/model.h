@@ -139,6 +139,7 @@ struct l2_qlinear {
     l2::SkParams* d_plan = nullptr;
     uint8_t* img = nullptr;   // batched path: digit image with the digit sums, and the factors
     float* osc = nullptr;
+    float* kpart = nullptr;   // [4][MAX_BATCH][out] partial results when the groups of a tile are split over CTAs
     int* status = nullptr;
     int cap_b = 0;
     cudaStream_t stream = nullptr;

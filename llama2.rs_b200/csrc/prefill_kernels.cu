@@ -1,6 +1,7 @@
 // Kernels of the batched forward pass transformer<B>, B >= 2 (src/models.rs:178-298), around the
 // tcgen05 GEMM of gemm_tc.cu: embedding rows, activation quantiser (rmsnorm folded in), RoPE +
 // cache append, causal attention over the cache, SwiGLU.  One CTA per token (and head).
+#include <algorithm>
 #include <cfloat>
 #include <cmath>
 
@@ -37,6 +38,7 @@ __global__ void embed_batch_kernel(const float* __restrict__ table, const int* _
 // the K-major, swizzled byte image the GEMM copies into shared memory: row 4*m + digit, inside a
 // block of 8 inputs the order (0,2,4,6,1,3,5,7) in which a weight word separates into nibbles.
 constexpr int AQ_THREADS = 256;
+constexpr int AQ_CACHE = 2;        // rounds of a CTA's own slice kept in registers between the two passes
 
 __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_constant__ QuantParams P) {
     __shared__ float red[2 * (AQ_THREADS / 32) + 2];
@@ -53,10 +55,28 @@ __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_cons
             v[j] = P.nw ? xv * P.nw[k] : xv;
         }
     };
+    // The row is cut into gridDim.y slices of whole groups; every slice's CTA takes the statistics of the whole row (the
+    // row is 16 to 112 KB and sits in the L2) and writes the digits of its own slice.  It walks the row starting at its
+    // slice and keeps what it fetched there (AQ_CACHE rounds), so its slice is gathered once.
+    const int G = P.in / (int)gs, S = (int)gridDim.y, slice = (int)blockIdx.y;
+    const int b0 = (slice * G / S) * (int)lanes_per_group, nslice = ((slice + 1) * G / S) * (int)lanes_per_group - b0;
+    float cache[AQ_CACHE][8];
     float mx = 0.f, sq = 0.f;
-    for (int blk = tid; blk < nblk; blk += AQ_THREADS) {
+    const int rounds = (nblk + AQ_THREADS - 1) / AQ_THREADS;
+#pragma unroll
+    for (int k = 0; k < AQ_CACHE; k++) {
+        const int idx = tid + k * AQ_THREADS;
+        if (idx < nblk) {
+            fetch(b0 + idx < nblk ? b0 + idx : b0 + idx - nblk, cache[k], sq);
+#pragma unroll
+            for (int j = 0; j < 8; j++) mx = fmaxf(mx, fabsf(cache[k][j]));
+        }
+    }
+    for (int k = AQ_CACHE; k < rounds; k++) {
+        const int idx = tid + k * AQ_THREADS;
+        if (idx >= nblk) break;
         float v[8];
-        fetch(blk, v, sq);
+        fetch(b0 + idx < nblk ? b0 + idx : b0 + idx - nblk, v, sq);
 #pragma unroll
         for (int j = 0; j < 8; j++) mx = fmaxf(mx, fabsf(v[j]));
     }
@@ -81,17 +101,30 @@ __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_cons
     if (mx > 0.f && mx < INFINITY) e = 26 - (int)((__float_as_uint(mx) >> 23) & 255u) + 127;
     e = max(-100, min(100, e));
     const float scale = __uint_as_float((uint32_t)(127 + e) << 23);
-    if (tid == 0) P.oscale[m] = rs / scale;
+    if (tid == 0 && slice == 0) P.oscale[m] = rs / scale;
 
     const size_t img_group = (size_t)P.n * gs + (size_t)P.mpad * 4;  // bytes of one group's block: the digit image, then the tokens' digit sums
-    const int rounds = (nblk + AQ_THREADS - 1) / AQ_THREADS;
-    for (int k = 0; k < rounds; k++) {
-        const int blk = tid + k * AQ_THREADS;
-        if ((blk & ~31) >= nblk) break;  // warp-uniform
-        const bool valid = blk < nblk;
+    const int erounds = (nslice + AQ_THREADS - 1) / AQ_THREADS;
+#pragma unroll 1
+    for (int k = 0; k < erounds; k++) {
+        const int idx = tid + k * AQ_THREADS;
+        if ((idx & ~31) >= nslice) break;  // warp-uniform
+        const bool valid = idx < nslice;   // a group is 4 to 16 adjacent lanes and nslice a multiple of that: valid for all lanes of a group or none
+        const int blk = b0 + idx;
         float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        float dummy = 0.f;
-        if (valid) fetch(blk, v, dummy);
+        if (valid) {
+            static_assert(AQ_CACHE == 2, "the rounds kept in registers are picked by name");
+            if (k == 0) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = cache[0][j];
+            } else if (k == 1) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = cache[1][j];
+            } else {
+                float dummy = 0.f;
+                fetch(blk, v, dummy);
+            }
+        }
         uint32_t E[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
@@ -218,7 +251,10 @@ void launch_embed_batch(const float* table, const int* tokens, float* x, int dim
 }
 void launch_act_quant(const QuantParams& p, int M, cudaStream_t st) {
     g_launches++;
-    act_quant_kernel<<<M, AQ_THREADS, 0, st>>>(p);
+    // slices of about one round of the CTA's threads (256 blocks of 8 inputs), whole groups each
+    const int G = p.in / p.gs;
+    const int S = std::max(1, std::min(std::min(4, G), p.in / 8 / AQ_THREADS));
+    act_quant_kernel<<<dim3(M, S), AQ_THREADS, 0, st>>>(p);
 }
 void launch_rope_append(const RopeParams& p, int n_heads, int M, cudaStream_t st) {
     g_launches++;
