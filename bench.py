@@ -109,7 +109,7 @@ def visible_gpus():
     return n
 
 
-def prefill_report(model, cfg, positions, ms, tp, hbm_peak, tensor_peak, peak_kind):
+def prefill_report(model, cfg, positions, ms, tp, hbm_peak, tensor_peak, peak_kind, cls_rows=None):
     """Batched prefill (the tcgen05 GEMM path) against both rooflines.  Algorithmic flops: 2 * K * N per position and
     QLinear (the classifier is not run in prefill); algorithmic bytes: the QLinear bytes of one pass over the weights per
     chunk of up to 64 positions.  The integer GEMM executes 4 digit columns per position (balanced base-128 digits of the
@@ -119,7 +119,8 @@ def prefill_report(model, cfg, positions, ms, tp, hbm_peak, tensor_peak, peak_ki
     d, h, L = cfg.dim, cfg.hidden_dim, cfg.n_layers
     kv = d * cfg.n_kv_heads // cfg.n_heads
     flops_per_pos = 2.0 * L * (2 * d * d + 2 * d * kv + 3 * d * h)
-    qbytes = float(model.decode_bytes) - 4.0 * cfg.vocab_size * d - 4.0 * (2 * L + 1) * d  # qweight + qzeros + scales of this process's rows
+    cls_rows = cfg.vocab_size if cls_rows is None else cls_rows  # classifier rows this process streams per token (a slice under tensor parallelism over peer memory)
+    qbytes = float(model.decode_bytes) - 4.0 * cls_rows * d - 4.0 * (2 * L + 1) * d  # qweight + qzeros + scales of this process's rows
     passes = positions if tp else (positions + 63) // 64  # tensor-parallel models take the prompt one position at a time
     tflops = flops_per_pos * positions / (ms * 1e-3) / 1e12
     gbs = qbytes * passes / (ms * 1e-3) / 1e9
@@ -376,7 +377,8 @@ def main():
         "warmup": max(args.min_warmup, args.warmup), "ms_per_step": (decode_ms + prefill_ms) / args.steps, "higher_is_better": True,
         "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32 activations / int4 weights", "data": "synthetic", "config": config,
         "prefill_tok_s": streams * pos0 * args.steps / max(prefill_ms, 1e-9) * 1e3,
-        "prefill": prefill_report(model, cfg, pos0, prefill_ms / args.steps, tp, peak, tensor_peak, peak_kind),
+        "prefill": prefill_report(model, cfg, pos0, prefill_ms / args.steps, tp, peak, tensor_peak, peak_kind,
+                                  cls_rows=(cfg.vocab_size * (rank + 1) // world - cfg.vocab_size * rank // world) if tp and not args.tp_nccl else None),
         "decode_ms_per_token": decode_ms / (n_loop * args.steps),
         "roofline": roofline,
         "token_roofline": {"bytes_per_token": model.decode_bytes, "achieved_gbs": model.decode_bytes * tok_s / 1e9,

@@ -146,6 +146,10 @@ struct ClsParams {
     int rows, in;
     float eps;
     int in_phase;         // token kernel only: x is (value, tag) pairs written by this phase
+    // Tensor parallelism over peer memory (token kernel only): this rank computes the logits of vocabulary rows
+    // [row0, row0 + rows) and stores them as (value, tag) pairs into every rank's `tagged` array; null = all rows, plain floats.
+    unsigned long long* tagged;
+    int row0, pad;
 };
 
 struct SelectParams {
@@ -154,6 +158,11 @@ struct SelectParams {
     const int* prompt;
     int* out_tokens;      // [SEQ] next token chosen at each position
     int vocab;
+    // Vocabulary-parallel classifier: the logits arrive as (value, tag) pairs from every rank; the selecting CTA polls
+    // them and writes the plain array first (which the selection, and the host, then read).  null = plain already.
+    const unsigned long long* tagged;
+    int tagged_phase;     // phase that wrote them
+    int collect_only;     // no selection: only the plain array (a forward pass that returns logits)
 };
 
 // ---- the whole token as one persistent kernel (token_kernel.cu) --------------------------------

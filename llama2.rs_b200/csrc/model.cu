@@ -449,14 +449,15 @@ static EmbedParams embed_params(l2_state* s, int kind) {
 
 // The tagged activation vectors of the token kernel live in one pool with the same layout on every rank,
 // so that a rank can store into a peer's pool at the offset it uses in its own.
-struct TaggedLayout { size_t off[11], n[11], total; };
+struct TaggedLayout { size_t off[12], n[12], total; };
 static TaggedLayout tagged_layout(const l2_model* m) {
     const l2_config& c = m->shape.c;
     const size_t D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
-    const size_t n[11] = {D, D, D, D, D, KV, KV, D, D, D, H};  // x, xq, xk, xv, q, k, v, att, x1, x3, hb
+    // x, xq, xk, xv, q, k, v, att, x1, x3, hb; under tensor parallelism also the logits (each rank computes a slice of the vocabulary)
+    const size_t n[12] = {D, D, D, D, D, KV, KV, D, D, D, H, m->tp_world > 1 ? (size_t)c.vocab_size : 0};
     TaggedLayout t{};
     size_t at = 0;
-    for (int i = 0; i < 11; i++) { t.off[i] = at; t.n[i] = n[i]; at += (n[i] * 8 + 255) & ~(size_t)255; }
+    for (int i = 0; i < 12; i++) { t.off[i] = at; t.n[i] = n[i]; at += (n[i] * 8 + 255) & ~(size_t)255; }
     t.total = at;
     return t;
 }
@@ -522,6 +523,7 @@ static int plan_token(l2_state* s) {
         if (!pool) return fail(L2_EINVAL, "token kernel: no activation pool");
         unsigned long long** bufs[11] = {&s->t_x, &s->t_xq, &s->t_xk, &s->t_xv, &s->t_q, &s->t_k, &s->t_v, &s->t_att, &s->t_x1, &s->t_x3, &s->t_hb};
         for (int i = 0; i < 11; i++) *bufs[i] = reinterpret_cast<unsigned long long*>(pool + lay.off[i]);
+        s->t_logits = lay.n[11] ? reinterpret_cast<unsigned long long*>(pool + lay.off[11]) : nullptr;
         // attention: the sequence of a kv head is split over the CTAs (one item per CTA at most); partial results per head and split
         s->tk_max_split = std::max(1, std::min(32, m->sms / std::max(1, c.n_kv_heads / m->tp_world)));
         const size_t part_bytes = (size_t)c.n_heads * s->tk_max_split * (HS + 2) * 8;
@@ -620,17 +622,27 @@ static int build_phase_table(l2_state* s, int kind) {
             }
         }
     }
+    int cls_phase_index = -1;
     if (kind == G_DECODE || kind == G_FWD_CLS) {
         ClsParams cp = classifier_params(s);
         cp.x = must(tg(cp.x));
         cp.in_phase = x_phase;
+        if (direct && s->t_logits) {  // vocabulary-parallel: this rank's slice of the rows, results to every rank as tagged values
+            int row0 = 0, nrows = c.vocab_size;
+            row0 = (int)((long long)c.vocab_size * m->tp_rank / m->tp_world);
+            nrows = (int)((long long)c.vocab_size * (m->tp_rank + 1) / m->tp_world) - row0;
+            cp.row0 = row0; cp.rows = nrows; cp.tagged = s->t_logits;
+        }
+        cls_phase_index = (int)t.size();
         PhaseRec& r = add(PH_CLS);
         r.u.cl = cp;
         r.barrier_after = 1;  // the selection reads every logit
     }
-    if (kind == G_DECODE) {
+    if (kind == G_DECODE || (kind == G_FWD_CLS && direct && s->t_logits)) {
         SelectParams sp{};
         sp.logits = s->logits; sp.ctl = s->ctl; sp.prompt = s->prompt; sp.out_tokens = s->out_tokens; sp.vocab = c.vocab_size;
+        if (direct && s->t_logits) { sp.tagged = s->t_logits; sp.tagged_phase = cls_phase_index; }
+        sp.collect_only = kind == G_FWD_CLS ? 1 : 0;
         add(PH_SELECT).u.se = sp;
     } else if (kind == G_FEED) {
         add(PH_ADVANCE).u.se.ctl = s->ctl;
@@ -931,7 +943,16 @@ extern "C" int l2_model_set_stream(l2_model* m, void* cuda_stream) {
     return L2_OK;
 }
 
-extern "C" uint64_t l2_model_decode_bytes(const l2_model* m) { return m ? m->decode_bytes : 0; }
+extern "C" uint64_t l2_model_decode_bytes(const l2_model* m) {
+    if (!m) return 0;
+    uint64_t b = m->decode_bytes;
+    if (m->tp_world > 1 && m->tp_direct) {  // vocabulary-parallel classifier: this rank streams its slice of the rows only
+        const l2_config& c = m->shape.c;
+        const long long row0 = (long long)c.vocab_size * m->tp_rank / m->tp_world, row1 = (long long)c.vocab_size * (m->tp_rank + 1) / m->tp_world;
+        b -= (uint64_t)(c.vocab_size - (row1 - row0)) * c.dim * 4;
+    }
+    return b;
+}
 
 // ---- C ABI: run state ---------------------------------------------------------------------------
 

@@ -121,6 +121,7 @@ struct l2_state {
     // activations of the token kernel as (value, tag) pairs, 8 bytes per element (see token_kernel.cu)
     unsigned long long *t_x = nullptr, *t_xq = nullptr, *t_xk = nullptr, *t_xv = nullptr, *t_q = nullptr, *t_k = nullptr, *t_v = nullptr;
     unsigned long long *t_att = nullptr, *t_x1 = nullptr, *t_x3 = nullptr, *t_hb = nullptr;
+    unsigned long long* t_logits = nullptr;  // [VOCAB] tagged logits, tensor parallel over peer memory only (every rank computes a slice of the rows)
     unsigned long long* t_part = nullptr;  // [n_heads][tk_max_split][HS + 2] partial attention results of the sequence splits, tagged
     int tk_max_split = 1;
     unsigned long long* tk_trace = nullptr;

@@ -771,10 +771,10 @@ __device__ L2_TK_PHASE_INLINE bool attn_phase(const TokenParams& tk, const AttnP
 }
 
 // final rmsnorm + dense f32 classifier (src/models.rs:288-297, src/model.rs:22-31)
-__device__ __forceinline__ bool cls_phase(const ClsParams& p, float* xs, float* red, uint32_t in_tag) {
+__device__ __forceinline__ bool cls_phase(const TokenParams& tk, const ClsParams& p, float* xs, float* red, uint32_t in_tag, uint32_t out_tag) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r0 = (int)(((long long)blockIdx.x * p.rows) / gridDim.x);
-    const int r1 = (int)(((long long)(blockIdx.x + 1) * p.rows) / gridDim.x);
+    const int r0 = p.row0 + (int)(((long long)blockIdx.x * p.rows) / gridDim.x);  // this rank's rows, dealt out over its CTAs
+    const int r1 = p.row0 + (int)(((long long)(blockIdx.x + 1) * p.rows) / gridDim.x);
     const int n4 = p.in / 4;
     // the residual stream arrives as tagged pairs; the raw values are parked in xs for the second pass
     float4* xs4 = reinterpret_cast<float4*>(xs);
@@ -820,8 +820,13 @@ __device__ __forceinline__ bool cls_phase(const ClsParams& p, float* xs, float* 
         }
         const float ya = tk_warp_sum(a0 + a1), yb = tk_warp_sum(b0 + b1);
         if (lane == 0) {
-            p.logits[row] = ya;
-            if (two) p.logits[row + 1] = yb;
+            if (p.tagged) {  // vocabulary-parallel: every rank gets this rank's logits
+                store_tagged_all(tk, true, p.tagged, (size_t)row, ya, out_tag);
+                if (two) store_tagged_all(tk, true, p.tagged, (size_t)row + 1, yb, out_tag);
+            } else {
+                p.logits[row] = ya;
+                if (two) p.logits[row + 1] = yb;
+            }
         }
     }
     return fine;
@@ -836,7 +841,7 @@ __device__ __forceinline__ unsigned tk_random_u32(unsigned long long& s) {  // s
 
 // Next-token selection by the consumer threads of one CTA: forced / prompt / argmax (last maximum
 // wins, src/util.rs:39-46) / temperature sample (src/inference.rs:164-173, src/util.rs:102-113).
-__device__ __forceinline__ void select_phase(const SelectParams& p, float* scratch) {
+__device__ __forceinline__ bool select_phase(const SelectParams& p, float* scratch, uint32_t tagbase) {
     float* s_val = scratch;                                   // [SK_WARPS]
     int* s_idx = reinterpret_cast<int*>(scratch + SK_WARPS);   // [SK_WARPS]
     float* s_f = scratch + 2 * SK_WARPS;                       // [SK_WARPS + 2]
@@ -847,7 +852,18 @@ __device__ __forceinline__ void select_phase(const SelectParams& p, float* scrat
     unsigned long long rng = ctl->rng;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int V = p.vocab;
-    consumer_sync();  // every thread has read the loop state before thread 0 rewrites it
+    bool fine = true;
+    if (p.tagged) {  // logits from every rank: poll them, keep the plain array (the host reads it too)
+        float* plain = const_cast<float*>(p.logits);
+        const uint32_t tag = tagbase | (uint32_t)p.tagged_phase;
+        for (int i = tid; i < V; i += SK_THREADS) {
+            float v;
+            fine = load_tagged(p.tagged, (size_t)i, tag, v) && fine;
+            plain[i] = v;
+        }
+    }
+    consumer_sync();  // every thread has read the loop state before thread 0 rewrites it; the plain logits are in place
+    if (p.collect_only) return fine;
     int chosen;
     if (force >= 0) {
         chosen = force;
@@ -931,6 +947,7 @@ __device__ __forceinline__ void select_phase(const SelectParams& p, float* scrat
         ctl->token = chosen;
         ctl->pos = pos + 1;
     }
+    return fine;
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
@@ -1055,8 +1072,8 @@ __global__ void __launch_bounds__(TK_BLOCK, 1) token_kernel(const __grid_constan
             case PH_GEMV1:
             case PH_GEMV2: ok = gemv_phase<W>(tk, rec.u.sk, rec.type == PH_GEMV2 ? 2 : 1, smem, R, red, oscale, kbase, stamp, tagbase, p); break;
             case PH_ATTN: fine = attn_phase<AG>(tk, rec.u.at, smem, tok_pos, stamp, tagbase | (uint32_t)rec.u.at.in_phase, out_tag); break;
-            case PH_CLS: fine = cls_phase(rec.u.cl, reinterpret_cast<float*>(smem), red, tagbase | (uint32_t)rec.u.cl.in_phase); break;
-            case PH_SELECT: if (blockIdx.x == 0) select_phase(rec.u.se, red); break;
+            case PH_CLS: fine = cls_phase(tk, rec.u.cl, reinterpret_cast<float*>(smem), red, tagbase | (uint32_t)rec.u.cl.in_phase, out_tag); break;
+            case PH_SELECT: if (blockIdx.x == 0) fine = select_phase(rec.u.se, red, tagbase); break;
             case PH_ADVANCE: if (blockIdx.x == 0 && threadIdx.x == 0) rec.u.se.ctl->pos = rec.u.se.ctl->pos + 1; break;
             default: break;
         }

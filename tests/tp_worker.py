@@ -17,8 +17,16 @@ import oracle as orc  # noqa: E402
 from conftest import assert_close, tiny_config  # noqa: E402
 
 
-def run_case(cfg, rank, world, steps, n_prompt, seed, direct):
+def run_case(cfg, rank, world, steps, n_prompt, seed, direct, ties=False):
     payload = l2.synth_fill(cfg, seed)
+    V, D = cfg.vocab_size, cfg.dim
+    if ties:
+        # The classifier is the last V x D floats of the file (src/gptq.rs:65).  Eight rows below the middle of the vocabulary
+        # are copied onto the eight rows above it and both sets scaled up, so that the largest logit is often an exact tie
+        # between a row of one rank's slice and a row of the next rank's: the last maximum must win (src/util.rs:39-46).
+        wcls = payload[-V * D * 4:].view(np.float32).reshape(V, D)
+        wcls[V // 2 - 8:V // 2] *= np.float32(4.0)
+        wcls[V // 2:V // 2 + 8] = wcls[V // 2 - 8:V // 2]
     gpu = l2.LlamaModel.from_blob(cfg, payload, device=rank, tp=(rank, world))
     if direct:
         # peer memory: every rank maps every other rank's activation pool; the token kernel stores into all of them
@@ -30,6 +38,27 @@ def run_case(cfg, rank, world, steps, n_prompt, seed, direct):
         ids = [l2.tp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         gpu.tp_connect(ids[0])
+    if ties:
+        # (on the model's first run state: under peer memory only that one runs as the token kernel)
+        # temperature sampling: softmax over all ranks' logits, CDF walk in index order, one draw per token (src/util.rs:102-113)
+        st = l2.RunState(gpu)
+        L = orc.lib()
+        import ctypes as C
+        agree = 0
+        for sd in range(1, 21):
+            rnd = l2.Random(sd)
+            nxt, logits = l2.decode_step(gpu, st, 7, 0, temperature=0.8, random=rnd, want_logits=True)
+            p = (logits / np.float32(0.8)).astype(np.float32)
+            L.orc_softmax(p.ctypes.data_as(C.POINTER(C.c_float)), p.size)
+            sv = C.c_uint64(sd)
+            want_tok = L.orc_sample(C.byref(sv), p.ctypes.data_as(C.POINTER(C.c_float)), p.size)
+            assert rnd.seed == sv.value
+            agree += int(nxt == want_tok)
+            picks = [None] * world
+            dist.all_gather_object(picks, int(nxt))
+            assert len(set(picks)) == 1, "ranks sampled different tokens: %s" % picks
+        assert agree >= 19, "sampled tokens differ from the oracle's in %d of 20 draws" % (20 - agree)
+        st.close()
     prompt = np.random.default_rng(seed).integers(0, cfg.vocab_size, n_prompt).astype(np.int32)
     got = l2.generate_ids(gpu, prompt, steps, trace_logits=True)
     fast = l2.generate_ids(gpu, prompt, steps)
@@ -42,6 +71,10 @@ def run_case(cfg, rank, world, steps, n_prompt, seed, direct):
     ref = mine.clone()
     dist.broadcast(ref, src=0)
     assert torch.equal(mine, ref), "rank %d differs from rank 0" % rank
+    if ties:
+        free = got["tokens"][n_prompt - got["pos0"]:]  # tokens chosen by argmax, not forced by the prompt
+        assert not ((free >= V // 2 - 8) & (free < V // 2)).any(), "the first of two equal maxima was chosen"
+        assert ((free >= V // 2) & (free < V // 2 + 8)).any(), "the tie case never occurred: the test checks nothing"
     gpu.close()
 
 
@@ -56,6 +89,7 @@ def main():
     for direct in (False, True):  # NCCL all-gathers between per-operator kernels; stores into peer memory from the token kernel
         run_case(cfg, rank, world, steps=40, n_prompt=21, seed=11, direct=direct)
         run_case(big, rank, world, steps=24, n_prompt=9, seed=12, direct=direct)
+        run_case(cfg, rank, world, steps=48, n_prompt=5, seed=13, direct=direct, ties=True)  # classifier split over the ranks (peer memory) or replicated (NCCL)
         dist.barrier()
         if rank == 0:
             print("tp parity ok (%s)" % ("peer memory" if direct else "nccl"), flush=True)
