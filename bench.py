@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the llama2.rs token loop on B200: batch-1 greedy decode tok/s (and prefill tok/s).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 7b|13b|70b] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 7b|13b|70b|70b-long] [--impl ours|reference]
 
 With one GPU visible the default workload is the 7B configuration the metric is quoted on.  Inside a scaling run (several
 GPUs visible, or launched by torch.distributed.run with one rank per GPU) the default is the 70B configuration, the one
@@ -36,6 +36,8 @@ WORKLOADS = {  # name: (model size, group size, prompt tokens, decode tokens)  -
     "7b": ("7B", 128, 32, 256),
     "13b": ("13B", 128, 128, 512),
     "70b": ("70B", 64, 64, 256),
+    # long-context stress case: the prompt fills three quarters of the 2048-entry KV cache, the decode tokens the rest
+    "70b-long": ("70B", 64, 1536, 512),
 }
 WEIGHT_SEED, PROMPT_SEED = 20240, 7
 TOKEN_KERNEL_TRAFFIC_RATIO = 1.022  # DRAM bytes / algorithmic bytes of the token kernel, from its ncu capture
@@ -143,11 +145,12 @@ class CpuArm:
         import llama2_rs as l2
         import oracle as orc
         self.np, self.orc = np, orc
+        self.workload = workload
         self.size, gs, self.n_prompt, _ = WORKLOADS[workload]
         self.cfg = cfg if cfg is not None else l2.preset_config(self.size, gs)
         self.payload = payload if payload is not None else l2.synth_fill(self.cfg, WEIGHT_SEED)
         self.model = orc.Model(self.cfg, self.payload)
-        self.sample_tokens = {"7b": 8, "13b": 4, "70b": 1}[workload]
+        self.sample_tokens = {"7b": 8, "13b": 4, "70b": 1, "70b-long": 1}[workload]
         self.prompt = make_prompt(np, self.n_prompt, self.cfg.vocab_size)
         self.cores = orc.lib().orc_num_threads()
         self.state = orc.State(self.model)
@@ -180,7 +183,7 @@ class CpuArm:
                 "sample": "%s synthetic checkpoint; set-up (untimed): %d-token prompt, %d positions through the 64/32/16/8/4/2 prefill ladder (%.0f ms, %.1f tok/s); "
                           "timed: %d B=1 positions per step, context %d..%d so far (the GPU arm averages over contexts up to %d)"
                           % (self.size, self.n_prompt, self.prefill_positions, self.prefill_s * 1e3, prefill_tok_s, self.sample_tokens,
-                             self.first_pos, self.pos, self.n_prompt + WORKLOADS[self.size.lower()][3]),
+                             self.first_pos, self.pos, self.n_prompt + WORKLOADS[self.workload][3]),
                 "prefill_tok_s": prefill_tok_s}
 
 
@@ -209,7 +212,7 @@ def main():
         # the 70B configuration, which is the one that shards, at every N including 1, so that the per-N values form the
         # strong-scaling curve of tensor parallelism.
         args.workload = "70b" if ("WORLD_SIZE" in os.environ or visible_gpus() > 1) else "7b"
-    tp = world > 1 and args.workload == "70b"  # 70B is sharded over the ranks (tensor parallel); smaller models run as replicas
+    tp = world > 1 and args.workload.startswith("70b")  # 70B is sharded over the ranks (tensor parallel); smaller models run as replicas
     size, gs, n_prompt, n_decode = WORKLOADS[args.workload]
     if args.prompt > 0:
         n_prompt = args.prompt
@@ -257,7 +260,7 @@ def main():
         config["truncated_layers"] = args.layers
     if args.prompt > 0:
         config["profiling_prompt"] = args.prompt
-    need_payload = rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload != "70b"
+    need_payload = rank == 0 and world == 1 and not args.no_cpu_baseline and not args.workload.startswith("70b")
     payload = l2.synth_fill(cfg, WEIGHT_SEED) if need_payload else None
     if payload is not None:
         model = l2.LlamaModel.from_blob(cfg, payload, device=dev, flags=args.flags)

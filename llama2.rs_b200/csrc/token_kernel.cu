@@ -1050,12 +1050,17 @@ __global__ void __launch_bounds__(TK_BLOCK, 1) token_kernel(const __grid_constan
     unsigned bar_target = tk.bar[33] * gridDim.x;  // arrivals of the grid barriers of earlier launches (the counter is never reset)
     unsigned bars_done = 0;
     bool ok = true;
-    for (int p = 0; p < tk.nphases && ok; p++) {
-        if (!mbar_wait(rec_full + p % TK_NREC, (uint32_t)(p / TK_NREC) & 1u)) {
+    // The record of a phase is waited for before the CTA barrier that ends the previous phase (the copy was requested two
+    // phases earlier), so that a phase boundary costs one barrier, not two.
+    auto await_record = [&](int q) {
+        if (q < tk.nphases && !mbar_wait(rec_full + q % TK_NREC, (uint32_t)(q / TK_NREC) & 1u)) {
             if (tk.status) atomicExch(tk.status, 1005);
             abort_flag = 1;
         }
-        consumer_sync();
+    };
+    await_record(0);
+    consumer_sync();
+    for (int p = 0; p < tk.nphases && ok; p++) {
         if (abort_flag) { ok = false; break; }
         const PhaseRec& rec = recs[p % TK_NREC];
 #ifdef L2_TK_TRACE
@@ -1104,6 +1109,7 @@ __global__ void __launch_bounds__(TK_BLOCK, 1) token_kernel(const __grid_constan
                 __threadfence();
             }
         }
+        await_record(p + 1);
         consumer_sync();  // the next phase reuses this phase's shared memory
         if (abort_flag) { ok = false; break; }
         TK_STAMP(p, 3);
