@@ -123,7 +123,7 @@ def prefill_report(model, cfg, positions, ms, tp, hbm_peak, tensor_peak, peak_ki
     flops_per_pos = 2.0 * L * (2 * d * d + 2 * d * kv + 3 * d * h)
     cls_rows = cfg.vocab_size if cls_rows is None else cls_rows  # classifier rows this process streams per token (a slice under tensor parallelism over peer memory)
     qbytes = float(model.decode_bytes) - 4.0 * cls_rows * d - 4.0 * (2 * L + 1) * d  # qweight + qzeros + scales of this process's rows
-    passes = positions if tp else (positions + 63) // 64  # tensor-parallel models take the prompt one position at a time
+    passes = positions if tp else (positions + 63) // 64  # tp here: tensor parallel over NCCL, which takes the prompt one position at a time
     tflops = flops_per_pos * positions / (ms * 1e-3) / 1e12
     gbs = qbytes * passes / (ms * 1e-3) / 1e9
     return {"positions": positions, "ms": ms, "weight_passes": passes, "tflops": tflops, "tensor_peak_tflops": tensor_peak,
@@ -380,7 +380,7 @@ def main():
         "warmup": max(args.min_warmup, args.warmup), "ms_per_step": (decode_ms + prefill_ms) / args.steps, "higher_is_better": True,
         "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": "f32 activations / int4 weights", "data": "synthetic", "config": config,
         "prefill_tok_s": streams * pos0 * args.steps / max(prefill_ms, 1e-9) * 1e3,
-        "prefill": prefill_report(model, cfg, pos0, prefill_ms / args.steps, tp, peak, tensor_peak, peak_kind,
+        "prefill": prefill_report(model, cfg, pos0, prefill_ms / args.steps, tp and args.tp_nccl, peak, tensor_peak, peak_kind,
                                   cls_rows=(cfg.vocab_size * (rank + 1) // world - cfg.vocab_size * rank // world) if tp and not args.tp_nccl else None),
         "decode_ms_per_token": decode_ms / (n_loop * args.steps),
         "roofline": roofline,

@@ -102,6 +102,7 @@ struct RopeParams {
     const float* rope_cos; const float* rope_sin;
     const int* pos;                              // [M]
     int n_kv_heads, ldq, ldkv;
+    int kv_stride;                               // floats between cache rows of consecutive positions (all kv heads of the model); 0 = n_kv_heads * 128
 };
 
 struct AttnBatchParams {
@@ -109,6 +110,19 @@ struct AttnBatchParams {
     const int* pos;
     float* out;                                  // [M][ldo], natural order
     int n_kv_heads, ag, ldq, ldo;
+    int kv_stride;                               // as in RopeParams
+};
+
+// Batched forward under tensor parallelism: a rank has computed columns [col0, col0 + ncols) of a [M][ld] buffer that every
+// rank keeps at the same offset of its pool; the kernel stores them into every peer's copy, tells the peers and waits for theirs.
+struct TpGatherParams {
+    char* pool[8];              // every rank's pool (this rank's own included)
+    size_t buf_off;             // the buffer inside a pool
+    size_t flag_off;            // [world] 64-bit arrival counters inside a pool: flag[r] of rank q's pool is written by rank r
+    unsigned long long seq;     // this exchange's number (the same on every rank, never repeated)
+    unsigned* done;             // CTAs of this launch that have stored their part (left at zero)
+    int* status;
+    int rank, world, M, ld, col0, ncols;
 };
 
 struct EmbedParams {
@@ -218,7 +232,8 @@ void launch_embed_batch(const float* table, const int* tokens, float* x, int dim
 void launch_act_quant(const QuantParams& p, int M, cudaStream_t st);
 void launch_rope_append(const RopeParams& p, int n_heads, int M, cudaStream_t st);
 void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_t st);
-void launch_swiglu(const float* h1, const float* h3, float* hb, size_t n, cudaStream_t st);
+void launch_tp_gather(const TpGatherParams& p, cudaStream_t st);
+void launch_swiglu(const float* h1, const float* h3, float* hb, int n, int ld, int M, cudaStream_t st);
 // out[m][o] (+)= sum over the K slices, in slice order: finishes a GEMM whose groups were split over several CTAs
 cudaError_t launch_gemm_tc(const TcParams& p, cudaStream_t st);
 cudaError_t gemm_tc_init(int max_smem);

@@ -449,7 +449,7 @@ static EmbedParams embed_params(l2_state* s, int kind) {
 
 // The tagged activation vectors of the token kernel live in one pool with the same layout on every rank,
 // so that a rank can store into a peer's pool at the offset it uses in its own.
-struct TaggedLayout { size_t off[12], n[12], total; };
+struct TaggedLayout { size_t off[12], n[12], total; size_t batch_off[3], flag_off; };
 static TaggedLayout tagged_layout(const l2_model* m) {
     const l2_config& c = m->shape.c;
     const size_t D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
@@ -458,6 +458,11 @@ static TaggedLayout tagged_layout(const l2_model* m) {
     TaggedLayout t{};
     size_t at = 0;
     for (int i = 0; i < 12; i++) { t.off[i] = at; t.n[i] = n[i]; at += (n[i] * 8 + 255) & ~(size_t)255; }
+    if (m->tp_world > 1) {  // batched forward: the vectors every rank needs in full (plain f32 rows of MAX_BATCH tokens) and the exchange counters
+        const size_t bn[3] = {D, D, H};  // x, att, hb
+        for (int i = 0; i < 3; i++) { t.batch_off[i] = at; at += (MAX_BATCH * bn[i] * 4 + 255) & ~(size_t)255; }
+        t.flag_off = at; at += 256;
+    }
     t.total = at;
     return t;
 }
@@ -887,6 +892,8 @@ extern "C" int l2_model_tp_pool_handle(l2_model* m, void* handle64) {
         L2_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->tp_pool), lay.total));
         L2_CUDA(cudaMemset(m->tp_pool, 0, lay.total));
         m->tp_peers[m->tp_rank] = m->tp_pool;
+        for (int i = 0; i < 3; i++) m->tp_batch_off[i] = lay.batch_off[i];
+        m->tp_flag_off = lay.flag_off;
     }
     cudaIpcMemHandle_t h;
     L2_CUDA(cudaIpcGetMemHandle(&h, m->tp_pool));
@@ -1118,8 +1125,11 @@ static int prefill_async(l2_model* m, l2_state* s, const int32_t* prompt, int n_
     int pos = 0;
     int32_t tokens[MAX_BATCH], positions[MAX_BATCH];
     while (pos < target) {
-        // tensor parallel models take the prompt one position at a time (the batched GEMM is single-GPU)
-        const int A = m->tp_world > 1 ? 1 : std::min<int>(MAX_BATCH, target - pos);
+        // tensor parallel models run the batched path when the ranks are connected through peer memory (the exchanges are
+        // stores into the peers' pools) and this state is the one that works in the pool; otherwise one position at a time
+        if (m->tp_direct && !m->tp_pool_owner) m->tp_pool_owner = s;
+        const bool batched = m->tp_world == 1 || (m->tp_direct && token_path(s));
+        const int A = batched ? std::min<int>(MAX_BATCH, target - pos) : 1;
         for (int i = 0; i < A; i++) {
             tokens[i] = pos == 0 ? L2_START : prompt[pos - 1];  // src/inference.rs:29-35
             positions[i] = pos++;

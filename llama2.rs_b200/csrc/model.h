@@ -59,6 +59,8 @@ struct BatchBuffers {
     // independent projections of a layer (wq/wk/wv, w1/w3) run side by side on two more streams
     cudaStream_t aux[2] = {nullptr, nullptr};
     cudaEvent_t fork = nullptr, join[2] = {nullptr, nullptr};
+    bool tp = false;          // tensor parallel over peer memory: x, att and hb live in the model's pool, the other buffers hold this rank's columns
+    unsigned* tp_done = nullptr;  // completion counter of the gather kernel
 };
 
 enum GraphKind : int { G_DECODE = 0, G_FEED, G_FWD_CLS, G_FWD, G_COUNT };
@@ -90,6 +92,9 @@ struct l2_model {
     // pools mapped through CUDA IPC; the first run state of the model works in the pool
     char* tp_pool = nullptr;
     char* tp_peers[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t tp_batch_off[3] = {0, 0, 0};   // batched forward under tensor parallelism: x, att, hb ([MAX_BATCH][dim or hidden] f32) inside the pool
+    size_t tp_flag_off = 0;               // [8] arrival counters of its exchanges
+    unsigned long long tp_batch_seq = 0;  // exchanges made so far (the same on every rank)
     bool tp_peer_borrowed[8] = {false, false, false, false, false, false, false, false};  // attached by pointer: not an IPC mapping to close
     bool tp_direct = false;          // every rank's pool is attached
     l2_state* tp_pool_owner = nullptr;

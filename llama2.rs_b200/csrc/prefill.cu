@@ -59,8 +59,22 @@ static int ensure_batch(l2_state* s) {
     BatchBuffers* b = new BatchBuffers;
     int rc = 0;
     auto F = [&](float** p, size_t n) { return dev_alloc_bytes(reinterpret_cast<void**>(p), n * sizeof(float), s->allocs); };
-    if ((rc = F(&b->x, B * D)) || (rc = F(&b->q, B * D)) || (rc = F(&b->k, B * KV)) || (rc = F(&b->v, B * KV)) ||
-        (rc = F(&b->att, B * D)) || (rc = F(&b->h1, B * H)) || (rc = F(&b->h3, B * H)) || (rc = F(&b->hb, B * H)) ||
+    // Tensor parallel over peer memory: the vectors that every rank needs in full (x, the attention output, the SwiGLU
+    // output) live in the model's pool, where the peers store their columns; q, k, v, h1, h3 hold this rank's columns only.
+    b->tp = m->tp_world > 1;
+    const size_t T = b->tp ? (size_t)m->tp_world : 1;
+    if (b->tp) {
+        if (!m->tp_direct || !m->tp_pool) { delete b; return fail(L2_EINVAL, "batched forward under tensor parallelism needs the peers' pools attached"); }
+        if (!m->tp_pool_owner) m->tp_pool_owner = s;
+        if (m->tp_pool_owner != s) { delete b; return fail(L2_EINVAL, "batched forward under tensor parallelism: another run state of this model works in the pool"); }
+        b->x = reinterpret_cast<float*>(m->tp_pool + m->tp_batch_off[0]);
+        b->att = reinterpret_cast<float*>(m->tp_pool + m->tp_batch_off[1]);
+        b->hb = reinterpret_cast<float*>(m->tp_pool + m->tp_batch_off[2]);
+        if ((rc = dev_alloc_bytes(reinterpret_cast<void**>(&b->tp_done), 256, s->allocs))) { delete b; return rc; }
+        L2_CUDA(cudaMemset(b->tp_done, 0, 256));
+    } else if ((rc = F(&b->x, B * D)) || (rc = F(&b->att, B * D)) || (rc = F(&b->hb, B * H))) { delete b; return rc; }
+    if ((rc = F(&b->q, B * D / T)) || (rc = F(&b->k, B * KV / T)) || (rc = F(&b->v, B * KV / T)) ||
+        (rc = F(&b->h1, B * H / T)) || (rc = F(&b->h3, B * H / T)) ||
         (rc = F(&b->kpart[0], 4 * B * kmax)) || (rc = F(&b->kpart[1], 4 * B * kmax)) || (rc = F(&b->kpart[2], 4 * B * kmax))) { delete b; return rc; }
     for (int i = 0; i < 3; i++) {
         const size_t img_bytes = gemm_tc_image_bytes((int)kmax, c.group_size, (int)B);
@@ -87,7 +101,20 @@ int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos)
     BatchBuffers* b = s->batch;
     cudaStream_t st = m->stream;
     const int D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
+    // this rank's share (everything on one GPU): rows of wq / wo (= heads), of wk / wv (= kv heads), of w1 / w3 / w2's inputs
+    const int T = b->tp ? m->tp_world : 1, R = b->tp ? m->tp_rank : 0;
+    const int Dl = D / T, KVl = KV / T, Hl = H / T, heads_l = c.n_heads / T, kvh_l = c.n_kv_heads / T;
     int* status = &s->ctl->status;
+    // After a stage whose result every rank needs in full, this rank's columns go to the peers (stores over NVLink into their
+    // pools) and the peers' columns are waited for: the same data flow as the tagged exchanges of the token kernel.
+    auto gather = [&](int which, int ld, int col0, int ncols) {
+        if (!b->tp) return;
+        TpGatherParams g{};
+        for (int r = 0; r < 8; r++) g.pool[r] = r < T ? m->tp_peers[r] : nullptr;
+        g.buf_off = m->tp_batch_off[which]; g.flag_off = m->tp_flag_off; g.seq = ++m->tp_batch_seq;
+        g.done = b->tp_done; g.status = status; g.rank = R; g.world = T; g.M = M; g.ld = ld; g.col0 = col0; g.ncols = ncols;
+        launch_tp_gather(g, st);
+    };
     // token ids and positions: own pinned slot per call until the copy has run
     if (++b->stage_slot >= CTL_RING) { L2_CUDA(cudaStreamSynchronize(st)); b->stage_slot = 0; }
     int* hs = b->h_stage + (size_t)b->stage_slot * 2 * MAX_BATCH;
@@ -95,44 +122,49 @@ int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos)
     memcpy(hs + MAX_BATCH, pos, sizeof(int) * M);
     L2_CUDA(cudaMemcpyAsync(b->tok, hs, sizeof(int) * M, cudaMemcpyHostToDevice, st));
     L2_CUDA(cudaMemcpyAsync(b->pos, hs + MAX_BATCH, sizeof(int) * M, cudaMemcpyHostToDevice, st));
-    launch_embed_batch(m->tok_emb, b->tok, b->x, D, M, st);  // src/models.rs:189-191
+    launch_embed_batch(m->tok_emb, b->tok, b->x, D, M, st);  // src/models.rs:189-191 (every rank holds the table: no exchange)
     const size_t ls = (size_t)c.seq_len * KV;
     for (int l = 0; l < c.n_layers; l++) {
         const DevLayer& y = m->layers[l];
         int rc;
-        // rmsnorm + wq/wk/wv (:217-226): three independent GEMMs of 32 CTAs each (7B), side by side on three streams
+        // rmsnorm + wq/wk/wv (:217-226): three independent GEMMs, side by side on three streams
         L2_CUDA(cudaEventRecord(b->fork, st));
         L2_CUDA(cudaStreamWaitEvent(b->aux[0], b->fork, 0));
         L2_CUDA(cudaStreamWaitEvent(b->aux[1], b->fork, 0));
-        if ((rc = gemm_batched(y.wq, b->x, D, true, y.nw_q, m->eps, M, b->img[0], b->osc[0], b->q, D, EPI_STORE, status, st, b->kpart[0], m->sms, (y.wk.tiles + 7) / 8 + (y.wv.tiles + 7) / 8))) return rc;
-        if ((rc = gemm_batched(y.wk, b->x, D, true, y.nw_k, m->eps, M, b->img[1], b->osc[1], b->k, KV, EPI_STORE, status, b->aux[0], b->kpart[1], m->sms, (y.wq.tiles + 7) / 8 + (y.wv.tiles + 7) / 8))) return rc;
-        if ((rc = gemm_batched(y.wv, b->x, D, true, y.nw_v, m->eps, M, b->img[2], b->osc[2], b->v, KV, EPI_STORE, status, b->aux[1], b->kpart[2], m->sms, (y.wq.tiles + 7) / 8 + (y.wk.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.wq, b->x, D, true, y.nw_q, m->eps, M, b->img[0], b->osc[0], b->q, Dl, EPI_STORE, status, st, b->kpart[0], m->sms, (y.wk.tiles + 7) / 8 + (y.wv.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.wk, b->x, D, true, y.nw_k, m->eps, M, b->img[1], b->osc[1], b->k, KVl, EPI_STORE, status, b->aux[0], b->kpart[1], m->sms, (y.wq.tiles + 7) / 8 + (y.wv.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.wv, b->x, D, true, y.nw_v, m->eps, M, b->img[2], b->osc[2], b->v, KVl, EPI_STORE, status, b->aux[1], b->kpart[2], m->sms, (y.wq.tiles + 7) / 8 + (y.wk.tiles + 7) / 8))) return rc;
         for (int i = 0; i < 2; i++) {
             L2_CUDA(cudaEventRecord(b->join[i], b->aux[i]));
             L2_CUDA(cudaStreamWaitEvent(st, b->join[i], 0));
         }
-        // rope, all rows into the cache, then attention (:228-256)
+        // rope, all rows into the cache (this rank's kv heads of the full-width cache rows), then attention (:228-256)
         RopeParams r{};
-        r.q = b->q; r.k = b->k; r.v = b->v; r.kc = s->kc + (size_t)l * ls; r.vc = s->vc + (size_t)l * ls;
+        r.q = b->q; r.k = b->k; r.v = b->v;
+        r.kc = s->kc + (size_t)l * ls + (size_t)R * KVl; r.vc = s->vc + (size_t)l * ls + (size_t)R * KVl;
         r.rope_cos = m->rope_cos; r.rope_sin = m->rope_sin; r.pos = b->pos;
-        r.n_kv_heads = c.n_kv_heads; r.ldq = D; r.ldkv = KV;
-        launch_rope_append(r, c.n_heads, M, st);
+        r.n_kv_heads = kvh_l; r.ldq = Dl; r.ldkv = KVl; r.kv_stride = KV;
+        launch_rope_append(r, heads_l, M, st);
         AttnBatchParams a{};
-        a.q = b->q; a.kc = r.kc; a.vc = r.vc; a.pos = b->pos; a.out = b->att;
-        a.n_kv_heads = c.n_kv_heads; a.ag = m->shape.attn_groups(); a.ldq = D; a.ldo = D;
-        launch_attn_batch(a, c.n_heads, M, st);
-        // wo + residual (:260-264)
-        if ((rc = gemm_batched(y.wo, b->att, D, true, nullptr, m->eps, M, b->img[0], b->osc[0], b->x, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
+        a.q = b->q; a.kc = r.kc; a.vc = r.vc; a.pos = b->pos; a.out = b->att + (size_t)R * Dl;
+        a.n_kv_heads = kvh_l; a.ag = m->shape.attn_groups(); a.ldq = Dl; a.ldo = D; a.kv_stride = KV;
+        launch_attn_batch(a, heads_l, M, st);
+        gather(1, D, R * Dl, Dl);
+        // wo + residual (:260-264): this rank's rows of wo update its columns of x
+        if ((rc = gemm_batched(y.wo, b->att, D, true, nullptr, m->eps, M, b->img[0], b->osc[0], b->x + y.wo.row0, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
+        gather(0, D, y.wo.row0, y.wo.out);
         // rmsnorm + w1/w3 + SwiGLU (:266-276); their rows are stored in w2's K order
         L2_CUDA(cudaEventRecord(b->fork, st));
         L2_CUDA(cudaStreamWaitEvent(b->aux[0], b->fork, 0));
-        if ((rc = gemm_batched(y.w1, b->x, D, true, y.nw_1, m->eps, M, b->img[0], b->osc[0], b->h1, H, EPI_STORE, status, st, b->kpart[0], m->sms, (y.w3.tiles + 7) / 8))) return rc;
-        if ((rc = gemm_batched(y.w3, b->x, D, true, y.nw_3, m->eps, M, b->img[1], b->osc[1], b->h3, H, EPI_STORE, status, b->aux[0], b->kpart[1], m->sms, (y.w1.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.w1, b->x, D, true, y.nw_1, m->eps, M, b->img[0], b->osc[0], b->h1, Hl, EPI_STORE, status, st, b->kpart[0], m->sms, (y.w3.tiles + 7) / 8))) return rc;
+        if ((rc = gemm_batched(y.w3, b->x, D, true, y.nw_3, m->eps, M, b->img[1], b->osc[1], b->h3, Hl, EPI_STORE, status, b->aux[0], b->kpart[1], m->sms, (y.w1.tiles + 7) / 8))) return rc;
         L2_CUDA(cudaEventRecord(b->join[0], b->aux[0]));
         L2_CUDA(cudaStreamWaitEvent(st, b->join[0], 0));
-        launch_swiglu(b->h1, b->h3, b->hb, (size_t)M * H, st);
+        launch_swiglu(b->h1, b->h3, b->hb + y.w1.row0, Hl, H, M, st);
+        gather(2, H, y.w1.row0, y.w1.out);
         // w2 + residual (:279-285)
-        if ((rc = gemm_batched(y.w2, b->hb, H, false, nullptr, m->eps, M, b->img[0], b->osc[0], b->x, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
+        if ((rc = gemm_batched(y.w2, b->hb, H, false, nullptr, m->eps, M, b->img[0], b->osc[0], b->x + y.w2.row0, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
+        gather(0, D, y.w2.row0, y.w2.out);
     }
     L2_CUDA(cudaGetLastError());
     return L2_OK;

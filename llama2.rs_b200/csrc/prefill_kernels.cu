@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(64) rope_append_kernel(const __grid_constant__
         q[HS / 2 + i] = nb;
     }
     if (h < P.n_kv_heads) {
-        const int KV = P.n_kv_heads * HS;
+        const int KV = P.kv_stride ? P.kv_stride : P.n_kv_heads * HS;
         const float* k = P.k + (size_t)m * P.ldkv + (size_t)h * HS;
         const float* v = P.v + (size_t)m * P.ldkv + (size_t)h * HS;
         const float a = k[i], b = k[HS / 2 + i];
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(128) attn_batch_kernel(const __grid_constant__
     __shared__ __align__(16) float sm_acc[4][HS];
     __shared__ float sm_m[4], sm_l[4];
     const int h = blockIdx.x, m = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = h / P.ag, KV = P.n_kv_heads * HS;
+    const int kvh = h / P.ag, KV = P.kv_stride ? P.kv_stride : P.n_kv_heads * HS;
     const int T = P.pos[m] + 1;
     const float4 q = reinterpret_cast<const float4*>(P.q + (size_t)m * P.ldq + (size_t)h * HS)[lane];
     const float4* kc = reinterpret_cast<const float4*>(P.kc) + (size_t)kvh * (HS / 4) + lane;
@@ -237,11 +237,12 @@ __global__ void __launch_bounds__(128) attn_batch_kernel(const __grid_constant__
 }
 
 // ---- hb = silu(h1) * h3 (src/models.rs:92-98) --------------------------------------------------------
-__global__ void swiglu_kernel(const float* __restrict__ h1, const float* __restrict__ h3, float* __restrict__ hb, size_t n) {
+// h1, h3: [M][n] (this process's columns); hb: [M][ld] with those columns at the pointer given
+__global__ void swiglu_kernel(const float* __restrict__ h1, const float* __restrict__ h3, float* __restrict__ hb, int n, int ld, int M) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) {
+    if (i < (size_t)M * n) {
         const float a = h1[i];
-        hb[i] = (a * (1.0f / (1.0f + expf(-a)))) * h3[i];
+        hb[(i / n) * ld + i % n] = (a * (1.0f / (1.0f + expf(-a)))) * h3[i];
     }
 }
 
@@ -264,9 +265,53 @@ void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_
     g_launches++;
     attn_batch_kernel<<<dim3(n_heads, M), 128, 0, st>>>(p);
 }
-void launch_swiglu(const float* h1, const float* h3, float* hb, size_t n, cudaStream_t st) {
+// ---- all-gather of a column slice over peer memory (batched forward under tensor parallelism) ----------------------------
+// Every CTA copies rows of this rank's columns into the peers' buffers with plain stores.  The CTA that finishes last
+// (completion counter behind a system-wide fence) then tells every peer "my part of exchange seq is in your memory" and waits,
+// bounded, until every peer has said the same: after this kernel the whole buffer is valid on this rank.
+constexpr uint32_t TPG_WAIT_LIMIT = 1u << 22;
+__global__ void __launch_bounds__(256) tp_gather_kernel(const __grid_constant__ TpGatherParams P) {
+    __shared__ unsigned last;
+    const int n4 = P.ncols / 4;
+    for (int m = blockIdx.x; m < P.M; m += gridDim.x) {
+        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.pool[P.rank] + P.buf_off) + (size_t)m * P.ld + P.col0);
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = src[i];
+            for (int r = 0; r < P.world; r++)
+                if (r != P.rank) reinterpret_cast<float4*>(reinterpret_cast<float*>(P.pool[r] + P.buf_off) + (size_t)m * P.ld + P.col0)[i] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(P.done, 1u) == gridDim.x - 1 ? 1u : 0u;
+    __syncthreads();
+    if (!last) return;
+    if (threadIdx.x == 0) *P.done = 0;  // ready for the next launch
+    __threadfence_system();
+    const int r = threadIdx.x;
+    if (r < P.world && r != P.rank) {
+        unsigned long long* theirs = reinterpret_cast<unsigned long long*>(P.pool[r] + P.flag_off) + P.rank;
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(theirs), "l"(P.seq) : "memory");
+        const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(P.pool[P.rank] + P.flag_off) + r;
+        bool ok = false;
+#pragma unroll 1
+        for (uint32_t it = 0; it < TPG_WAIT_LIMIT; it++) {
+            unsigned long long v;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
+            if (v >= P.seq) { ok = true; break; }
+            __nanosleep(200);
+        }
+        if (!ok && P.status) atomicCAS(P.status, 0, 3001);
+    }
+}
+void launch_tp_gather(const TpGatherParams& p, cudaStream_t st) {
     g_launches++;
-    swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(h1, h3, hb, n);
+    tp_gather_kernel<<<std::min(p.M, 64), 256, 0, st>>>(p);
+}
+
+void launch_swiglu(const float* h1, const float* h3, float* hb, int n, int ld, int M, cudaStream_t st) {
+    g_launches++;
+    swiglu_kernel<<<(unsigned)(((size_t)M * n + 255) / 256), 256, 0, st>>>(h1, h3, hb, n, ld, M);
 }
 
 __global__ void __launch_bounds__(256) ksum_kernel(const float* __restrict__ part, size_t kstride, int ksplit, float* __restrict__ out,
