@@ -114,8 +114,8 @@ def visible_gpus():
 def prefill_report(model, cfg, positions, ms, tp, hbm_peak, tensor_peak, peak_kind, cls_rows=None):
     """Batched prefill (the tcgen05 GEMM path) against both rooflines.  Algorithmic flops: 2 * K * N per position and
     QLinear (the classifier is not run in prefill); algorithmic bytes: the QLinear bytes of one pass over the weights per
-    chunk of up to 64 positions.  The integer GEMM executes 4 digit columns per position (balanced base-128 digits of the
-    activations), i.e. 4x the algorithmic multiply-adds on the int8 pipe."""
+    chunk of up to 64 positions.  The integer GEMM executes 3 digit columns per position (balanced base-256 digits of the
+    activations), i.e. 3x the algorithmic multiply-adds on the int8 pipe."""
     if positions <= 0 or ms <= 0:
         return None
     d, h, L = cfg.dim, cfg.hidden_dim, cfg.n_layers
@@ -128,7 +128,7 @@ def prefill_report(model, cfg, positions, ms, tp, hbm_peak, tensor_peak, peak_ki
     gbs = qbytes * passes / (ms * 1e-3) / 1e9
     return {"positions": positions, "ms": ms, "weight_passes": passes, "tflops": tflops, "tensor_peak_tflops": tensor_peak,
             "tensor_frac": tflops / tensor_peak, "weight_gbs": gbs, "hbm_frac": gbs / hbm_peak, "peak_kind": peak_kind,
-            "executed_mma_inflation": 1 if tp else 4}
+            "executed_mma_inflation": 1 if tp else 3}
 
 
 def make_prompt(np, n, vocab):

@@ -3,14 +3,14 @@
 //
 //   out[m][o] = f[m] * sum_g scale[o][g] * sum_{k in g} (q[o][k] - z[o][g]) * X[m][k]
 //
-// X[m][k] is the activation of token m as an exact 28-bit integer (four 7-bit digits, see
+// X[m][k] is the activation of token m as a 23-bit signed integer (three balanced base-256 digits, see
 // act_quant_kernel in prefill_kernels.cu), so every product and every sum inside a quantisation
 // group is exact integer arithmetic; f[m] carries the block exponent and the rmsnorm factor.
 //
 // One CTA owns 128 output rows and a slice of the quantisation groups (grid.y slices).  Per group:
 //   A  128 rows x GS weights, unpacked from nibbles to unsigned bytes in shared memory (3 bit
 //      operations per 8 weights), K-major with the 128/64/32-byte swizzle the MMA unit expects;
-//   B  N = 4 digits x M tokens rows x GS signed bytes, one bulk copy from the image the quantiser
+//   B  N = 3 digits x M tokens rows x GS signed bytes, one bulk copy from the image the quantiser
 //      wrote (already swizzled);
 //   D  128 x N s32 in tensor memory, overwritten by the first MMA of the group (GS/32 MMAs of K = 32).
 //
@@ -51,7 +51,7 @@ constexpr int TC_RING = 4;       // barrier ring of groups in flight (full / don
 constexpr int TC_RAW = 8;        // raw ring: groups whose packed weight words are in shared memory or on their way there
 constexpr int TC_SIDE = 12;      // side ring (scales, zero points, digit sums)
 constexpr int TC_AHEAD = TC_RAW - 1;  // groups between a request and the step that makes it (both rings)
-constexpr int MAX_TOKENS = 64;   // tokens of one pass (N = 4 * tokens <= 256 columns)
+constexpr int MAX_TOKENS = 64;   // tokens of one pass (N = 3 * tokens <= 192 columns)
 constexpr int TC_HALF = MAX_TOKENS / 2;   // tokens a drain thread holds at most
 constexpr int TC_META = 8 * 80;  // bytes of a group's scales and zero points: 20 words of each of the 8 records
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 20;
@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_tc_kernel(const __grid_
         const int tq = P.mpad / 2;                               // tokens per column half, a multiple of 8 (mpad % 16 == 0)
         const uint32_t moff_s = (uint32_t)(row >> 4) * 20u + (uint32_t)(orow & 15), moff_z = (uint32_t)(row >> 4) * 20u + 16u + (uint32_t)((orow & 15) >> 3);
         const uint32_t zsh = 4 * (orow & 7);
-        const uint32_t tcol = tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(half * tq * 4);
+        const uint32_t tcol = tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(half * tq);  // column of digit p, token t: p * mpad + t
         // ---- side ring: 16-byte pieces of the 8 records' scales and zero points (40) and of the tokens' digit sums (mpad / 4)
         const bool has_m = dt < 40, has_s = dt >= 64 && dt < 64 + (int)(sv_bytes / 16);
         const uint32_t* rq_m = P.rec + ((size_t)min(tile * 8 + dt / 5, P.tiles16 - 1) * Gfull + gb) * UW + 64 * W + (size_t)(dt % 5) * 4;
@@ -308,30 +308,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_tc_kernel(const __grid_
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tbase = tcol + b * 256u;
 #pragma unroll
-            for (int c0 = 0; c0 < TC_HALF * 4; c0 += 32) {  // 32 columns = 8 tokens per load
-                if (c0 >= tq * 4) break;  // warp-uniform: tq is a multiple of 8
-                uint32_t v[32];
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                             "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
-                               "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-                               "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                             : "r"(tbase + (uint32_t)c0) : "memory");
+            for (int t0 = 0; t0 < TC_HALF; t0 += 16) {  // 16 tokens per step: one 16-column load per digit
+                if (t0 >= tq) break;  // warp-uniform: tq is a multiple of 8
+                uint32_t v[3][16];
+#pragma unroll
+                for (int p = 0; p < 3; p++)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(v[p][0]), "=r"(v[p][1]), "=r"(v[p][2]), "=r"(v[p][3]), "=r"(v[p][4]), "=r"(v[p][5]), "=r"(v[p][6]), "=r"(v[p][7]),
+                                   "=r"(v[p][8]), "=r"(v[p][9]), "=r"(v[p][10]), "=r"(v[p][11]), "=r"(v[p][12]), "=r"(v[p][13]), "=r"(v[p][14]), "=r"(v[p][15])
+                                 : "r"(tbase + (uint32_t)(p * P.mpad + t0)) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c0 + 32 >= tq * 4) {  // the last columns of this accumulator have been read: the MMAs of group g + 2 may overwrite it
+                if (t0 + 16 >= tq) {  // the last columns of this accumulator have been read: the MMAs of group g + 2 may overwrite it
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(&acc_free[b]);
                 }
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    // c0 2^21 + c1 2^14 + c2 2^7 + c3 (|c| < 2^18), each half rounded once to f32: the upper half as an
-                    // integer through the conversion unit (quarter rate, but it takes one issue slot), the lower half
-                    // through floats: an integer below 2^22 becomes a float exactly with one integer add and one float add.
-                    // The zero point enters through the token's digit sum (a float).
-                    const int tk = c0 / 4 + q;  // token inside this half
-                    const float fh = (float)((int)v[4 * q] * 128 + (int)v[4 * q + 1]);
-                    const float fl = fmaf(magic_float((int)v[4 * q + 2]), 128.0f, magic_float((int)v[4 * q + 3]));
-                    acc[tk] = fmaf(nzs, sv[tk], fmaf(scf, fmaf(fh, 16384.0f, fl), acc[tk]));
+                for (int q8 = 0; q8 < 16; q8 += 8) {
+                    if (t0 + q8 < tq) {  // warp-uniform
+#pragma unroll
+                        for (int q = q8; q < q8 + 8; q++) {
+                            // c0 2^16 + c1 2^8 + c2 (|c| < 2^18): the upper two as an integer through the conversion unit (quarter
+                            // rate, but one issue slot; rounded once to f32), the lowest through floats: an integer below 2^22 becomes
+                            // a float exactly with one integer add and one float add.  The zero point enters through the token's sum
+                            // of integers over the group (a float).
+                            const int tk = t0 + q;  // token inside this half
+                            const float fh = (float)((int)v[0][q] * 256 + (int)v[1][q]);
+                            acc[tk] = fmaf(nzs, sv[tk], fmaf(scf, fmaf(fh, 256.0f, magic_float((int)v[2][q])), acc[tk]));
+                        }
+                    }
                 }
             }
             dr_side = dr_side == TC_SIDE - 1 ? 0 : dr_side + 1;
@@ -410,7 +414,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_tc_kernel(const __grid_
 // at least 120 KB so that only one CTA (one owner of the tensor memory) is resident per SM
 size_t gemm_tc_smem_bytes(int gs, int n) {
     const size_t need = (size_t)TC_STAGES * ((size_t)128 * gs + (((size_t)n * gs + 1023) & ~(size_t)1023)) + (size_t)TC_RAW * 8 * 64 * (gs / 32) * 4 +
-                        (size_t)TC_SIDE * (TC_META + (size_t)n) + 1024;  // digit sums: 4 bytes per token = n
+                        (size_t)TC_SIDE * (TC_META + (size_t)n / 3 * 4) + 1024;  // digit sums: 4 bytes per token, n = 3 tokens
     return need < 120 * 1024 ? 120 * 1024 : need;
 }
 
@@ -418,7 +422,7 @@ int gemm_tc_mpad(int tokens) { return (tokens + 15) & ~15; }
 
 size_t gemm_tc_image_bytes(int in, int gs, int tokens) {
     const size_t mpad = (size_t)gemm_tc_mpad(tokens);
-    return (size_t)(in / gs) * (4 * mpad * gs + mpad * 4);
+    return (size_t)(in / gs) * (3 * mpad * gs + mpad * 4);
 }
 
 cudaError_t gemm_tc_init(int max_smem) {

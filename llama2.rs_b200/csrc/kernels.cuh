@@ -79,7 +79,7 @@ struct TcParams {
     float* out;            // [M][ldo]
     int* status;
     int tiles16, G, gs, rows;
-    int m, mpad, n;        // tokens, tokens padded to a multiple of 16, n = 4 * mpad
+    int m, mpad, n;        // tokens, tokens padded to a multiple of 16, n = 3 * mpad (three digits per token)
     int ldo, epi;
     int ksplit;            // > 1: the groups are split over gridDim.y CTAs; slice k stores part + k * kstride [m][rows]
     size_t kstride;

@@ -21,12 +21,12 @@ int gemm_batched(const DevQ& q, const float* x, int ldx, bool gather, const floa
     QuantParams a{};
     a.x = x; a.perm = gather ? q.perm : nullptr; a.nw = nw;
     a.bimg = img; a.oscale = osc;
-    a.in = q.in; a.gs = q.gs; a.ldx = ldx; a.mpad = mpad; a.n = 4 * mpad; a.eps = eps;
+    a.in = q.in; a.gs = q.gs; a.ldx = ldx; a.mpad = mpad; a.n = 3 * mpad; a.eps = eps;
     launch_act_quant(a, M, st);
     TcParams t{};
     t.rec = q.rec; t.bimg = img; t.oscale = osc; t.out = out; t.status = status;
     t.tiles16 = q.tiles; t.G = q.G; t.gs = q.gs; t.rows = q.out;
-    t.m = M; t.mpad = mpad; t.n = 4 * mpad; t.ldo = ldo; t.epi = epi;
+    t.m = M; t.mpad = mpad; t.n = 3 * mpad; t.ldo = ldo; t.epi = epi;
     // A matrix with few 128-row tiles would leave most SMs idle: its groups are split over several CTAs
     // per tile, which store partial results that a small kernel adds up in slice order.
     // (side_tiles: 128-row tiles of the GEMMs that run side by side with this one on other streams)

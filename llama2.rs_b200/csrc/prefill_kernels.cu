@@ -34,9 +34,10 @@ __global__ void embed_batch_kernel(const float* __restrict__ table, const int* _
 // ---- activation quantiser ---------------------------------------------------------------------
 // Token m of x (natural order) is gathered into the consumer's K order, multiplied by the rmsnorm
 // weight (linearity: the 1/sqrt(mean(x^2)+eps) factor goes into oscale), scaled by a power of two
-// so that |X| < 2^27 and written as four 7-bit digits (d0 = X >> 21 signed, d1..d3 in 0..127) into
-// the K-major, swizzled byte image the GEMM copies into shared memory: row 4*m + digit, inside a
-// block of 8 inputs the order (0,2,4,6,1,3,5,7) in which a weight word separates into nibbles.
+// so that |X| <= 2^22 (23 of the 24 bits of an f32 mantissa for the token's largest element) and written
+// as three balanced base-256 digits (-128..127 each) into the K-major, swizzled byte image the GEMM
+// copies into shared memory: row digit * mpad + m (most significant digit first), inside a block of
+// 8 inputs the order (0,2,4,6,1,3,5,7) in which a weight word separates into nibbles.
 constexpr int AQ_THREADS = 256;
 constexpr int AQ_CACHE = 2;        // rounds of a CTA's own slice kept in registers between the two passes
 
@@ -98,7 +99,8 @@ __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_cons
     const float total = red[2 * (AQ_THREADS / 32) + 1];
     const float rs = P.nw ? 1.0f / sqrtf(total / (float)P.in + P.eps) : 1.0f;  // src/models.rs:58-60
     int e = 0;
-    if (mx > 0.f && mx < INFINITY) e = 26 - (int)((__float_as_uint(mx) >> 23) & 255u) + 127;
+    // |x| * scale < 2^22: three balanced digits reach from -0x808080 to 0x7F7F7F, a little short of 2^23
+    if (mx > 0.f && mx < INFINITY) e = 21 - (int)((__float_as_uint(mx) >> 23) & 255u) + 127;
     e = max(-100, min(100, e));
     const float scale = __uint_as_float((uint32_t)(127 + e) << 23);
     if (tid == 0 && slice == 0) P.oscale[m] = rs / scale;
@@ -125,42 +127,44 @@ __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_cons
                 fetch(blk, v, dummy);
             }
         }
-        uint32_t E[8];
+        uint32_t E[8];  // per element: bytes d2, d1, d0 (least significant digit first), balanced: X = d0 2^16 + d1 2^8 + d2, d in -128..127
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const uint32_t X = (uint32_t)__float2int_rn(v[j] * scale);
-            E[j] = (X & 0x7Fu) | ((X << 1) & 0x7F00u) | ((X << 2) & 0x7F0000u) | ((X << 3) & 0xFF000000u);
+            const int X = __float2int_rn(v[j] * scale);
+            E[j] = ((uint32_t)X + 0x00808080u) ^ 0x00808080u;
         }
-        uint32_t lo[4], hi[4];
+        // 4x4 byte transposes: words of one digit for inputs (0,2,4,6) and (1,3,5,7), the order in which the nibbles of a
+        // weight word separate into its low and high halves; index 0 = most significant digit
+        uint32_t lo[3], hi[3];
         {
             const uint32_t a = __byte_perm(E[0], E[2], 0x5140), b = __byte_perm(E[0], E[2], 0x7362);
             const uint32_t c = __byte_perm(E[4], E[6], 0x5140), d = __byte_perm(E[4], E[6], 0x7362);
-            lo[3] = __byte_perm(a, c, 0x5410); lo[2] = __byte_perm(a, c, 0x7632);
-            lo[1] = __byte_perm(b, d, 0x5410); lo[0] = __byte_perm(b, d, 0x7632);
+            lo[2] = __byte_perm(a, c, 0x5410); lo[1] = __byte_perm(a, c, 0x7632);
+            lo[0] = __byte_perm(b, d, 0x5410);
         }
         {
             const uint32_t a = __byte_perm(E[1], E[3], 0x5140), b = __byte_perm(E[1], E[3], 0x7362);
             const uint32_t c = __byte_perm(E[5], E[7], 0x5140), d = __byte_perm(E[5], E[7], 0x7362);
-            hi[3] = __byte_perm(a, c, 0x5410); hi[2] = __byte_perm(a, c, 0x7632);
-            hi[1] = __byte_perm(b, d, 0x5410); hi[0] = __byte_perm(b, d, 0x7632);
+            hi[2] = __byte_perm(a, c, 0x5410); hi[1] = __byte_perm(a, c, 0x7632);
+            hi[0] = __byte_perm(b, d, 0x5410);
         }
         const int g = valid ? (int)((uint32_t)(blk * 8) / gs) : 0;
         const uint32_t kb = (uint32_t)(blk * 8) % gs;
-        int sum[4];
+        int sum[3];
 #pragma unroll
-        for (int p = 0; p < 4; p++) {
+        for (int p = 0; p < 3; p++) {
             if (valid)
-                *reinterpret_cast<uint2*>(P.bimg + (size_t)g * img_group + swz((uint32_t)(4 * m + p), kb, gs)) = make_uint2(lo[p], hi[p]);
+                *reinterpret_cast<uint2*>(P.bimg + (size_t)g * img_group + swz((uint32_t)(p * P.mpad + m), kb, gs)) = make_uint2(lo[p], hi[p]);
             sum[p] = __dp4a((int)lo[p], 0x01010101, __dp4a((int)hi[p], 0x01010101, 0));
         }
-        int s01 = 128 * sum[0] + sum[1], s23 = 128 * sum[2] + sum[3];
+        int s01 = 256 * sum[0] + sum[1], s2 = sum[2];
         for (uint32_t o = 1; o < lanes_per_group; o <<= 1) {
             s01 += __shfl_xor_sync(0xffffffffu, s01, o);
-            s23 += __shfl_xor_sync(0xffffffffu, s23, o);
+            s2 += __shfl_xor_sync(0xffffffffu, s2, o);
         }
         if (valid && (tid & (lanes_per_group - 1)) == 0) {
-            // the digit sum of the token's 28-bit integers over the group, as the f32 nearest to it (|s01|, |s23| < 2^22 are exact)
-            *reinterpret_cast<float*>(P.bimg + (size_t)g * img_group + (size_t)P.n * gs + (size_t)m * 4) = fmaf((float)s01, 16384.0f, (float)s23);
+            // the sum of the token's integers over the group, as the f32 nearest to it (|s01| < 2^23 and |s2| < 2^15 are exact)
+            *reinterpret_cast<float*>(P.bimg + (size_t)g * img_group + (size_t)P.n * gs + (size_t)m * 4) = fmaf((float)s01, 256.0f, (float)s2);
         }
     }
 }
