@@ -119,7 +119,7 @@ struct TpGatherParams {
     char* pool[8];              // every rank's pool (this rank's own included)
     size_t buf_off;             // the buffer inside a pool
     size_t flag_off;            // [world] 64-bit arrival counters inside a pool: flag[r] of rank q's pool is written by rank r
-    unsigned long long seq;     // this exchange's number (the same on every rank, never repeated)
+    unsigned long long* seq;    // device counter of exchanges made: the kernel takes the next number (the same on every rank, never repeated)
     unsigned* done;             // CTAs of this launch that have stored their part (left at zero)
     int* status;
     int rank, world, M, ld, col0, ncols;

@@ -61,6 +61,8 @@ struct BatchBuffers {
     cudaEvent_t fork = nullptr, join[2] = {nullptr, nullptr};
     bool tp = false;          // tensor parallel over peer memory: x, att and hb live in the model's pool, the other buffers hold this rank's columns
     unsigned* tp_done = nullptr;  // completion counter of the gather kernel
+    cudaGraphExec_t graph[MAX_BATCH + 1] = {};  // the pass as a CUDA graph, per batch size
+    int graph_nodes[MAX_BATCH + 1] = {};
 };
 
 enum GraphKind : int { G_DECODE = 0, G_FEED, G_FWD_CLS, G_FWD, G_COUNT };
@@ -93,8 +95,7 @@ struct l2_model {
     char* tp_pool = nullptr;
     char* tp_peers[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     size_t tp_batch_off[3] = {0, 0, 0};   // batched forward under tensor parallelism: x, att, hb ([MAX_BATCH][dim or hidden] f32) inside the pool
-    size_t tp_flag_off = 0;               // [8] arrival counters of its exchanges
-    unsigned long long tp_batch_seq = 0;  // exchanges made so far (the same on every rank)
+    size_t tp_flag_off = 0;               // [8] arrival counters of its exchanges; at + 128 bytes this rank's count of exchanges made
     bool tp_peer_borrowed[8] = {false, false, false, false, false, false, false, false};  // attached by pointer: not an IPC mapping to close
     bool tp_direct = false;          // every rank's pool is attached
     l2_state* tp_pool_owner = nullptr;

@@ -94,34 +94,29 @@ static int ensure_batch(l2_state* s) {
     return L2_OK;
 }
 
-int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos) {
-    if (int rc = ensure_batch(s)) return rc;
+// The kernels of one batched forward of M tokens (their ids and positions already in b->tok / b->pos), enqueued on `st`
+// and, for the projections that run side by side, on the two auxiliary streams forked from it and joined back.
+static int enqueue_batch(l2_state* s, int M, cudaStream_t st) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
     BatchBuffers* b = s->batch;
-    cudaStream_t st = m->stream;
     const int D = c.dim, KV = m->shape.kv_dim(), H = c.hidden_dim;
     // this rank's share (everything on one GPU): rows of wq / wo (= heads), of wk / wv (= kv heads), of w1 / w3 / w2's inputs
     const int T = b->tp ? m->tp_world : 1, R = b->tp ? m->tp_rank : 0;
     const int Dl = D / T, KVl = KV / T, Hl = H / T, heads_l = c.n_heads / T, kvh_l = c.n_kv_heads / T;
     int* status = &s->ctl->status;
     // After a stage whose result every rank needs in full, this rank's columns go to the peers (stores over NVLink into their
-    // pools) and the peers' columns are waited for: the same data flow as the tagged exchanges of the token kernel.
+    // pools) and the peers' columns are waited for: the same data flow as the tagged exchanges of the token kernel.  The
+    // exchanges are numbered by a counter on the device (every rank makes the same exchanges in the same order), so that
+    // the launch parameters do not change from call to call and the pass can be replayed as a CUDA graph.
     auto gather = [&](int which, int ld, int col0, int ncols) {
         if (!b->tp) return;
         TpGatherParams g{};
         for (int r = 0; r < 8; r++) g.pool[r] = r < T ? m->tp_peers[r] : nullptr;
-        g.buf_off = m->tp_batch_off[which]; g.flag_off = m->tp_flag_off; g.seq = ++m->tp_batch_seq;
+        g.buf_off = m->tp_batch_off[which]; g.flag_off = m->tp_flag_off; g.seq = reinterpret_cast<unsigned long long*>(m->tp_pool + m->tp_flag_off + 128);  // in the pool: it outlives run states, like the peers' counters
         g.done = b->tp_done; g.status = status; g.rank = R; g.world = T; g.M = M; g.ld = ld; g.col0 = col0; g.ncols = ncols;
         launch_tp_gather(g, st);
     };
-    // token ids and positions: own pinned slot per call until the copy has run
-    if (++b->stage_slot >= CTL_RING) { L2_CUDA(cudaStreamSynchronize(st)); b->stage_slot = 0; }
-    int* hs = b->h_stage + (size_t)b->stage_slot * 2 * MAX_BATCH;
-    memcpy(hs, tokens, sizeof(int) * M);
-    memcpy(hs + MAX_BATCH, pos, sizeof(int) * M);
-    L2_CUDA(cudaMemcpyAsync(b->tok, hs, sizeof(int) * M, cudaMemcpyHostToDevice, st));
-    L2_CUDA(cudaMemcpyAsync(b->pos, hs + MAX_BATCH, sizeof(int) * M, cudaMemcpyHostToDevice, st));
     launch_embed_batch(m->tok_emb, b->tok, b->x, D, M, st);  // src/models.rs:189-191 (every rank holds the table: no exchange)
     const size_t ls = (size_t)c.seq_len * KV;
     for (int l = 0; l < c.n_layers; l++) {
@@ -167,6 +162,45 @@ int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos)
         gather(0, D, y.w2.row0, y.w2.out);
     }
     L2_CUDA(cudaGetLastError());
+    return L2_OK;
+}
+
+// One batched forward.  The ids and positions travel through a pinned ring; the kernels of the pass (about 25 per layer,
+// most of them a few microseconds long: launched one by one the host cannot keep up with the GPU) are captured once per
+// batch size into a CUDA graph and replayed.
+int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos) {
+    if (int rc = ensure_batch(s)) return rc;
+    l2_model* m = s->m;
+    BatchBuffers* b = s->batch;
+    cudaStream_t st = m->stream;
+    if (M < 1 || M > MAX_BATCH) return fail(L2_EINVAL, "forward_batch: %d tokens", M);
+    // token ids and positions: own pinned slot per call until the copy has run
+    if (++b->stage_slot >= CTL_RING) { L2_CUDA(cudaStreamSynchronize(st)); b->stage_slot = 0; }
+    int* hs = b->h_stage + (size_t)b->stage_slot * 2 * MAX_BATCH;
+    memcpy(hs, tokens, sizeof(int) * M);
+    memcpy(hs + MAX_BATCH, pos, sizeof(int) * M);
+    L2_CUDA(cudaMemcpyAsync(b->tok, hs, sizeof(int) * M, cudaMemcpyHostToDevice, st));
+    L2_CUDA(cudaMemcpyAsync(b->pos, hs + MAX_BATCH, sizeof(int) * M, cudaMemcpyHostToDevice, st));
+    if (!m->use_graph) return enqueue_batch(s, M, st);
+    if (!b->graph[M]) {
+        cudaStream_t cap;
+        L2_CUDA(cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking));
+        const unsigned long long before = g_launches;
+        L2_CUDA(cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal));
+        const int rc = enqueue_batch(s, M, cap);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(cap, &graph);
+        b->graph_nodes[M] = (int)(g_launches - before);
+        g_launches = before;  // captured launches have not run
+        cudaStreamDestroy(cap);
+        if (rc != L2_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+        if (e != cudaSuccess) return fail(L2_ECUDA, "batched forward: graph capture failed: %s", cudaGetErrorString(e));
+        const cudaError_t e2 = cudaGraphInstantiate(&b->graph[M], graph, 0);
+        cudaGraphDestroy(graph);
+        if (e2 != cudaSuccess) { b->graph[M] = nullptr; return fail(L2_ECUDA, "batched forward: graph instantiate failed: %s", cudaGetErrorString(e2)); }
+    }
+    L2_CUDA(cudaGraphLaunch(b->graph[M], st));
+    g_launches += b->graph_nodes[M];
     return L2_OK;
 }
 

@@ -276,6 +276,7 @@ void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_
 constexpr uint32_t TPG_WAIT_LIMIT = 1u << 22;
 __global__ void __launch_bounds__(256) tp_gather_kernel(const __grid_constant__ TpGatherParams P) {
     __shared__ unsigned last;
+    __shared__ unsigned long long seq_s;
     const int n4 = P.ncols / 4;
     for (int m = blockIdx.x; m < P.M; m += gridDim.x) {
         const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.pool[P.rank] + P.buf_off) + (size_t)m * P.ld + P.col0);
@@ -290,19 +291,21 @@ __global__ void __launch_bounds__(256) tp_gather_kernel(const __grid_constant__ 
     if (threadIdx.x == 0) last = atomicAdd(P.done, 1u) == gridDim.x - 1 ? 1u : 0u;
     __syncthreads();
     if (!last) return;
-    if (threadIdx.x == 0) *P.done = 0;  // ready for the next launch
+    if (threadIdx.x == 0) { *P.done = 0; seq_s = ++*P.seq; }  // ready for the next launch; this exchange's number
     __threadfence_system();
+    __syncthreads();
+    const unsigned long long seq = seq_s;
     const int r = threadIdx.x;
     if (r < P.world && r != P.rank) {
         unsigned long long* theirs = reinterpret_cast<unsigned long long*>(P.pool[r] + P.flag_off) + P.rank;
-        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(theirs), "l"(P.seq) : "memory");
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(theirs), "l"(seq) : "memory");
         const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(P.pool[P.rank] + P.flag_off) + r;
         bool ok = false;
 #pragma unroll 1
         for (uint32_t it = 0; it < TPG_WAIT_LIMIT; it++) {
             unsigned long long v;
             asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
-            if (v >= P.seq) { ok = true; break; }
+            if (v >= seq) { ok = true; break; }
             __nanosleep(200);
         }
         if (!ok && P.status) atomicCAS(P.status, 0, 3001);
