@@ -1,6 +1,6 @@
 // Device-side building blocks shared by the stand-alone GEMV kernel (gemv_kernels.cu) and the
 // one-kernel-per-token path (token_kernel.cu): integer MMA, mbarriers, bulk copies, the barrier of
-// the consumer warps, and the staging of an activation vector as 7-bit digits.
+// the consumer warps, and the staging of an activation vector as signed byte digits (per-operator kernels: 7-bit digits).
 #pragma once
 
 #include <cfloat>

@@ -45,7 +45,7 @@ struct DevLayer {
 
 constexpr int CTL_RING = 128;
 constexpr int L2_MAX_TP = 8;   // ranks of a tensor-parallel group (the GPUs of one box)
-constexpr int MAX_BATCH = 64;  // tokens of one batched forward (one tcgen05 tile holds 4 digits x 64 tokens)
+constexpr int MAX_BATCH = 64;  // tokens of one batched forward (one tcgen05 accumulator holds 3 digits x 64 tokens = 192 columns)
 
 // Device buffers of the batched forward pass (transformer<B>, B >= 2).
 struct BatchBuffers {
