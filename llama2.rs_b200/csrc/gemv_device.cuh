@@ -476,10 +476,50 @@ __device__ __forceinline__ float stage_direct(const void* x_tagged, int in, uint
 
 template <int W>
 __device__ __forceinline__ float stage_natural(const SkSeg* seg, int nseg, int in, int G, uint8_t* digits, int pstride, uint4* sp, float* xs, uint32_t tag,
-                                               bool* fail, unsigned long long* stamp = nullptr) {
+                                               bool* fail, bool gather, unsigned long long* stamp = nullptr) {
     const int nblk = in / 8;
     float* xs1 = xs + in;  // the second matrix's K order (w3 beside w1)
     float sq = 0.f;
+    if (gather) {
+        // Two matrices on a long input (w1 and w3 of the 70B shapes): two K-ordered copies of the vector would take the
+        // shared memory of a ring slot or two, and the ring's depth is what the weight stream of these shapes is short of.
+        // The vector is kept once, in natural order, and each matrix's blocks are gathered from it through its g_index
+        // (seg[s].perm: forward 16-bit indices) when the digits are cut.
+#pragma unroll 1
+        for (int blk = threadIdx.x; blk < nblk; blk += SK_THREADS) {
+            float4 w0 = make_float4(1.f, 1.f, 1.f, 1.f), w1 = w0;
+            if (seg[0].nw) {
+                w0 = __ldg(reinterpret_cast<const float4*>(seg[0].nw) + 2 * blk);
+                w1 = __ldg(reinterpret_cast<const float4*>(seg[0].nw) + 2 * blk + 1);
+            }
+            float4 v0, v1;
+            if (!load_tagged8(seg[0].x, (size_t)blk * 8, tag, v0, v1)) *fail = true;
+            sq += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w + v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+            v0.x *= w0.x; v0.y *= w0.y; v0.z *= w0.z; v0.w *= w0.w;
+            v1.x *= w1.x; v1.y *= w1.y; v1.z *= w1.z; v1.w *= w1.w;
+            reinterpret_cast<float4*>(xs)[2 * blk] = v0;
+            reinterpret_cast<float4*>(xs)[2 * blk + 1] = v1;
+        }
+        if (stamp && threadIdx.x == 0) stamp[21] = clock64();
+        consumer_sync();
+        if (stamp && threadIdx.x == 0) stamp[22] = clock64();
+#pragma unroll 1
+        for (int s = 0; s < nseg; s++) {
+#pragma unroll 1
+            for (int blk = threadIdx.x; (blk & ~31) < nblk; blk += SK_THREADS) {
+                const bool valid = blk < nblk;
+                float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (valid) {
+                    const uint4 ix = __ldg(reinterpret_cast<const uint4*>(seg[s].perm) + blk);
+                    v[0] = xs[ix.x & 0xFFFFu]; v[1] = xs[ix.x >> 16]; v[2] = xs[ix.y & 0xFFFFu]; v[3] = xs[ix.y >> 16];
+                    v[4] = xs[ix.z & 0xFFFFu]; v[5] = xs[ix.z >> 16]; v[6] = xs[ix.w & 0xFFFFu]; v[7] = xs[ix.w >> 16];
+                }
+                stage_emit8<W>(v, valid, blk, digits + (size_t)s * in, pstride, sp + s * G);
+            }
+        }
+        if (stamp && threadIdx.x == 0) stamp[23] = clock64();
+        return sq;
+    }
     // (1) everything that does not depend on the awaited values is requested first: positions and norm weights
 #pragma unroll 1
     for (int blk = threadIdx.x; blk < nblk; blk += SK_THREADS) {

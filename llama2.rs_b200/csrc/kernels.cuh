@@ -52,6 +52,9 @@ struct SkJob {
     // table) that write this job's inputs and the residual it adds to
     int in_phase[2], resid_phase;
     int bcast;  // tensor parallel token kernel: the results are stored into every rank's buffers, not only this one's
+    int gather; // token kernel, two matrices on one input (w1, w3): seg[].perm are FORWARD 16-bit indices (position p of the K order reads
+                // input perm[p]); the input is kept once in natural order and each matrix's digits are gathered from it
+    int pad1;
 };
 
 struct alignas(16) SkParams {
@@ -220,7 +223,7 @@ cudaError_t launch_token(const TokenParams& tk, int group_size, int attn_groups,
 cudaError_t token_set_poll_limit(unsigned polls);  // polls of a tagged input before giving up; 0 = default
 cudaError_t token_init(int max_optin);     // max_optin: opt-in shared memory per block of the device
 size_t token_attn_scratch_bytes(int ag);   // shared memory the attention phase needs
-size_t token_gemv_smem(int in, int G, int nseg, int ptiles, bool natural);  // shared memory a GEMV phase of the token kernel needs in front of the ring
+size_t token_gemv_smem(int in, int G, int nseg, int ptiles, bool natural, bool gather);  // shared memory a GEMV phase of the token kernel needs in front of the ring
 
 void launch_embed(const EmbedParams& p, cudaStream_t st, bool pdl);
 // `p` points to device memory: the kernel copies the record into shared memory with one cooperative load

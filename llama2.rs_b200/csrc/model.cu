@@ -96,6 +96,8 @@ int upload_qlinear(const PackedQ& p, const int32_t* g_index, DevQ& d, std::vecto
         if (p.in < 65536) {
             std::vector<uint16_t> i16(inv.begin(), inv.end());
             if (int rc = dev_upload(&d.inv16, i16.data(), (size_t)p.in, allocs, bytes)) return rc;
+            std::vector<uint16_t> p16(g_index, g_index + p.in);
+            if (int rc = dev_upload(&d.perm16, p16.data(), (size_t)p.in, allocs, bytes)) return rc;
         }
     }
     return L2_OK;
@@ -475,30 +477,54 @@ static bool token_path(const l2_state* s) {
     return m->tp_world == 1 || (m->tp_direct && m->tp_pool_owner == s);
 }
 
-// Ring geometry and shared-memory carve-up shared by every phase of the token kernel.
-static int plan_token(l2_state* s) {
-    l2_model* m = s->m;
+// Shared memory in front of the ring (the largest need of any phase) and the ring slots that fit behind it.  The next
+// smaller carve-out (196 KB) leaves 60 KB of L1 instead of 28 KB, which the kernel's local memory (stack, the few spilled
+// registers of 544 threads) and read-only operands need more than a fourth or fifth ring slot (measured: 3 slots of 35 KB beat
+// 5 on the 7B model); the largest carve-out only where the ring would otherwise be shorter than three slots.
+static size_t tk_fixed_bytes(const l2_state* s, bool gather13) {
+    const l2_model* m = s->m;
     const l2_config& c = m->shape.c;
     size_t fixed = std::max<size_t>(token_attn_scratch_bytes(m->shape.attn_groups()), (size_t)c.dim * 4);
     for (int which = 0; which < 4; which++) {
         const SkLaunch& L = s->plans[which];  // every layer has the same shapes
         int max_g = 0;
         for (int i = 0; i < L.p.njobs; i++) max_g = std::max(max_g, L.p.job[i].G);
-        fixed = std::max(fixed, token_gemv_smem(L.p.job[0].in, max_g, L.nseg, L.p.ptiles, which != 3));  // all inputs but w2's arrive in natural order
+        // all inputs but w2's arrive in natural order
+        fixed = std::max(fixed, token_gemv_smem(L.p.job[0].in, max_g, L.nseg, L.p.ptiles, which != 3, which == 2 && gather13));
     }
-    fixed = (fixed + 127) & ~(size_t)127;
-    const int su = 2 * SK_WARPS;  // unit records per slot fill: every consumer warp takes one pair
-    // Shared memory: the next smaller carve-out (196 KB) leaves 60 KB of L1 instead of 28 KB, which the kernel's local
-    // memory (stack, the few spilled registers of 544 threads) and read-only operands need more than a fourth or fifth
-    // ring slot (measured: 3 slots of 35 KB beat 5 on the 7B model); the largest carve-out only where the ring would
-    // otherwise be shorter than three slots.
+    return (fixed + 127) & ~(size_t)127;
+}
+static int tk_slots(const l2_state* s, size_t fixed, int su) {
     int slots = 0;
     size_t budget = 190 * 1024;
     if (const char* e = getenv("L2_TK_SMEM_KB")) budget = (size_t)std::max(64, std::min(222, atoi(e))) * 1024;  // tuning knob
     for (int attempt = 0; attempt < 2; attempt++, budget = 222 * 1024) {
-        slots = fixed < budget ? (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(c.group_size, su)) : 0;
+        slots = fixed < budget ? (int)std::min<size_t>(SK_MAX_SLOTS, (budget - fixed) / sk_slot_bytes(s->m->shape.c.group_size, su)) : 0;
         if (slots >= 3) break;
     }
+    return slots;
+}
+// w1 and w3 read one input through two different g_index orders.  Keeping the input once in natural order and gathering each
+// matrix's blocks from it saves 4 * dim bytes of shared memory against two K-ordered copies, at the price of scattered
+// shared-memory reads while the digits are cut.  It is used where it lets three ring slots fit into the smaller carve-out
+// (13B and 70B shapes; measured on the 70B shapes: + 3 %, the same with three slots and 60 KB of L1 as with four slots and
+// 28 KB), or where it buys a slot at all.
+static bool tk_gather13(const l2_state* s) {
+    const int su = 2 * SK_WARPS;
+    if (const char* e = getenv("L2_TK_GATHER13")) return atoi(e) != 0;  // tuning knob
+    const size_t with = tk_fixed_bytes(s, true), without = tk_fixed_bytes(s, false);
+    const size_t three = 3 * sk_slot_bytes(s->m->shape.c.group_size, su), small = 190 * 1024;
+    if (without + three > small && with + three <= small) return true;
+    return tk_slots(s, with, su) > tk_slots(s, without, su);
+}
+
+// Ring geometry and shared-memory carve-up shared by every phase of the token kernel.
+static int plan_token(l2_state* s) {
+    l2_model* m = s->m;
+    const l2_config& c = m->shape.c;
+    const int su = 2 * SK_WARPS;  // unit records per slot fill: every consumer warp takes one pair
+    const size_t fixed = tk_fixed_bytes(s, tk_gather13(s));
+    int slots = tk_slots(s, fixed, su);
     if (slots < 2) return fail(L2_EINVAL, "the token kernel needs %zu bytes of shared memory before its weight ring", fixed);
     if (const char* e = getenv("L2_SK_SLOTS")) slots = std::max(2, std::min(slots, atoi(e)));
     s->tk = TokenParams{};
@@ -587,7 +613,10 @@ static int build_phase_table(l2_state* s, int kind) {
             // w2's K order) already write in the right order.
             const DevLayer& y = m->layers[l];
             auto p16 = [](const DevQ& q) { return reinterpret_cast<const int*>(q.inv16); };
-            const int* perms[4][3] = {{p16(y.wq), p16(y.wk), p16(y.wv)}, {p16(y.wo), nullptr, nullptr}, {p16(y.w1), p16(y.w3), nullptr}, {nullptr, nullptr, nullptr}};
+            auto f16 = [](const DevQ& q) { return reinterpret_cast<const int*>(q.perm16); };
+            const bool g13 = tk_gather13(s);
+            const int* perms[4][3] = {{p16(y.wq), p16(y.wk), p16(y.wv)}, {p16(y.wo), nullptr, nullptr},
+                                      {g13 ? f16(y.w1) : p16(y.w1), g13 ? f16(y.w3) : p16(y.w3), nullptr}, {nullptr, nullptr, nullptr}};
             const float* norms[4] = {y.rms_att, nullptr, y.rms_ffn, nullptr};
             if (c.dim >= 65536) return fail(L2_EINVAL, "token kernel: DIM %d does not fit 16-bit gather indices", c.dim);
             float* inputs[4] = {reinterpret_cast<float*>(s->t_x), reinterpret_cast<float*>(s->t_att), reinterpret_cast<float*>(s->t_x), reinterpret_cast<float*>(s->t_hb)};
@@ -596,6 +625,7 @@ static int build_phase_table(l2_state* s, int kind) {
                 for (int sg = 0; sg < L.nseg; sg++) {
                     J.seg[sg].x = inputs[which];
                     J.seg[sg].perm = perms[which][which == 2 ? sg : j];
+                    J.gather = which == 2 && g13 ? 1 : 0;
                     J.seg[sg].nw = norms[which];
                     J.in_phase[sg] = in_phase;
                 }

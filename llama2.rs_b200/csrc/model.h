@@ -24,6 +24,7 @@ struct DevQ {
     uint32_t* rec = nullptr;   // [tiles][G] unit records: weights, scales, zero nibbles (see repack.cpp)
     int* perm = nullptr;  // g_index: permuted position j reads input perm[j]
     int* inv = nullptr;   // inverse: input o is written to permuted position inv[o]
+    uint16_t* perm16 = nullptr;  // perm as 16-bit indices
     uint16_t* inv16 = nullptr;   // inv as 16-bit indices (IN < 65536): where the token kernel puts input o when it brings a vector into K order
     int in = 0, out = 0, tiles = 0, G = 0, gs = 0;  // out / tiles: the rows held by this process
     int row0 = 0;                                   // first row held (tensor parallelism), else 0

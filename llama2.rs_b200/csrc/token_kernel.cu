@@ -203,10 +203,10 @@ __device__ __forceinline__ void warm_operands(const SkParams& P, int NSEG) {
 // runs each phase's code once per layer, so what is not shared is fetched from the L2 every time:
 // the instruction cache of an SM holds far less than an unrolled copy per phase type would need).
 // Shared memory in front of the weight ring that a GEMV phase needs (host side of the carve-up in gemv_phase).
-size_t token_gemv_smem(int in, int G, int nseg, int ptiles, bool natural) {
+size_t token_gemv_smem(int in, int G, int nseg, int ptiles, bool natural, bool gather) {
     size_t b = (size_t)4 * ((size_t)nseg * in + 16);       // digit planes
     b += (size_t)nseg * G * 16;                            // group records
-    if (natural) b += (size_t)nseg * in * 4;               // the vector in each matrix's K order as plain floats
+    if (natural) b += (size_t)(gather ? 1 : nseg) * in * 4;  // the vector as plain floats: in each matrix's K order, or once in natural order
     b += (size_t)ptiles * SK_WARPS * 32 * 4;               // tile sums per warp
     return b;
 }
@@ -236,7 +236,7 @@ __device__ L2_TK_PHASE_INLINE bool gemv_phase(const TokenParams& tk, const SkPar
     uint4* sp = reinterpret_cast<uint4*>(smem + (size_t)4 * pstride);    // [nseg * G] group records
     const bool natural = J.seg[0].perm != nullptr;                       // the input arrives in natural order and is gathered into the K order
     float* xs = reinterpret_cast<float*>(sp + Gs);                       // [nseg][in] the vector in each matrix's K order as plain floats (only then)
-    float* partial = xs + (natural ? nseg * J.in : 0);                   // [nt][SK_WARPS][PROWS]
+    float* partial = xs + (natural ? (J.gather ? 1 : nseg) * J.in : 0);  // [nt][SK_WARPS][PROWS]
 
     for (int i = threadIdx.x; i < nt * SK_WARPS * PROWS; i += SK_THREADS) partial[i] = 0.f;
     bool stage_failed = false;  // a poll for a tagged input gave up
@@ -244,7 +244,7 @@ __device__ L2_TK_PHASE_INLINE bool gemv_phase(const TokenParams& tk, const SkPar
     if (n > 0) {
         float sq;
         if (natural)  // w1 and w3 read the same x, each through its own g_index
-            sq = stage_natural<W>(J.seg, nseg, J.in, G, digits, pstride, sp, xs, tagbase | (uint32_t)J.in_phase[0], &stage_failed, stamp);
+            sq = stage_natural<W>(J.seg, nseg, J.in, G, digits, pstride, sp, xs, tagbase | (uint32_t)J.in_phase[0], &stage_failed, J.gather != 0, stamp);
         else          // the producer's row order is this matrix's K order (w2 after w1/w3)
             sq = stage_direct<W>(J.seg[0].x, J.in, digits, pstride, sp, tagbase | (uint32_t)J.in_phase[0], &stage_failed, stamp);
         if (stamp && threadIdx.x == 0) stamp[17] = clock64();
