@@ -271,6 +271,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_tc_kernel(const __grid_
         const uint32_t zsh = 4 * (orow & 7);
         const uint32_t tcol = tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(half * tq);  // column of digit p, token t: p * mpad + t
         // ---- side ring: 16-byte pieces of the 8 records' scales and zero points (40) and of the tokens' digit sums (mpad / 4)
+        // the tokens' digit sums are written by the quantiser that runs in front of this kernel; with a programmatic launch
+        // this kernel may have started before that one finished (the loaders need nothing of it): wait for it here
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const bool has_m = dt < 40, has_s = dt >= 64 && dt < 64 + (int)(sv_bytes / 16);
         const uint32_t* rq_m = P.rec + ((size_t)min(tile * 8 + dt / 5, P.tiles16 - 1) * Gfull + gb) * UW + 64 * W + (size_t)(dt % 5) * 4;
         const uint8_t* rq_s = P.bimg + (size_t)gb * img_group + b_bytes + (size_t)(dt - 64) * 16;
@@ -391,6 +394,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_tc_kernel(const __grid_
     } else {
         // ================= B stages: one thread ========================================================================
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // the digit image is the output of the kernel in front of this one
             uint32_t s = 0;
             const uint8_t* src = P.bimg + (size_t)gb * img_group;
 #pragma unroll 1
@@ -432,14 +436,24 @@ cudaError_t gemm_tc_init(int max_smem) {
     return cudaFuncSetAttribute(gemm_q4_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
 }
 
+// Launched programmatically after the activation quantiser: set-up, tensor-memory allocation and the first weight requests
+// of this kernel overlap the quantiser's run (about a third of a short GEMM is the time to fill its pipeline); the two
+// roles that read the quantiser's output wait for it inside the kernel.
 cudaError_t launch_gemm_tc(const TcParams& p, cudaStream_t st) {
-    const dim3 grid((p.tiles16 + 7) / 8, p.ksplit > 1 ? p.ksplit : 1);
-    const size_t smem = gemm_tc_smem_bytes(p.gs, p.n);
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3((p.tiles16 + 7) / 8, p.ksplit > 1 ? p.ksplit : 1);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = gemm_tc_smem_bytes(p.gs, p.n);
+    cfg.stream = st;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     g_launches++;
-    if (p.gs == 128) gemm_q4_tc_kernel<4><<<grid, TC_THREADS, smem, st>>>(p);
-    else if (p.gs == 64) gemm_q4_tc_kernel<2><<<grid, TC_THREADS, smem, st>>>(p);
-    else gemm_q4_tc_kernel<1><<<grid, TC_THREADS, smem, st>>>(p);
-    return cudaGetLastError();
+    if (p.gs == 128) return cudaLaunchKernelEx(&cfg, gemm_q4_tc_kernel<4>, p);
+    if (p.gs == 64) return cudaLaunchKernelEx(&cfg, gemm_q4_tc_kernel<2>, p);
+    return cudaLaunchKernelEx(&cfg, gemm_q4_tc_kernel<1>, p);
 }
 
 }  // namespace l2

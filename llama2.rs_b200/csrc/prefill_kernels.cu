@@ -43,6 +43,9 @@ constexpr int AQ_CACHE = 2;        // rounds of a CTA's own slice kept in regist
 
 __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const __grid_constant__ QuantParams P) {
     __shared__ float red[2 * (AQ_THREADS / 32) + 2];
+    // the GEMM behind this kernel is launched programmatically: it may start now (its loaders need nothing from here) and
+    // waits inside for this grid to finish before it reads the image
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int m = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const float* x = P.x + (size_t)m * P.ldx;
     const int nblk = P.in / 8;
