@@ -495,6 +495,7 @@ cudaError_t kernels_init() {
     if ((e = cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
     if ((e = sk_init(max_optin - 2048)) != cudaSuccess) return e;
     if ((e = gemm_tc_init(max_optin - 2048)) != cudaSuccess) return e;
+    if ((e = attn_batch_init()) != cudaSuccess) return e;
     if ((e = token_init(max_optin)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(cls_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_optin - 2048)) != cudaSuccess) return e;
     return cudaSuccess;

@@ -234,12 +234,13 @@ cudaError_t sk_init(int max_smem);
 void launch_embed_batch(const float* table, const int* tokens, float* x, int dim, int M, cudaStream_t st);
 void launch_act_quant(const QuantParams& p, int M, cudaStream_t st);
 void launch_rope_append(const RopeParams& p, int n_heads, int M, cudaStream_t st);
-void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_t st);
+void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, bool tiled, cudaStream_t st);
 void launch_tp_gather(const TpGatherParams& p, cudaStream_t st);
 void launch_swiglu(const float* h1, const float* h3, float* hb, int n, int ld, int M, cudaStream_t st);
 // out[m][o] (+)= sum over the K slices, in slice order: finishes a GEMM whose groups were split over several CTAs
 cudaError_t launch_gemm_tc(const TcParams& p, cudaStream_t st);
 cudaError_t gemm_tc_init(int max_smem);
+cudaError_t attn_batch_init();
 void launch_ksum(const float* part, size_t kstride, int ksplit, float* out, int ldo, int rows, int M, int epi, cudaStream_t st);
 size_t gemm_tc_smem_bytes(int gs, int n);
 int gemm_tc_mpad(int tokens);  // tokens of a pass, padded to the granularity of the kernel's drain (16)

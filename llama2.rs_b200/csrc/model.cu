@@ -1080,8 +1080,9 @@ extern "C" void l2_state_free(l2_state* s) {
             if (s->batch->join[i]) cudaEventDestroy(s->batch->join[i]);
         }
         if (s->batch->fork) cudaEventDestroy(s->batch->fork);
-        for (cudaGraphExec_t g : s->batch->graph)
-            if (g) cudaGraphExecDestroy(g);
+        for (auto& row : s->batch->graph)
+            for (cudaGraphExec_t g : row)
+                if (g) cudaGraphExecDestroy(g);
         delete s->batch;
     }
     if (s->m->gen_state == s) s->m->gen_state = nullptr;

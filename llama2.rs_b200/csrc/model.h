@@ -62,8 +62,8 @@ struct BatchBuffers {
     cudaEvent_t fork = nullptr, join[2] = {nullptr, nullptr};
     bool tp = false;          // tensor parallel over peer memory: x, att and hb live in the model's pool, the other buffers hold this rank's columns
     unsigned* tp_done = nullptr;  // completion counter of the gather kernel
-    cudaGraphExec_t graph[MAX_BATCH + 1] = {};  // the pass as a CUDA graph, per batch size
-    int graph_nodes[MAX_BATCH + 1] = {};
+    cudaGraphExec_t graph[2][MAX_BATCH + 1] = {};  // the pass as a CUDA graph, per (short / long context, batch size)
+    int graph_nodes[2][MAX_BATCH + 1] = {};
 };
 
 enum GraphKind : int { G_DECODE = 0, G_FEED, G_FWD_CLS, G_FWD, G_COUNT };

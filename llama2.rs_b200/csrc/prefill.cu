@@ -96,7 +96,7 @@ static int ensure_batch(l2_state* s) {
 
 // The kernels of one batched forward of M tokens (their ids and positions already in b->tok / b->pos), enqueued on `st`
 // and, for the projections that run side by side, on the two auxiliary streams forked from it and joined back.
-static int enqueue_batch(l2_state* s, int M, cudaStream_t st) {
+static int enqueue_batch(l2_state* s, int M, bool long_context, cudaStream_t st) {
     l2_model* m = s->m;
     const l2_config& c = m->shape.c;
     BatchBuffers* b = s->batch;
@@ -143,7 +143,7 @@ static int enqueue_batch(l2_state* s, int M, cudaStream_t st) {
         AttnBatchParams a{};
         a.q = b->q; a.kc = r.kc; a.vc = r.vc; a.pos = b->pos; a.out = b->att + (size_t)R * Dl;
         a.n_kv_heads = kvh_l; a.ag = m->shape.attn_groups(); a.ldq = Dl; a.ldo = D; a.kv_stride = KV;
-        launch_attn_batch(a, heads_l, M, st);
+        launch_attn_batch(a, heads_l, M, long_context, st);
         gather(1, D, R * Dl, Dl);
         // wo + residual (:260-264): this rank's rows of wo update its columns of x
         if ((rc = gemm_batched(y.wo, b->att, D, true, nullptr, m->eps, M, b->img[0], b->osc[0], b->x + y.wo.row0, D, EPI_RESID, status, st, b->kpart[0], m->sms, 0))) return rc;
@@ -181,26 +181,30 @@ int forward_batch(l2_state* s, int M, const int32_t* tokens, const int32_t* pos)
     memcpy(hs + MAX_BATCH, pos, sizeof(int) * M);
     L2_CUDA(cudaMemcpyAsync(b->tok, hs, sizeof(int) * M, cudaMemcpyHostToDevice, st));
     L2_CUDA(cudaMemcpyAsync(b->pos, hs + MAX_BATCH, sizeof(int) * M, cudaMemcpyHostToDevice, st));
-    if (!m->use_graph) return enqueue_batch(s, M, st);
-    if (!b->graph[M]) {
+    // two graphs per batch size: the attention kernel differs between short and long contexts
+    int last = 0;
+    for (int i = 0; i < M; i++) last = std::max(last, (int)pos[i]);
+    const int lc = last >= 192 ? 1 : 0;
+    if (!m->use_graph) return enqueue_batch(s, M, lc != 0, st);
+    if (!b->graph[lc][M]) {
         cudaStream_t cap;
         L2_CUDA(cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking));
         const unsigned long long before = g_launches;
         L2_CUDA(cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal));
-        const int rc = enqueue_batch(s, M, cap);
+        const int rc = enqueue_batch(s, M, lc != 0, cap);
         cudaGraph_t graph = nullptr;
         const cudaError_t e = cudaStreamEndCapture(cap, &graph);
-        b->graph_nodes[M] = (int)(g_launches - before);
+        b->graph_nodes[lc][M] = (int)(g_launches - before);
         g_launches = before;  // captured launches have not run
         cudaStreamDestroy(cap);
         if (rc != L2_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
         if (e != cudaSuccess) return fail(L2_ECUDA, "batched forward: graph capture failed: %s", cudaGetErrorString(e));
-        const cudaError_t e2 = cudaGraphInstantiate(&b->graph[M], graph, 0);
+        const cudaError_t e2 = cudaGraphInstantiate(&b->graph[lc][M], graph, 0);
         cudaGraphDestroy(graph);
-        if (e2 != cudaSuccess) { b->graph[M] = nullptr; return fail(L2_ECUDA, "batched forward: graph instantiate failed: %s", cudaGetErrorString(e2)); }
+        if (e2 != cudaSuccess) { b->graph[lc][M] = nullptr; return fail(L2_ECUDA, "batched forward: graph instantiate failed: %s", cudaGetErrorString(e2)); }
     }
-    L2_CUDA(cudaGraphLaunch(b->graph[M], st));
-    g_launches += b->graph_nodes[M];
+    L2_CUDA(cudaGraphLaunch(b->graph[lc][M], st));
+    g_launches += b->graph_nodes[lc][M];
     return L2_OK;
 }
 

@@ -268,9 +268,141 @@ void launch_rope_append(const RopeParams& p, int n_heads, int M, cudaStream_t st
     g_launches++;
     rope_append_kernel<<<dim3(n_heads, M), 64, 0, st>>>(p);
 }
-void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, cudaStream_t st) {
+
+// ---- the same attention with the cache rows shared by the queries that need them ---------------------------------------
+// One CTA takes a kv head and a block of tokens: all their queries (AG heads per token) walk the cache together, 32
+// positions at a time.  A tile of K and V rows is brought into shared memory once and used by up to 64 queries, instead of
+// once per (head, token) as above — at a context of 1500 that kernel moved 64 times the cache through the L2 per kv head
+// and was a fifth of a long prompt's prefill.  Scores: lane = position, the query comes as broadcast loads from shared
+// memory; softmax state per query (online, one rescale per tile); values: lane = four of the 128 dimensions, the
+// probabilities come by shuffle.  Plain f32 FMAs: the arithmetic is the reference's, only the order of the sums differs.
+constexpr int AT_WARPS = 8, AT_TILE = 32, AT_KPAD = HS + 4;  // K rows padded: a lane reads "its" row without bank conflicts
+template <int AG, int NQW>  // query heads per kv head; queries per warp (NQW / AG tokens)
+__global__ void __launch_bounds__(32 * AT_WARPS) attn_batch_tiled_kernel(const __grid_constant__ AttnBatchParams P, int M) {
+    extern __shared__ __align__(16) float at_smem[];
+    constexpr int TPW = NQW / AG;                       // tokens per warp
+    constexpr int QB = AT_WARPS * TPW;                  // tokens per CTA
+    float* Qs = at_smem;                                // [AT_WARPS * NQW][HS]
+    float* Ks = Qs + AT_WARPS * NQW * HS;               // [AT_TILE][AT_KPAD]
+    float* Vs = Ks + AT_TILE * AT_KPAD;                 // [AT_TILE][HS]
+    const int kvh = blockIdx.x, m0 = blockIdx.y * QB, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int KV = P.kv_stride ? P.kv_stride : P.n_kv_heads * HS;
+    const float div = sqrtf((float)HS);
+    // queries of this CTA: query i = (token m0 + i / AG, head kvh * AG + i % AG)
+    for (int i = tid; i < AT_WARPS * NQW * (HS / 4); i += 32 * AT_WARPS) {
+        const int qi = i / (HS / 4), c = i % (HS / 4), m = m0 + qi / AG;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m < M) v = reinterpret_cast<const float4*>(P.q + (size_t)m * P.ldq + (size_t)(kvh * AG + qi % AG) * HS)[c];
+        reinterpret_cast<float4*>(Qs)[i] = v;
+    }
+    int last[TPW];   // last position each of this warp's tokens attends to (-1: no such token)
+    int tmax = -1;   // over the CTA
+#pragma unroll
+    for (int j = 0; j < TPW; j++) {
+        const int m = m0 + warp * TPW + j;
+        last[j] = m < M ? P.pos[m] : -1;
+    }
+    for (int m = m0; m < min(M, m0 + QB); m++) tmax = max(tmax, P.pos[m]);
+    float mx[NQW], l[NQW];
+    float4 acc[NQW];
+#pragma unroll
+    for (int q = 0; q < NQW; q++) { mx[q] = -INFINITY; l[q] = 0.f; acc[q] = make_float4(0.f, 0.f, 0.f, 0.f); }
+    const float4* kc = reinterpret_cast<const float4*>(P.kc) + (size_t)kvh * (HS / 4);
+    const float4* vc = reinterpret_cast<const float4*>(P.vc) + (size_t)kvh * (HS / 4);
+    const size_t rs = (size_t)KV / 4;
+    for (int t0 = 0; t0 <= tmax; t0 += AT_TILE) {
+        __syncthreads();  // the previous tile has been used (and Qs is complete)
+        for (int i = tid; i < AT_TILE * (HS / 4); i += 32 * AT_WARPS) {
+            const int r = i / (HS / 4), c = i % (HS / 4), t = t0 + r;
+            float4 k = make_float4(0.f, 0.f, 0.f, 0.f), v = k;
+            if (t <= tmax) { k = kc[(size_t)t * rs + c]; v = vc[(size_t)t * rs + c]; }
+            reinterpret_cast<float4*>(Ks + r * AT_KPAD)[c] = k;
+            reinterpret_cast<float4*>(Vs + r * HS)[c] = v;
+        }
+        __syncthreads();
+        // scores of position t0 + lane for this warp's queries
+        float s[NQW];
+#pragma unroll
+        for (int q = 0; q < NQW; q++) s[q] = 0.f;
+        const float4* krow = reinterpret_cast<const float4*>(Ks + lane * AT_KPAD);
+        const float4* qrow = reinterpret_cast<const float4*>(Qs + (size_t)warp * NQW * HS);
+#pragma unroll 4
+        for (int c = 0; c < HS / 4; c++) {
+            const float4 k = krow[c];
+#pragma unroll
+            for (int q = 0; q < NQW; q++) {
+                const float4 qq = qrow[q * (HS / 4) + c];
+                s[q] = fmaf(qq.x, k.x, s[q]); s[q] = fmaf(qq.y, k.y, s[q]); s[q] = fmaf(qq.z, k.z, s[q]); s[q] = fmaf(qq.w, k.w, s[q]);
+            }
+        }
+        // online softmax per query, then the values
+        float p[NQW];
+#pragma unroll
+        for (int q = 0; q < NQW; q++) {
+            const bool valid = t0 + lane <= last[q / AG];
+            const float sc = valid ? __fdiv_rn(s[q], div) : -INFINITY;  // src/models.rs:158
+            float tm = sc;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
+            const float mn = fmaxf(mx[q], tm);
+            const float corr = mn == -INFINITY ? 1.f : expf(mx[q] - mn);
+            p[q] = valid ? expf(sc - mn) : 0.f;
+            const float ps = warp_sum_f(p[q]);
+            l[q] = l[q] * corr + ps;
+            acc[q].x *= corr; acc[q].y *= corr; acc[q].z *= corr; acc[q].w *= corr;
+            mx[q] = mn;
+        }
+        const float4* vcol = reinterpret_cast<const float4*>(Vs) + lane;
+#pragma unroll 4
+        for (int t = 0; t < AT_TILE; t++) {
+            const float4 v = vcol[t * (HS / 4)];
+#pragma unroll
+            for (int q = 0; q < NQW; q++) {
+                const float pq = __shfl_sync(0xffffffffu, p[q], t);
+                acc[q].x = fmaf(pq, v.x, acc[q].x); acc[q].y = fmaf(pq, v.y, acc[q].y);
+                acc[q].z = fmaf(pq, v.z, acc[q].z); acc[q].w = fmaf(pq, v.w, acc[q].w);
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < NQW; q++) {
+        const int qi = warp * NQW + q, m = m0 + qi / AG;
+        if (m < M) {
+            const float inv = 1.0f / l[q];
+            reinterpret_cast<float4*>(P.out + (size_t)m * P.ldo + (size_t)(kvh * AG + qi % AG) * HS)[lane] =
+                make_float4(acc[q].x * inv, acc[q].y * inv, acc[q].z * inv, acc[q].w * inv);
+        }
+    }
+}
+
+template <int AG, int NQW>
+static void launch_attn_tiled(const AttnBatchParams& p, int M, cudaStream_t st) {
+    constexpr int QB = AT_WARPS * (NQW / AG);
+    const size_t smem = (size_t)(AT_WARPS * NQW * HS + AT_TILE * AT_KPAD + AT_TILE * HS) * sizeof(float);
+    attn_batch_tiled_kernel<AG, NQW><<<dim3(p.n_kv_heads, (M + QB - 1) / QB), 32 * AT_WARPS, smem, st>>>(p, M);
+}
+
+// the tiled kernel's shared memory (65 KB at most) is above the default limit: once per device, at start-up
+cudaError_t attn_batch_init() {
+    const int smem = (AT_WARPS * 8 * HS + AT_TILE * AT_KPAD + AT_TILE * HS) * (int)sizeof(float);
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(attn_batch_tiled_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(attn_batch_tiled_kernel<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(attn_batch_tiled_kernel<4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(attn_batch_tiled_kernel<8, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+}
+
+// tiled: the kernel that shares cache tiles among queries (long contexts); otherwise one CTA per (head, token), which has
+// more CTAs and less set-up (short contexts: the cache is small and sits in the L2 anyway)
+void launch_attn_batch(const AttnBatchParams& p, int n_heads, int M, bool tiled, cudaStream_t st) {
     g_launches++;
-    attn_batch_kernel<<<dim3(n_heads, M), 128, 0, st>>>(p);
+    switch (tiled ? p.ag : 0) {
+        case 1: launch_attn_tiled<1, 4>(p, M, st); break;
+        case 2: launch_attn_tiled<2, 8>(p, M, st); break;
+        case 4: launch_attn_tiled<4, 8>(p, M, st); break;
+        case 8: launch_attn_tiled<8, 8>(p, M, st); break;
+        default: attn_batch_kernel<<<dim3(n_heads, M), 128, 0, st>>>(p); break;
+    }
 }
 // ---- all-gather of a column slice over peer memory (batched forward under tensor parallelism) ----------------------------
 // Every CTA copies rows of this rank's columns into the peers' buffers with plain stores.  The CTA that finishes last

@@ -34,6 +34,21 @@ def test_tiny_generate_parity(l2, orc, gs, kvh):
     assert slow["pos0"] == 0 and np.array_equal(slow["tokens"][20:], want["tokens"])
 
 
+@pytest.mark.parametrize("dim,kvh", [(256, 2), (256, 1), (512, 1), (1024, 1)])  # 1, 2, 4, 8 query heads per kv head
+def test_long_prompt_prefill_parity(l2, orc, dim, kvh):
+    # Past about 200 cached positions the batched forward switches to the attention kernel that shares cache tiles among the
+    # queries of a kv head: a 330-token prompt (ladder 5 x 64 + 8) runs it in its later passes, with a ragged last pass;
+    # the tokens decoded afterwards see every cache row it wrote.
+    cfg = tiny_config(l2, group_size=64, n_kv_heads=kvh, dim=dim, hidden=2 * dim, seq_len=512)
+    gpu, cpu = make_pair(l2, orc, cfg, seed=17)
+    prompt = np.random.default_rng(dim + kvh).integers(0, cfg.vocab_size, 330).astype(np.int32)
+    want = cpu.generate_ids(prompt, 340, trace_logits=True)
+    got = l2.generate_ids(gpu, prompt, 340, trace_logits=True)
+    assert got["pos0"] == want["pos0"] == 328
+    assert_close(got["logits"], want["logits"], what="logits after a long batched prefill")
+    assert np.array_equal(got["tokens"], want["tokens"])
+
+
 def test_golden_fixture(l2):
     g = np.load(os.path.join(GOLDEN, "tiny_generate.npz"))
     cfg = tiny_config(l2, group_size=int(g["group_size"]), n_kv_heads=int(g["n_kv_heads"]))
