@@ -150,3 +150,33 @@ def test_random_matches_oracle(l2, orc):
     for _ in range(10):
         assert a.random_u32() == orc.lib().orc_random_u32(C.byref(b))
     assert a.random() == orc.lib().orc_random_f32(C.byref(b))
+
+
+def test_bench_workloads_and_prefill_report():
+    """bench.py's workload table and the prefill roofline arithmetic (no GPU: a stand-in for the model handle)."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.WORKLOADS["7b"] == ("7B", 128, 32, 256) and bench.WORKLOADS["70b"] == ("70B", 64, 64, 256)
+    assert bench.WORKLOADS["70b-long"][2] + bench.WORKLOADS["70b-long"][3] == 2048  # the prompt and the decoded tokens fill the cache
+
+    class Cfg:
+        dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size = 4096, 11008, 32, 32, 32, 32000
+
+    class Model:
+        decode_bytes = 3991027712
+
+    r = bench.prefill_report(Model, Cfg, 30, 4.4, False, 6549.4, 1642.0, "measured")
+    assert r["weight_passes"] == 1 and r["executed_mma_inflation"] == 3
+    flops = 2.0 * 32 * (4 * 4096 * 4096 + 3 * 4096 * 11008) * 30
+    assert abs(r["tflops"] - flops / 4.4e-3 / 1e12) < 1e-6
+    qbytes = 3991027712 - 4.0 * 32000 * 4096 - 4.0 * 65 * 4096
+    assert abs(r["weight_gbs"] - qbytes / 4.4e-3 / 1e9) < 1e-6
+    # 130 positions need three passes of up to 64; under NCCL tensor parallelism every position is a pass
+    assert bench.prefill_report(Model, Cfg, 130, 10.0, False, 6549.4, 1642.0, "measured")["weight_passes"] == 3
+    assert bench.prefill_report(Model, Cfg, 130, 10.0, True, 6549.4, 1642.0, "measured")["weight_passes"] == 130
+    # a vocabulary-parallel rank streams a slice of the classifier: its QLinear bytes are what is left of its decode bytes
+    half = bench.prefill_report(Model, Cfg, 30, 4.4, False, 6549.4, 1642.0, "measured", cls_rows=16000)
+    assert half["weight_gbs"] > r["weight_gbs"]
