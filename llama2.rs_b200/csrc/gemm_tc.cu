@@ -21,7 +21,7 @@
 //   warps 4-11  drain: tcgen05.ld of the finished accumulator (a warp reads the 32 tensor-memory lanes of its
 //               quadrant and half of the token columns), zero point through the tokens' digit sums, one f32 FMA
 //               per (row, token) with the scale.  The group's scales, zero points and digit sums arrive in a side
-//               ring that the drain warps fill themselves, eight groups ahead.
+//               ring that the drain warps fill themselves, seven groups ahead.
 //   warp 12     one thread issues the MMAs of a group into one of two accumulators and commits once: the
 //               commit frees the A and B stages and tells the drain that the accumulator is complete.
 //   warp 13     one thread keeps three B stages filled, up to three groups ahead.
@@ -30,6 +30,8 @@
 // number, and the work is cut so that the bookkeeping of a group is paid by few warps.
 // Split K: the CTAs of a tile whose groups are divided among several (grid.y) store partial results, which
 // ksum_kernel adds in slice order (measured: letting the last CTA of a tile add them cost more than the extra launch).
+// The kernel is launched programmatically behind the activation quantiser: everything that does not read the quantiser's
+// output (set-up, tensor-memory allocation, the loaders' first requests) runs while that kernel still does.
 // Every wait on an mbarrier is bounded; a wait that gives up raises a flag that ends every loop.
 #include <cuda_runtime.h>
 
