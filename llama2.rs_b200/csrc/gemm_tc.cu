@@ -31,7 +31,10 @@
 // Split K: the CTAs of a tile whose groups are divided among several (grid.y) store partial results, which
 // ksum_kernel adds in slice order (measured: letting the last CTA of a tile add them cost more than the extra launch).
 // The kernel is launched programmatically behind the activation quantiser: everything that does not read the quantiser's
-// output (set-up, tensor-memory allocation, the loaders' first requests) runs while that kernel still does.
+// output (set-up, tensor-memory allocation, the loaders' first requests) runs while that kernel still does.  Extending the
+// chain (slice sum behind this kernel, the next quantiser behind the slice sum) was measured slower: the early-resident
+// kernels of the next projection take issue slots and bandwidth from the one that is running (1.13 -> 1.32 ms for eight
+// 7B layers at 30 tokens).
 // Every wait on an mbarrier is bounded; a wait that gives up raises a flag that ends every loop.
 #include <cuda_runtime.h>
 
