@@ -78,3 +78,25 @@ def test_tp_rows_rejects_ragged_splits(l2):
     r0, n = C.c_int(0), C.c_int(0)
     assert l2.lib.l2_tp_rows(8192, 3, 8, C.byref(r0), C.byref(n)) == 0 and (r0.value, n.value) == (3072, 1024)
     assert l2.lib.l2_tp_rows(1000, 0, 8, C.byref(r0), C.byref(n)) == -1
+
+
+def test_splits_of_the_70b_shapes_at_every_world_size(l2):
+    """What the tensor-parallel kernels assume about a rank's share: whole 16-row tiles of every projection, heads and kv heads
+    divided evenly, slices that are contiguous and cover the matrix; and the vocabulary slices of the classifier
+    (rows V r / T .. V (r + 1) / T) cover 0..V without overlap."""
+    cfg = l2.preset_config("70B", 64)
+    kv = cfg.dim * cfg.n_kv_heads // cfg.n_heads
+    for world in (1, 2, 4, 8):
+        assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0
+        for total in (cfg.dim, kv, cfg.hidden_dim):
+            end = 0
+            for rank in range(world):
+                r0, n = C.c_int(0), C.c_int(0)
+                assert l2.lib.l2_tp_rows(total, rank, world, C.byref(r0), C.byref(n)) == 0
+                assert r0.value == end and n.value == total // world and n.value % 16 == 0 and r0.value % 16 == 0
+                end = r0.value + n.value
+            assert end == total
+        edges = [cfg.vocab_size * r // world for r in range(world + 1)]
+        assert edges[0] == 0 and edges[-1] == cfg.vocab_size and all(b > a for a, b in zip(edges, edges[1:]))
+        # a rank's kv heads are whole heads of 128 values inside the full-width cache row
+        assert (kv // world) % 128 == 0
