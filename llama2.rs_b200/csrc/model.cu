@@ -512,6 +512,9 @@ static int tk_slots(const l2_state* s, size_t fixed, int su) {
 static bool tk_gather13(const l2_state* s) {
     const int su = 2 * SK_WARPS;
     if (const char* e = getenv("L2_TK_GATHER13")) return atoi(e) != 0;  // tuning knob
+    // under tensor parallelism staging is a larger share of a token (the weight stream shrinks, the vectors do not) and the
+    // gathered staging costs more than the larger L1 returns (70B on 4 GPUs: 148 tok/s without, 145 with)
+    if (s->m->tp_world > 1) return false;
     const size_t with = tk_fixed_bytes(s, true), without = tk_fixed_bytes(s, false);
     const size_t three = 3 * sk_slot_bytes(s->m->shape.c.group_size, su), small = 190 * 1024;
     if (without + three > small && with + three <= small) return true;
